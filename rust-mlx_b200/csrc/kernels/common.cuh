@@ -1,0 +1,60 @@
+// Shared helpers of the kernels: element types, loads and stores through float,
+// fixed-order reductions, and the error channel of the C entry points.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define RMX_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes of the C interface
+enum { RMX_F32 = 0, RMX_BF16 = 1 };
+
+// Every entry point returns 0 or a negative code and leaves a message for rmx_last_error().
+void rmx_set_error(const char* fmt, ...);
+#define RMX_FAIL(...)                 \
+    do {                              \
+        rmx_set_error(__VA_ARGS__);   \
+        return -1;                    \
+    } while (0)
+#define RMX_REQUIRE(cond, ...)        \
+    do {                              \
+        if (!(cond)) RMX_FAIL(__VA_ARGS__); \
+    } while (0)
+#define RMX_CHECK_LAUNCH(name)                                              \
+    do {                                                                    \
+        cudaError_t e__ = cudaGetLastError();                               \
+        if (e__ != cudaSuccess) RMX_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+    } while (0)
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Butterfly reductions: every lane ends with the same value, formed in the same order
+// whatever the data, so a row's result does not depend on what else is in the batch.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats.  Warps are added in
+// index order by every thread alike.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nwarps; ++w) total += scratch[w];
+    return total;
+}

@@ -1,0 +1,143 @@
+// Embedding gather, residual add + RMSNorm, and SwiGLU.
+//
+// The residual stream is float32 in every run; activations that kernels hand to one
+// another are in the compute type T (float or bfloat16).  Sums of squares, rsqrt and the
+// scaling are done in float and rounded once.
+#include "common.cuh"
+
+// h[t, :] = table[ids[t], :] as float.  An id outside the table writes zeros (the host
+// rejects such ids before the step; the kernel never reads outside the table).
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ h, int width, int vocab) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    const T* row = table + (size_t)(ok ? id : 0) * width;
+    float* out = h + (size_t)t * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = ok ? to_float(row[i]) : 0.f;
+}
+
+RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tokens, int width, int vocab,
+                          int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    RMX_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embedding: bad sizes");
+    const int threads = width >= 1024 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        embedding_kernel<float><<<n_tokens, threads, 0, s>>>(ids, (const float*)table, h, width, vocab);
+    else if (dtype == RMX_BF16)
+        embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, h, width, vocab);
+    else
+        RMX_FAIL("embedding: unknown dtype %d", dtype);
+    RMX_CHECK_LAUNCH("embedding");
+    return 0;
+}
+
+// One block per output row.  src_row = rows ? rows[r] : r.
+//   v = h[src_row] + delta[src_row]          (float; delta may be null)
+//   if (write_h) h[src_row] = v
+//   x[r] = v * rsqrt(mean(v^2) + eps) * w     (rounded once to T)
+// The reduction order depends on the width and the block size only.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta,
+                                   const int* __restrict__ rows, const float* __restrict__ w, float eps,
+                                   T* __restrict__ x, int width, int write_h) {
+    __shared__ float scratch[32];
+    extern __shared__ float vals[];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* hrow = h + (size_t)src * width;
+    const T* drow = delta ? delta + (size_t)src * width : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = hrow[i];
+        if (drow) v += to_float(drow[i]);
+        vals[i] = v;
+        if (write_h) hrow[i] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)width + eps);
+    T* xrow = x + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xrow[i] = from_float<T>(vals[i] * inv * w[i]);
+}
+
+RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const int* rows, const float* w, float eps, void* x,
+                            int n_rows, int width, int write_h, int dtype, void* stream) {
+    if (n_rows == 0) return 0;
+    RMX_REQUIRE(n_rows > 0 && width > 0, "add_rmsnorm: bad sizes");
+    RMX_REQUIRE((size_t)width * 4 <= 160 * 1024, "add_rmsnorm: width %d is beyond 40960", width);
+    RMX_REQUIRE(!(rows && write_h), "add_rmsnorm: rows and write_h do not go together");
+    const int threads = 256;
+    const size_t smem = (size_t)width * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<float><<<n_rows, threads, smem, s>>>(h, (const float*)delta, rows, w, eps, (float*)x, width, write_h);
+    } else if (dtype == RMX_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, s>>>(h, (const __nv_bfloat16*)delta, rows, w, eps,
+                                                                      (__nv_bfloat16*)x, width, write_h);
+    } else {
+        RMX_FAIL("add_rmsnorm: unknown dtype %d", dtype);
+    }
+    RMX_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+}
+
+// out[t, j] = silu(gate_up[t, j]) * gate_up[t, inter + j], silu(z) = z / (1 + exp(-z)),
+// in float with one rounding.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / inter;
+    const int j = (int)(idx - t * inter);
+    const float g = to_float(gate_up[t * 2 * inter + j]);
+    const float u = to_float(gate_up[t * 2 * inter + inter + j]);
+    const float sg = g / (1.f + expf(-g));
+    out[idx] = from_float<T>(sg * u);
+}
+
+RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    RMX_REQUIRE(n_tokens > 0 && inter > 0, "swiglu: bad sizes");
+    const size_t total = (size_t)n_tokens * inter;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
+    else if (dtype == RMX_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    else
+        RMX_FAIL("swiglu: unknown dtype %d", dtype);
+    RMX_CHECK_LAUNCH("swiglu");
+    return 0;
+}
+
+// h[t, :] += delta[t, :] (float add, delta in T): closes the residual stream when no norm follows.
+template <typename T>
+__global__ void add_residual_kernel(float* __restrict__ h, const T* __restrict__ delta, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) h[idx] += to_float(delta[idx]);
+}
+
+RMX_API int rmx_add_residual(float* h, const void* delta, int n_rows, int width, int dtype, void* stream) {
+    if (n_rows == 0) return 0;
+    const size_t total = (size_t)n_rows * width;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        add_residual_kernel<float><<<blocks, threads, 0, s>>>(h, (const float*)delta, total);
+    else if (dtype == RMX_BF16)
+        add_residual_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(h, (const __nv_bfloat16*)delta, total);
+    else
+        RMX_FAIL("add_residual: unknown dtype %d", dtype);
+    RMX_CHECK_LAUNCH("add_residual");
+    return 0;
+}

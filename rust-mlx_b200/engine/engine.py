@@ -1,0 +1,187 @@
+"""The engine: a model on one GPU, its cache, and the step function.
+
+``Engine.step`` takes a batch of (request, its next tokens) — portions of prompts
+beside single decoded tokens, cut anywhere — runs only those tokens, as one
+batch, against the cache that earlier steps left, and returns float32 logits at
+the wanted places.  The reference's ``DenseModel::forward`` (src/dense.rs:371-397)
+runs one request's tokens and returns logits of every position; its batched decode
+needs all rows at one offset (src/batching.rs:34-53).
+
+There is no CPU path: the engine needs a CUDA device and this package's kernels.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+import torch
+
+from ..cache.page_table import OutOfPages
+from ..cache.pools import CachePools
+from ..kernels import ops as _ops
+from ..parts.base import BuildContext
+from ..registry import build_model_spec, load_config
+from ..weights.loader import load_tensors
+from ..weights.random_init import random_tensors
+from .batch import SequenceInput, StepBatch, build_batch
+from .workspace import Workspace
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+def _log(msg):
+    print(f"[rust_mlx_b200] {msg}", file=sys.stderr, flush=True)
+
+
+class Engine:
+    """A model ready to step.
+
+    ``model``: a folder with config.json and safetensors, or (with
+    ``random_weights=True``) a typed configuration / a folder whose config.json alone
+    is read.  ``max_tokens``: how many tokens the cache holds in all (rounded up to
+    pages).  ``dtype``: "bfloat16" (serving kernels) or "float32" (every product,
+    norm and softmax in true 32-bit).
+    """
+
+    def __init__(self, model, *, dtype: str = "bfloat16", random_weights: bool = False, seed: int = 0,
+                 max_tokens: int = 8192, page_size: int = 64, max_requests: int = 256, device: str = "cuda:0",
+                 verbose: bool = False):
+        if dtype not in _DTYPES:
+            raise EngineError(f"dtype must be one of {sorted(set(_DTYPES))}, got {dtype!r}")
+        if not torch.cuda.is_available():
+            raise EngineError("no CUDA device: this engine runs on an NVIDIA B200 only and has no CPU path")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        major, minor = torch.cuda.get_device_capability(self.device)
+        if major != 10:
+            raise EngineError(f"the kernels are built for sm_100a; this device is sm_{major}{minor}")
+        self.dtype = _DTYPES[dtype]
+        self.dtype_name = "bfloat16" if self.dtype == torch.bfloat16 else "float32"
+        if page_size <= 0 or page_size & (page_size - 1):
+            raise EngineError(f"page_size must be a power of two, got {page_size}")
+        t0 = time.time()
+        _ops.kernels_library()  # builds at first use; raises if the extension cannot be had
+        folder = None
+        if isinstance(model, (str, os.PathLike)):
+            folder = os.fspath(model)
+            self.config = load_config(folder)
+        else:
+            self.config = model
+        self.spec = build_model_spec(self.config)
+        self.workspace = Workspace(self.device)
+        ctx = BuildContext(self.device, self.dtype, _ops, self.workspace)
+        specs = self.spec.all_param_specs()
+        if random_weights:
+            tensors = random_tensors(specs, seed, self.dtype, self.device)
+        else:
+            if folder is None:
+                raise EngineError("a model folder is needed unless random_weights is set")
+            progress = (lambda i, n, name: _log(f"loaded {i}/{n} tensors") if i % 64 == 0 else None) if verbose else None
+            tensors = load_tensors(folder, specs, self.dtype, self.device, self.spec.ignored_tensors, progress)
+        self.spec.bind_all(tensors, ctx)
+        del tensors
+        self.vocab_size = self.spec.vocab_size
+        self.page_size = page_size
+        self.pools = CachePools(self.spec.cache_specs(), max_tokens=max_tokens, page_size=page_size,
+                                max_requests=max_requests, dtype=self.dtype, device=self.device)
+        # which schedule entry writes each cache: the first that names it
+        seen = set()
+        self._calls = []
+        for call in self.spec.schedule:
+            self._calls.append((call, call.cache in seen))
+            seen.add(call.cache)
+        self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._req_ids = {}
+        self._next_id = 0
+        self.load_seconds = time.time() - t0
+        if verbose:
+            _log(f"model ready in {self.load_seconds:.1f}s: {len(self.spec.blocks)} layers, {self.dtype_name}, "
+                 f"{self.pools.num_pages} pages of {page_size}")
+
+    # ------------------------------------------------------------------ requests
+    def _rid(self, key) -> int:
+        rid = self._req_ids.get(key)
+        if rid is None:
+            rid = self._next_id
+            self._next_id += 1
+            self._req_ids[key] = rid
+        return rid
+
+    def length(self, key) -> int:
+        """Tokens of request ``key`` in the cache (0 if it is not live)."""
+        rid = self._req_ids.get(key)
+        if rid is None or not self.pools.table.has(rid):
+            return 0
+        return self.pools.table.length(rid)
+
+    def release(self, key) -> None:
+        """The request is finished: its pages and its slot are given back."""
+        rid = self._req_ids.pop(key, None)
+        if rid is not None and self.pools.table.has(rid):
+            self.pools.table.close(rid)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: list, end=()) -> torch.Tensor:
+        """Run one batch.  ``entries``: (request, tokens, want) triples; ``want`` lists the
+        places among these tokens whose logits are asked for.  Returns float32 logits
+        [wanted, vocab] on the device, in the order of the entries and of ``want``.
+        Requests in ``end`` are released after the step.  Raises ``OutOfPages`` (and
+        changes nothing) if the cache cannot hold the step's tokens."""
+        table = self.pools.table
+        seqs, opened, grown = [], [], []
+        try:
+            keys = set()
+            for key, tokens, want in entries:
+                if key in keys:
+                    raise EngineError(f"request {key!r} appears twice in one step")
+                keys.add(key)
+                rid = self._rid(key)
+                if not table.has(rid):
+                    self.pools.open(rid)
+                    opened.append((key, rid))
+                start = table.length(rid)
+                table.reserve(rid, start + len(tokens))
+                seqs.append(SequenceInput(rid, start, list(tokens), list(want)))
+            batch = build_batch(seqs, self.pools, self.device, self._status, self.vocab_size)
+        except Exception:
+            for s in seqs:
+                table.release_reserved(s.req)
+            for key, rid in opened:
+                table.close(rid)
+                self._req_ids.pop(key, None)
+            raise
+        logits = self.forward(batch)
+        self.check_status()
+        for s in seqs:
+            table.commit(s.req, s.start + len(s.tokens))
+        for key in end:
+            self.release(key)
+        return logits
+
+    def forward(self, batch: StepBatch) -> torch.Tensor:
+        """The model over one batch whose pages are reserved: embedding, the schedule's
+        layer runs, then final norm and head on the wanted rows."""
+        spec = self.spec
+        h = spec.embedding.forward(batch.token_ids)
+        pending = None
+        for call, read_only in self._calls:
+            cache = self.pools.view(call.cache, batch, read_only) if call.cache in self.pools._where else None
+            h, pending = spec.blocks[call.layer].forward(h, pending, batch, cache)
+        if batch.n_rows == 0:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        x = spec.final_norm.forward_rows(h, pending, batch.logit_rows)
+        return spec.head.forward(x)
+
+    def check_status(self) -> None:
+        """Kernels report what they could not do (a token without a page) in a status word."""
+        code = int(self._status.item())
+        if code != 0:
+            self._status.zero_()
+            what = {1: "a key was to be written to a position without a page",
+                    2: "a key was to be read from a position without a page"}.get(code, f"code {code}")
+            raise EngineError(f"a kernel refused its input: {what}")

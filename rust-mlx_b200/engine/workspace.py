@@ -1,0 +1,35 @@
+"""Scratch tensors that kernels hand to one another, kept between steps.
+
+``get(name, shape, dtype)`` returns a view of a buffer that lives as long as the
+engine; a buffer grows when a larger shape is asked for, unless the workspace is
+frozen (while a CUDA graph that holds its addresses exists).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+
+class Workspace:
+    def __init__(self, device):
+        self.device = device
+        self.buffers = {}
+        self.frozen = False
+
+    def get(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        numel = math.prod(shape)
+        key = (name, dtype)
+        buf = self.buffers.get(key)
+        if buf is None or buf.numel() < numel:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name} would have to grow to {numel} while frozen")
+            buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            self.buffers[key] = buf
+        return buf[:numel].view(shape)
+
+    def reserve(self, name: str, shape: tuple, dtype: torch.dtype) -> None:
+        self.get(name, shape, dtype)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self.buffers.values())

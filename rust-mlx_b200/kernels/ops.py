@@ -1,0 +1,167 @@
+"""Python faces of the CUDA kernels.
+
+Every function takes torch tensors on the CUDA device, checks what the kernel
+assumes (device, dtype, contiguity), and launches on torch's current stream.
+There is no CPU path: a tensor that is not on a CUDA device is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from .library import KernelError, check, kernels_library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+# how many launches of this package's kernels were made (bench reports it)
+launch_count = 0
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {t.dtype}: kernels take float32 and bfloat16") from None
+
+
+def _ptr(t, dtype=None, name="tensor"):
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}: kernels run on a CUDA device only")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    return c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _launched(n=1):
+    global launch_count
+    launch_count += n
+
+
+def embedding(ids, table, h_out):
+    """h_out[t] = table[ids[t]] as float32 (the residual stream)."""
+    lib = kernels_library()
+    n, width = h_out.shape
+    check(lib.rmx_embedding(_ptr(ids, torch.int32, "ids"), _ptr(table, name="table"), _ptr(h_out, torch.float32, "h"),
+                            c_int(n), c_int(width), c_int(table.shape[0]), c_int(dtype_code(table)), _stream()))
+    _launched()
+
+
+def add_rmsnorm(h, delta, weight, eps, x_out, rows=None, write_h=True):
+    """v = h + delta; h = v (if write_h); x_out = RMSNorm(v; weight, eps).  With ``rows`` the
+    rows rows[r] are read, x_out[r] is written and h is left alone."""
+    lib = kernels_library()
+    n = x_out.shape[0]
+    width = h.shape[1]
+    if delta is not None and delta.dtype != x_out.dtype:
+        raise KernelError("add_rmsnorm: delta and output must have the same dtype")
+    check(lib.rmx_add_rmsnorm(_ptr(h, torch.float32, "h"), _ptr(delta, name="delta"), _ptr(rows, torch.int32, "rows"),
+                              _ptr(weight, torch.float32, "weight"), c_float(eps), _ptr(x_out, name="x"),
+                              c_int(n), c_int(width), c_int(1 if (write_h and rows is None) else 0),
+                              c_int(dtype_code(x_out)), _stream()))
+    _launched()
+
+
+def add_residual(h, delta):
+    lib = kernels_library()
+    check(lib.rmx_add_residual(_ptr(h, torch.float32, "h"), _ptr(delta, name="delta"), c_int(h.shape[0]),
+                               c_int(h.shape[1]), c_int(dtype_code(delta)), _stream()))
+    _launched()
+
+
+def swiglu(gate_up, out):
+    lib = kernels_library()
+    n, inter = out.shape
+    if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype:
+        raise KernelError("swiglu: gate_up must be [tokens, 2 * inter] of the output's dtype")
+    check(lib.rmx_swiglu(_ptr(gate_up, name="gate_up"), _ptr(out, name="out"), c_int(n), c_int(inter),
+                         c_int(dtype_code(out)), _stream()))
+    _launched()
+
+
+def gemm_plain(a, w, out):
+    """out[M, N] = a[M, K] . w[N, K]^T on the FMA units, k in ascending order."""
+    lib = kernels_library()
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n) or a.dtype != w.dtype:
+        raise KernelError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not fit")
+    check(lib.rmx_gemm_plain(_ptr(a, name="a"), _ptr(w, name="w"), _ptr(out, name="out"), c_int(m), c_int(n), c_int(k),
+                             c_int(k), c_int(k), c_int(n), c_int(dtype_code(a)), c_int(dtype_code(out)), _stream()))
+    _launched()
+
+
+def qk_rope_cache(qkv, q_norm, k_norm, eps, inv_freq, rotary_dim, positions, seq_index, block_table, page_size,
+                  k_pool, v_pool, q_out, nq, nkv, hd, write_kv, status):
+    lib = kernels_library()
+    n = qkv.shape[0]
+    check(lib.rmx_qk_rope_cache(
+        _ptr(qkv, name="qkv"), _ptr(q_norm, torch.float32, "q_norm"), _ptr(k_norm, torch.float32, "k_norm"),
+        c_float(eps), _ptr(inv_freq, torch.float32, "inv_freq"), c_int(rotary_dim),
+        _ptr(positions, torch.int32, "positions"), _ptr(seq_index, torch.int32, "seq_index"),
+        _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
+        _ptr(k_pool, qkv.dtype, "k_pool"), _ptr(v_pool, qkv.dtype, "v_pool"), _ptr(q_out, qkv.dtype, "q_out"),
+        c_int(n), c_int(nq), c_int(nkv), c_int(hd), c_int(qkv.shape[1]), c_int(1 if write_kv else 0),
+        _ptr(status, torch.int32, "status"), c_int(dtype_code(qkv)), _stream()))
+    _launched()
+
+
+def attention_plain(q, k_pool, v_pool, positions, seq_index, block_table, page_size, out, nq, nkv, hd, window,
+                    scale, status):
+    lib = kernels_library()
+    n = q.shape[0]
+    check(lib.rmx_attention_plain(
+        _ptr(q, name="q"), _ptr(k_pool, q.dtype, "k_pool"), _ptr(v_pool, q.dtype, "v_pool"),
+        _ptr(positions, torch.int32, "positions"), _ptr(seq_index, torch.int32, "seq_index"),
+        _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
+        _ptr(out, q.dtype, "out"), c_int(n), c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale),
+        _ptr(status, torch.int32, "status"), c_int(dtype_code(q)), _stream()))
+    _launched()
+
+
+def sample(logits, temperature, uniform, out):
+    """out[r] = greedy choice (temperature None or 0) or a draw from softmax(logits / temperature)."""
+    lib = kernels_library()
+    r, v = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("sample: logits rows must be contiguous")
+    if not logits.is_cuda or logits.dtype != torch.float32:
+        raise KernelError("sample: logits must be float32 on a CUDA device")
+    check(lib.rmx_sample(c_void_p(logits.data_ptr()), c_int(logits.stride(0)), _ptr(temperature, torch.float32, "temperature"),
+                         _ptr(uniform, torch.float32, "uniform"), _ptr(out, torch.int32, "out"), c_int(r), c_int(v),
+                         _stream()))
+    _launched()
+
+
+# ---------------------------------------------------------------------------
+# Dispatch: which kernel serves a call.  float32 always takes the plain kernels (fixed
+# order of summation, no tensor cores); bfloat16 takes the fast ones where they apply.
+
+def linear(x, w, out):
+    """out = x . w^T.  w is [out_features, in_features] as stored in the checkpoint."""
+    if x.dtype == torch.float32:
+        gemm_plain(x, w, out)
+    else:
+        linear_bf16(x, w, out)
+
+
+def linear_bf16(x, w, out):
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)
+    else:
+        gemm_plain(x, w, out)
+
+
+def attention(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale):
+    attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
+                    window, scale, batch.status)

@@ -1,0 +1,149 @@
+"""Interfaces that every part of a layer implements.
+
+A model is an embedding, a list of blocks, a schedule that says in which order
+the blocks run and which cache each run uses, a final norm and an output head.
+A block is put together from a mixer, a feed-forward and norms; an attention
+mixer takes a position encoding.  Every part is built from sizes and constants
+only (no part sees a model configuration), declares the tensors it needs by
+their checkpoint names, and is bound to them once they are on the device.
+
+The reference holds the same split with concrete types: ``Attention`` with its
+constants as fields (src/dense.rs:112-126), ``Mlp`` (272-299), the norms as bare
+arrays in ``DenseLayer`` (300-305).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    """One tensor a part needs.
+
+    ``init`` names the recipe of the random-weights mode ("linear", "embedding":
+    N(0, 0.02); "norm": 1 + N(0, 0.05); "zeros"; "ones").  ``keep`` says how the tensor is
+    held on the device: "compute" follows the run's dtype (bfloat16 or float32),
+    "float32" stays 32-bit whatever the run's dtype, "int32" is an integer table.
+    """
+
+    name: str
+    shape: tuple
+    init: str = "linear"
+    keep: str = "compute"
+
+
+@dataclass(frozen=True)
+class CacheSpec:
+    """What a mixer needs to remember per request.
+
+    kind "paged": keys and values per token, ``kv_heads`` x ``head_dim`` each, in
+    pages; ``window`` > 0 means only the last ``window`` positions are ever read, so
+    older pages can be given back.  kind "state": ``state_shape`` numbers of
+    ``state_dtype`` per request, of fixed size, zero when a request starts.
+    Layers with equal specs share a cache group (one page pool geometry, one block
+    table per request).
+    """
+
+    kind: str
+    kv_heads: int = 0
+    head_dim: int = 0
+    window: int = 0
+    state_shape: tuple = ()
+    state_dtype: str = "float32"
+
+    def group_key(self) -> tuple:
+        if self.kind == "paged":
+            return ("paged", self.kv_heads, self.head_dim, self.window)
+        return ("state", self.state_shape, self.state_dtype)
+
+
+@dataclass
+class BuildContext:
+    """What ``bind`` gets besides the tensors: the device, the compute dtype and the ops."""
+
+    device: torch.device
+    dtype: torch.dtype
+    ops: object
+    workspace: object
+
+
+class Part:
+    """Base of mixers, feed-forwards, norms, position encodings, embeddings and heads."""
+
+    def param_specs(self) -> list:
+        return []
+
+    def bind(self, tensors: dict, ctx: BuildContext) -> None:
+        """Take this part's tensors (by the names of ``param_specs``) from ``tensors``."""
+        self.ctx = ctx
+
+    def children(self) -> list:
+        return []
+
+    def all_param_specs(self) -> list:
+        specs = list(self.param_specs())
+        for c in self.children():
+            specs.extend(c.all_param_specs())
+        return specs
+
+    def bind_all(self, tensors: dict, ctx: BuildContext) -> None:
+        for c in self.children():
+            c.bind_all(tensors, ctx)
+        self.bind(tensors, ctx)
+
+
+class Norm(Part):
+    """``forward(h, delta) -> (h, x)``: adds ``delta`` (or nothing) to the 32-bit residual
+    stream ``h`` in place and returns the normalised rows in the compute dtype."""
+
+    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor]):
+        raise NotImplementedError
+
+    def forward_rows(self, h, delta, rows):
+        """The same for the rows ``rows`` (int32 indices) only; ``h`` is left as it is."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Gives the rotation table an attention mixer hands to its kernel:
+    ``rotary_dim`` (0: no rotation) and ``inv_freq`` (float32, rotary_dim/2 entries)."""
+
+    rotary_dim: int = 0
+    inv_freq: Optional[torch.Tensor] = None
+
+
+class Mixer(Part):
+    """``forward(x, batch, cache) -> y`` over the flat token batch ``x`` [tokens, width].
+
+    ``cache_spec`` says what the mixer remembers per request (None: nothing);
+    ``cache`` is the view of its cache group for this run of the layer: pools,
+    block tables or state slots (see ``cache.views``).  ``cache.read_only`` is set
+    when the schedule lets this run read a cache that another run writes."""
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return None
+
+    def forward(self, x: torch.Tensor, batch, cache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """``forward(x) -> y`` row by row: [tokens, width] -> [tokens, width]."""
+
+    def forward(self, x: torch.Tensor, batch=None):
+        raise NotImplementedError
+
+
+@dataclass(frozen=True)
+class LayerCall:
+    """One entry of a model's schedule: run block ``layer`` with cache ``cache``.
+
+    The first entry that names a cache writes it; a later entry with the same cache
+    reads what the first wrote and writes nothing.  A block may appear in several
+    entries (it then runs more than once with the same weights)."""
+
+    layer: int
+    cache: int

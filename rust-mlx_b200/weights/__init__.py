@@ -1,0 +1,6 @@
+from .loader import WeightsError, load_tensors
+from .random_init import random_tensors, write_random_model
+from .safetensors_io import SafetensorsError, SafetensorsFile, save_file
+
+__all__ = ["WeightsError", "load_tensors", "random_tensors", "write_random_model", "SafetensorsError",
+           "SafetensorsFile", "save_file"]

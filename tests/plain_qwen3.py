@@ -1,0 +1,225 @@
+"""A plain, slow implementation of the Qwen3 dense decoder, for tests only.
+
+Whole sequences, no cache, no batching, one function for each part, float64
+arithmetic on the CPU.  It shares no code with the engine: it reads the model
+folder with the ``safetensors`` package and restates the reference's formulas,
+each cited by file:line of d9beuD/rust-mlx.
+
+The reference's own model code cannot be compiled or imported on this machine
+(no Rust toolchain, no MLX), so this file rests on the formulas; it is anchored
+on the reference's shipped fixture instead (tests/fixtures/dense: weights, a
+prompt, the logits of its last position and 32 greedy tokens), see
+tests/test_plain_fixture.py and tests/golden/.
+
+``rounding="bfloat16"`` restates what the engine's bfloat16 path stores between
+kernels: matrices are rounded to bfloat16, and so is every activation that the
+engine writes to memory in bfloat16 (the residual stream, softmax, norms and
+rotations stay unrounded, as the engine computes them in 32-bit).
+"""
+import json
+import math
+import os
+
+import torch
+from safetensors import safe_open
+
+F = torch.float64
+
+
+def read_folder(folder):
+    """config.json as a dict and every tensor by name (src/weights.rs:22-63)."""
+    with open(os.path.join(folder, "config.json")) as fh:
+        config = json.load(fh)
+    tensors = {}
+    for name in sorted(os.listdir(folder)):
+        if name.endswith(".safetensors"):
+            with safe_open(os.path.join(folder, name), framework="pt") as f:
+                for key in f.keys():
+                    tensors[key] = f.get_tensor(key)
+    return config, tensors
+
+
+def make_round(rounding):
+    if rounding in (None, "float32", "none"):
+        return lambda t: t
+    if rounding == "bfloat16":
+        return lambda t: t.to(torch.bfloat16).to(F)
+    raise ValueError(rounding)
+
+
+def rope_theta(config):
+    """rope_theta, else rope_parameters.rope_theta, else 1e6 (src/dense.rs:323-332)."""
+    if config.get("rope_theta") is not None:
+        return float(config["rope_theta"])
+    params = config.get("rope_parameters") or {}
+    if params.get("rope_theta") is not None:
+        return float(params["rope_theta"])
+    return 1e6
+
+
+def layer_windows(config):
+    """Window of every layer (0: all keys).  The reference's dense model has no window
+    (src/dense.rs:249-256); a window is used only where config.json asks for it."""
+    n = config["num_hidden_layers"]
+    if not config.get("use_sliding_window"):
+        return [0] * n
+    w = int(config["sliding_window"])
+    kinds = config.get("layer_types")
+    if not kinds:
+        kinds = ["sliding_attention" if i >= config.get("max_window_layers", 0) else "full_attention"
+                 for i in range(n)]
+    return [w if k == "sliding_attention" else 0 for k in kinds]
+
+
+def embedding(table, ids):
+    """h = embed_tokens.weight[ids] (src/weights.rs:203-204, src/dense.rs:378-379)."""
+    return table[torch.as_tensor(ids, dtype=torch.long)]
+
+
+def rms_norm(v, weight, eps):
+    """v * rsqrt(mean(v^2) + eps) * weight over the last axis (src/dense.rs:382; the
+    same shape of formula, written out, in src/compiled.rs:22-28 — dense uses the
+    plain weight, not weight + 1)."""
+    ms = (v * v).mean(dim=-1, keepdim=True)
+    return v * torch.rsqrt(ms + eps) * weight
+
+
+def linear(x, weight):
+    """y = x . W^T with W stored [out, in] (src/weights.rs:196)."""
+    return x @ weight.t()
+
+
+def rope(x, positions, theta, rotary_dim):
+    """Half-split rotation of the first ``rotary_dim`` numbers of each head:
+    pairs (j, j + rotary_dim/2), inv_freq[j] = theta^(-2j/rotary_dim),
+    out[j] = x[j] cos - x[j+half] sin, out[j+half] = x[j+half] cos + x[j] sin
+    (src/dense.rs:187-195 with traditional=false; kernels/text_rope.metal:3-14).
+    x: [T, heads, head_dim]; positions: [T]."""
+    half = rotary_dim // 2
+    j = torch.arange(half, dtype=F)
+    inv_freq = theta ** (-2.0 * j / rotary_dim)
+    angle = positions.to(F)[:, None] * inv_freq[None, :]          # [T, half]
+    cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+    a, b = x[..., :half], x[..., half:rotary_dim]
+    out = x.clone()
+    out[..., :half] = a * cos - b * sin
+    out[..., half:rotary_dim] = b * cos + a * sin
+    return out
+
+
+def attention_scores(q, k, v, positions, window):
+    """softmax(scale * q k^T + mask) v with scale = head_dim^-0.5, causal mask aligned
+    to the end, query head i reading kv head i // (heads / kv_heads)
+    (src/dense.rs:221-227, 249-256).  q: [T, nq, hd]; k, v: [T, nkv, hd].
+    ``window`` > 0: a query at position p sees keys p - window + 1 .. p only."""
+    T, nq, hd = q.shape
+    nkv = k.shape[1]
+    group = nq // nkv
+    scale = hd ** -0.5
+    pos = positions.to(torch.long)
+    allowed = pos[None, :] <= pos[:, None]
+    if window > 0:
+        allowed &= pos[None, :] > pos[:, None] - window
+    out = torch.empty_like(q)
+    for head in range(nq):
+        kh = head // group
+        s = (q[:, head, :] @ k[:, kh, :].t()) * scale
+        s = s.masked_fill(~allowed, float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        out[:, head, :] = p @ v[:, kh, :]
+    return out
+
+
+def attention(x, w, prefix, config, positions, window, rnd):
+    """q/k/v projections, per-head RMSNorm of q and k before the rotation, rotation of
+    all head_dim numbers, attention, output projection (src/dense.rs:139-270)."""
+    T = x.shape[0]
+    nq, nkv, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+    eps = config["rms_norm_eps"]
+    q = rnd(linear(x, w[prefix + ".q_proj.weight"])).reshape(T, nq, hd)       # dense.rs:147,155
+    k = rnd(linear(x, w[prefix + ".k_proj.weight"])).reshape(T, nkv, hd)      # dense.rs:157-160
+    v = rnd(linear(x, w[prefix + ".v_proj.weight"])).reshape(T, nkv, hd)      # dense.rs:161-165
+    q = rms_norm(q, w[prefix + ".q_norm.weight"], eps)                       # dense.rs:169
+    k = rms_norm(k, w[prefix + ".k_norm.weight"], eps)                       # dense.rs:175
+    theta = rope_theta(config)
+    q = rnd(rope(q, positions, theta, hd))                                   # dense.rs:187-195
+    k = rnd(rope(k, positions, theta, hd))                                   # dense.rs:206-214
+    o = rnd(attention_scores(q, k, v, positions, window))                    # dense.rs:249-256
+    return rnd(linear(o.reshape(T, nq * hd), w[prefix + ".o_proj.weight"]))  # dense.rs:258-269
+
+
+def swiglu_mlp(x, w, prefix, rnd):
+    """down(silu(gate(x)) * up(x)), silu(z) = z * sigmoid(z) (src/dense.rs:293-298;
+    src/compiled.rs:7-12: the product is formed without rounding silu(gate) first)."""
+    g = rnd(linear(x, w[prefix + ".gate_proj.weight"]))
+    u = rnd(linear(x, w[prefix + ".up_proj.weight"]))
+    act = rnd(g * torch.sigmoid(g) * u)
+    return rnd(linear(act, w[prefix + ".down_proj.weight"]))
+
+
+def prepare_weights(config, tensors, rounding):
+    """Weights in float64; for the bfloat16 restatement matrices are rounded to bfloat16
+    first, one-dimensional tensors (norm weights) keep the precision they are stored in."""
+    out = {}
+    for name, t in tensors.items():
+        if rounding == "bfloat16" and t.dim() >= 2:
+            t = t.to(torch.bfloat16)
+        out[name] = t.to(F)
+    return out
+
+
+def forward(config, w, ids, rounding=None, positions=None):
+    """Logits [T, vocab] of the whole sequence ``ids`` (src/dense.rs:371-397)."""
+    rnd = make_round(rounding)
+    T = len(ids)
+    if any(i < 0 or i >= config["vocab_size"] for i in ids):
+        raise ValueError("token outside vocabulary")                          # dense.rs:374-377
+    if positions is None:
+        positions = torch.arange(T)
+    eps = config["rms_norm_eps"]
+    windows = layer_windows(config)
+    h = embedding(w["model.embed_tokens.weight"], ids)                        # dense.rs:379
+    for i in range(config["num_hidden_layers"]):
+        p = f"model.layers.{i}"
+        x = rnd(rms_norm(h, w[p + ".input_layernorm.weight"], eps))           # dense.rs:382
+        h = h + attention(x, w, p + ".self_attn", config, positions, windows[i], rnd)  # dense.rs:381
+        x = rnd(rms_norm(h, w[p + ".post_attention_layernorm.weight"], eps))  # dense.rs:385-389
+        h = h + swiglu_mlp(x, w, p + ".mlp", rnd)                             # dense.rs:385
+    x = rnd(rms_norm(h, w["model.norm.weight"], eps))                         # dense.rs:391
+    head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings") else w["lm_head.weight"]
+    return linear(x, head)                                                    # dense.rs:392-396
+
+
+def argmax_lowest(logits):
+    """Greedy choice; ties go to the lowest id (kernels/greedy_reduce.metal:10-14)."""
+    m = logits.max()
+    return int(torch.nonzero(logits == m)[0, 0])
+
+
+def greedy(config, w, prompt, n, rounding=None):
+    """n greedy tokens after ``prompt``, recomputing the whole sequence for each
+    (the loop of src/bin/parity.rs:41-45 without its cache)."""
+    ids = list(prompt)
+    out = []
+    for _ in range(n):
+        t = argmax_lowest(forward(config, w, ids, rounding)[-1])
+        out.append(t)
+        ids.append(t)
+    return out
+
+
+class PlainModel:
+    """A folder read once: ``logits(ids)`` and ``greedy(prompt, n)``."""
+
+    def __init__(self, folder, rounding=None):
+        self.config, tensors = read_folder(folder)
+        if "head_dim" not in self.config:
+            self.config["head_dim"] = self.config["hidden_size"] // self.config["num_attention_heads"]
+        self.rounding = rounding
+        self.w = prepare_weights(self.config, tensors, rounding)
+
+    def logits(self, ids):
+        return forward(self.config, self.w, list(ids), self.rounding)
+
+    def greedy(self, prompt, n):
+        return greedy(self.config, self.w, prompt, n, self.rounding)

@@ -1,0 +1,45 @@
+"""Tiny configurations and helpers shared by the tests.
+
+A and B differ in every size and option: layers, width, head counts and group size,
+head_dim (A: heads * head_dim equals the width, B: it does not), feed-forward width,
+vocabulary (B: odd), rope_theta, eps, tied or untied head, page size, and B's upper
+layers attend through a sliding window.
+"""
+import os
+import random
+
+import torch
+
+TINY_A = dict(
+    model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=64,
+    num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=128, vocab_size=256,
+    rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096)
+PAGE_A = 16
+
+TINY_B = dict(
+    model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, hidden_size=96,
+    num_attention_heads=6, num_key_value_heads=2, head_dim=32, intermediate_size=160, vocab_size=509,
+    rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=4096,
+    use_sliding_window=True, sliding_window=20, max_window_layers=1)
+PAGE_B = 8
+
+CONFIGS = {"A": (TINY_A, PAGE_A), "B": (TINY_B, PAGE_B)}
+
+
+def make_folder(tmp_path, raw: dict, seed: int = 0, store: str = "float32") -> str:
+    """Write a model folder with the engine's random-weights mode."""
+    from rust_mlx_b200.config import Qwen3Config
+    from rust_mlx_b200.weights import write_random_model
+    folder = os.path.join(str(tmp_path), f"model_{abs(hash(str(sorted(raw.items()))))%10**8}_{seed}_{store}")
+    if not os.path.exists(os.path.join(folder, "model.safetensors")):
+        write_random_model(Qwen3Config.from_dict(raw), folder, seed=seed, store_dtype=store)
+    return folder
+
+
+def prompts(vocab: int, lengths, seed: int = 1) -> list:
+    rng = random.Random(seed)
+    return [[rng.randrange(vocab) for _ in range(n)] for n in lengths]
+
+
+def max_abs(a: torch.Tensor, b: torch.Tensor) -> float:
+    return (a.double() - b.double()).abs().max().item()
