@@ -140,6 +140,9 @@ class Engine:
                 if key in keys:
                     raise EngineError(f"request {key!r} appears twice in one step")
                 keys.add(key)
+                if any((not isinstance(t, int)) or t < 0 or t >= self.vocab_size for t in tokens):
+                    raise ValueError(f"request {key!r}: token outside vocabulary")
+            for key, tokens, want in entries:
                 rid = self._rid(key)
                 if not table.has(rid):
                     self.pools.open(rid)
@@ -161,7 +164,7 @@ class Engine:
             table.commit(s.req, s.start + len(s.tokens))
         for key in end:
             self.release(key)
-        return logits
+        return logits.clone()  # the caller's own: the workspace buffer is written again by the next step
 
     def forward(self, batch: StepBatch) -> torch.Tensor:
         """The model over one batch whose pages are reserved: embedding, the schedule's
@@ -176,6 +179,16 @@ class Engine:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         x = spec.final_norm.forward_rows(h, pending, batch.logit_rows)
         return spec.head.forward(x)
+
+    def generate(self, prompts: list, **options):
+        """Token ids in, token ids out: see ``engine.generate.generate``.  Returns the list of
+        generated ids per prompt."""
+        from .generate import generate
+        return generate(self, prompts, **options).tokens
+
+    def generate_detailed(self, prompts: list, **options):
+        from .generate import generate
+        return generate(self, prompts, **options)
 
     def check_status(self) -> None:
         """Kernels report what they could not do (a token without a page) in a status word."""

@@ -94,11 +94,14 @@ def rope(x, positions, theta, rotary_dim):
     pairs (j, j + rotary_dim/2), inv_freq[j] = theta^(-2j/rotary_dim),
     out[j] = x[j] cos - x[j+half] sin, out[j+half] = x[j+half] cos + x[j] sin
     (src/dense.rs:187-195 with traditional=false; kernels/text_rope.metal:3-14).
+    The table of inverse frequencies is held in float32 and the angle is the float32
+    product float(pos) * inv_freq[j], as in kernels/text_rope.metal:11 and
+    src/rope.rs:21-27; sine, cosine and the rotation are then exact here.
     x: [T, heads, head_dim]; positions: [T]."""
     half = rotary_dim // 2
     j = torch.arange(half, dtype=F)
-    inv_freq = theta ** (-2.0 * j / rotary_dim)
-    angle = positions.to(F)[:, None] * inv_freq[None, :]          # [T, half]
+    inv_freq = (theta ** (-2.0 * j / rotary_dim)).to(torch.float32)
+    angle = (positions.to(torch.float32)[:, None] * inv_freq[None, :]).to(F)   # [T, half]
     cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
     a, b = x[..., :half], x[..., half:rotary_dim]
     out = x.clone()

@@ -1,0 +1,178 @@
+"""Generation through the entry points against the plain implementation."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def workdir(tmp_path_factory):
+    return tmp_path_factory.mktemp("generate")
+
+
+def engine(folder, dtype, page, tokens=2048, requests=8):
+    from rust_mlx_b200.engine import Engine
+    return Engine(folder, dtype=dtype, max_tokens=tokens, page_size=page, max_requests=requests)
+
+
+@pytest.mark.parametrize("name, lengths, n, chunk", [("A", [5, 17, 33], 8, 7), ("B", [1, 9, 24, 40], 6, 5)])
+def test_greedy_generation_equals_the_plain_implementation(workdir, name, lengths, n, chunk):
+    raw, page = tiny.CONFIGS[name]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=11))
+    ps = tiny.prompts(raw["vocab_size"], lengths, seed=5)
+    pm = plain.PlainModel(folder)
+    want = [pm.greedy(p, n) for p in ps]
+    eng = engine(folder, "float32", page)
+    assert eng.generate(ps, max_tokens=n, prefill_chunk=chunk) == want                  # one mixed batch
+    assert [eng.generate([p], max_tokens=n, prefill_chunk=1000)[0] for p in ps] == want  # each alone, whole
+    assert eng.generate(ps, max_tokens=n, prefill_chunk=1, max_batch_tokens=3) == want   # token by token
+    eng.pools.table.check()
+    assert eng.pools.table.live() == 0
+
+
+def test_bfloat16_greedy_follows_the_plain_bfloat16_restatement(workdir):
+    raw, page = tiny.CONFIGS["A"]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=11))
+    ps = tiny.prompts(raw["vocab_size"], [5, 17, 33], seed=5)
+    pm = plain.PlainModel(folder, rounding="bfloat16")
+    eng = engine(folder, "bfloat16", page)
+    got = eng.generate(ps, max_tokens=8, prefill_chunk=7)
+    for p, g in zip(ps, got):
+        ids = list(p)
+        for t in g:   # every chosen token must be (nearly) the plain argmax given the same history
+            logits = pm.logits(ids)[-1]
+            assert logits[t] >= logits.max() - 2e-2
+            ids.append(t)
+
+
+def test_long_decoding_and_the_first_tokens(workdir):
+    """200 decoded tokens across many page edges, teacher-forced against the plain logits, and
+    the very first positions of a sequence (one token, two tokens)."""
+    raw, page = tiny.CONFIGS["B"]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=4))
+    ids = tiny.prompts(raw["vocab_size"], [260], seed=9)[0]
+    ref = plain.PlainModel(folder).logits(ids).float()
+    eng = engine(folder, "float32", page, tokens=264)
+    first = eng.step([("s", ids[:1], [0])]).cpu()
+    assert tiny.max_abs(first[0], ref[0]) < 2e-5
+    second = eng.step([("s", ids[1:2], [0])]).cpu()
+    assert tiny.max_abs(second[0], ref[1]) < 2e-5
+    eng.step([("s", ids[2:60], [])])
+    for i in range(60, 260):
+        row = eng.step([("s", ids[i:i + 1], [0])]).cpu()
+        assert tiny.max_abs(row[0], ref[i]) < 2e-5, i
+    eng.release("s")
+    two = eng.step([("t", ids[:2], [0, 1])]).cpu()
+    assert tiny.max_abs(two, ref[:2]) < 2e-5
+
+
+def test_long_greedy_generation_with_a_window(workdir):
+    raw, page = tiny.CONFIGS["B"]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=12))
+    p = tiny.prompts(raw["vocab_size"], [30], seed=2)[0]
+    want = plain.PlainModel(folder).greedy(p, 60)
+    eng = engine(folder, "float32", page, tokens=96)
+    assert eng.generate([p], max_tokens=60, prefill_chunk=16)[0] == want
+
+
+def test_eos_stops_and_is_not_part_of_the_output(workdir):
+    raw, page = tiny.CONFIGS["A"]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=11))
+    p = tiny.prompts(raw["vocab_size"], [17], seed=5)[0]
+    pm = plain.PlainModel(folder)
+    want = pm.greedy(p, 8)
+    eng = engine(folder, "float32", page)
+    stop_at = want[3]
+    cut = want.index(stop_at)
+    r = eng.generate_detailed([p], max_tokens=8, eos_token_ids=[stop_at])
+    assert r.tokens[0] == want[:cut] and r.finish_reasons == ["stop"]
+    r = eng.generate_detailed([p], max_tokens=8, eos_token_ids=[stop_at], ignore_eos=True)
+    assert r.tokens[0] == want and r.finish_reasons == ["length"]
+
+
+def test_temperature_sampling_is_seeded_and_independent_of_the_batch(workdir):
+    raw, page = tiny.CONFIGS["B"]
+    folder = tiny.make_folder(workdir, raw, seed=11)
+    ps = tiny.prompts(raw["vocab_size"], [1, 9, 24, 40], seed=5)
+    eng = engine(folder, "float32", page)
+    a = eng.generate(ps, max_tokens=6, temperature=0.7, seed=3, prefill_chunk=5)
+    b = eng.generate(ps, max_tokens=6, temperature=0.7, seed=3, prefill_chunk=40)
+    c = eng.generate(ps, max_tokens=6, temperature=0.7, seed=4, prefill_chunk=5)
+    assert a == b and a != c
+    # request 0 alone draws the same numbers as request 0 in the batch
+    assert eng.generate(ps[:1], max_tokens=6, temperature=0.7, seed=3)[0] == a[0]
+    # every drawn token is the inverse-CDF choice of the plain softmax with the same uniform
+    from rust_mlx_b200.sampling import uniform
+    pm = plain.PlainModel(folder)
+    ids = list(ps[1])
+    for step, t in enumerate(a[1]):
+        p = torch.softmax(pm.logits(ids)[-1] / 0.7, -1)
+        cdf = torch.cumsum(p, 0)
+        u = uniform(3, 1, step)
+        lo = cdf[t - 1].item() if t > 0 else 0.0
+        assert lo - 1e-4 <= u <= cdf[t].item() + 1e-4
+        ids.append(t)
+    mixed = eng.generate(ps, max_tokens=6, temperature=[0.0, 0.7, 0.0, 0.7], seed=3)
+    greedy = eng.generate(ps, max_tokens=6)
+    assert mixed[0] == greedy[0] and mixed[2] == greedy[2] and mixed[1] == a[1]
+
+
+def test_pages_run_out_during_generation_requests_are_computed_again(workdir):
+    raw, page = tiny.CONFIGS["A"]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=11))
+    ps = tiny.prompts(raw["vocab_size"], [30, 28, 25], seed=8)
+    pm = plain.PlainModel(folder)
+    want = [pm.greedy(p, 24) for p in ps]
+    eng = engine(folder, "float32", page, tokens=112)        # 7 pages of 16: not enough for all three to finish together
+    r = eng.generate_detailed(ps, max_tokens=24, prefill_chunk=16)
+    assert r.tokens == want
+    assert r.preemptions > 0
+    assert eng.pools.table.live() == 0 and eng.pools.table.free_pages(0) == 7
+
+
+def test_python_entry_point_and_command_line(workdir):
+    import rust_mlx_b200
+    raw, page = tiny.CONFIGS["A"]
+    folder = tiny.make_folder(workdir, raw, seed=11)
+    p = tiny.prompts(raw["vocab_size"], [12], seed=5)[0]
+    want = plain.PlainModel(folder).greedy(p, 5)
+    assert rust_mlx_b200.generate(folder, [p], dtype="float32", max_tokens=5, page_size=page) == [want]
+    ids = os.path.join(str(workdir), "prompt.json")
+    json.dump(p, open(ids, "w"))
+    out = os.path.join(str(workdir), "report.json")
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "infer"), "--model", folder, "--prompt-ids", ids, "--max-tokens", "5",
+           "--runs", "2", "--warmup-tokens", "2", "--prefill-chunk", "4", "--ignore-eos", "--dtype", "float32",
+           "--page-size", str(page), "--output", out]
+    subprocess.run(cmd, check=True, timeout=300)
+    report = json.load(open(out))
+    assert [r["tokens"] for r in report["runs"]] == [want, want]
+    assert report["prompt_ids"] == p and report["runs"][0]["generated_tokens"] == 5
+    assert subprocess.run(cmd[:-2] + ["--runs", "0"], capture_output=True).returncode != 0
+
+
+def test_refusals(workdir):
+    from rust_mlx_b200.engine import Engine, EngineError
+    from rust_mlx_b200.engine.scheduler import RequestRejected
+    raw, page = tiny.CONFIGS["A"]
+    folder = tiny.make_folder(workdir, raw, seed=11)
+    with pytest.raises(EngineError):
+        Engine(folder, dtype="float16")
+    with pytest.raises(EngineError):
+        Engine(folder, page_size=24)
+    eng = engine(folder, "float32", page, tokens=32)
+    with pytest.raises(RequestRejected):
+        eng.generate([list(range(40))], max_tokens=4)
+    with pytest.raises(RequestRejected):
+        eng.generate([[]], max_tokens=4)
+    with pytest.raises(ValueError):
+        eng.generate([[1, 2, 999]], max_tokens=4)
+    assert eng.pools.table.live() == 0

@@ -1,0 +1,374 @@
+"""Each kernel alone against a plain PyTorch restatement of the same operation, at sizes
+other than the tiny models': head sizes in steps of 16, head counts and groups that are
+no power of two, odd widths and vocabularies."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def ops():
+    from rust_mlx_b200.kernels import ops as o
+    return o
+
+
+def rnd(shape, dtype, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n, width, vocab", [(1, 16, 3), (37, 200, 509), (300, 4096, 1000)])
+def test_embedding(dtype, n, width, vocab):
+    table = rnd((vocab, width), DT[dtype])
+    ids = torch.randint(0, vocab, (n,), dtype=torch.int32, device=DEV)
+    h = torch.empty(n, width, dtype=torch.float32, device=DEV)
+    ops().embedding(ids, table, h)
+    assert torch.equal(h, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n, width", [(1, 16), (5, 96), (33, 1000), (64, 4096), (3, 12288 + 8)])
+def test_add_rmsnorm(dtype, n, width):
+    dt = DT[dtype]
+    h = rnd((n, width), torch.float32, 2.0, 1)
+    delta = rnd((n, width), dt, 0.5, 2)
+    w = (1 + 0.1 * torch.randn(width)).to(DEV)
+    eps = 1e-5
+    x = torch.empty(n, width, dtype=dt, device=DEV)
+    h0 = h.clone()
+    ops().add_rmsnorm(h, delta, w, eps, x)
+    v = h0.double() + delta.double()
+    want = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * w.double()
+    assert torch.allclose(h, v.float(), atol=1e-6)
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    assert (x.double() - want).abs().max().item() < tol * max(1.0, want.abs().max().item())
+    # without a delta, and for chosen rows only (h untouched)
+    rows = torch.tensor([n - 1, 0], dtype=torch.int32, device=DEV)
+    x2 = torch.empty(2, width, dtype=dt, device=DEV)
+    h1 = h.clone()
+    ops().add_rmsnorm(h, None, w, eps, x2, rows=rows)
+    assert torch.equal(h, h1)
+    v = h1.double()[rows.long()]
+    want = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * w.double()
+    assert (x2.double() - want).abs().max().item() < tol * max(1.0, want.abs().max().item())
+
+
+def test_rmsnorm_rows_do_not_depend_on_the_batch():
+    h = rnd((40, 777), torch.float32, 1.0, 3)
+    w = torch.ones(777, device=DEV)
+    a = torch.empty(40, 777, device=DEV)
+    b = torch.empty(1, 777, device=DEV)
+    ops().add_rmsnorm(h.clone(), None, w, 1e-6, a)
+    ops().add_rmsnorm(h[17:18].clone(), None, w, 1e-6, b)
+    assert torch.equal(a[17], b[0])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n, inter", [(1, 16), (7, 160), (130, 1111)])
+def test_swiglu(dtype, n, inter):
+    dt = DT[dtype]
+    gu = rnd((n, 2 * inter), dt, 3.0)
+    out = torch.empty(n, inter, dtype=dt, device=DEV)
+    ops().swiglu(gu, out)
+    g, u = gu.double()[:, :inter], gu.double()[:, inter:]
+    want = g * torch.sigmoid(g) * u
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    assert ((out.double() - want).abs() <= tol * (1 + want.abs())).all()
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 16, 16), (3, 509, 96), (70, 130, 257), (128, 64, 4096), (200, 1000, 33)])
+def test_gemm_plain_float32(m, n, k):
+    a, w = rnd((m, k), torch.float32, 1.0, 1), rnd((n, k), torch.float32, 1.0, 2)
+    out = torch.empty(m, n, device=DEV)
+    ops().gemm_plain(a, w, out)
+    want = a.double() @ w.double().t()
+    assert (out.double() - want).abs().max().item() < 1e-5 * math.sqrt(k) * 4
+    # a row's result does not depend on the other rows
+    one = torch.empty(1, n, device=DEV)
+    ops().gemm_plain(a[m // 2:m // 2 + 1].contiguous(), w, one)
+    assert torch.equal(one[0], out[m // 2])
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 48, 64), (5, 509, 96), (130, 200, 1000)])
+def test_gemm_plain_bfloat16_and_float_logits(m, n, k):
+    a, w = rnd((m, k), torch.bfloat16, 1.0, 1), rnd((n, k), torch.bfloat16, 1.0, 2)
+    want = a.double() @ w.double().t()
+    out32 = torch.empty(m, n, device=DEV)
+    ops().gemm_plain(a, w, out32)
+    assert (out32.double() - want).abs().max().item() < 1e-4 * math.sqrt(k)
+    out16 = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_plain(a, w, out16)
+    assert ((out16.double() - want).abs() <= 1e-2 * (1 + want.abs())).all()
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 48, 64), (8, 6144, 4096), (64, 509 * 2, 96), (300, 200, 1000)])
+def test_linear_bfloat16(m, n, k):
+    a, w = rnd((m, k), torch.bfloat16, 1.0, 1), rnd((n, k), torch.bfloat16, 0.05, 2)
+    want = a.double() @ w.double().t()
+    for odt in (torch.bfloat16, torch.float32):
+        out = torch.empty(m, n, dtype=odt, device=DEV)
+        ops().linear(a, w, out)
+        tol = 1e-2 if odt == torch.bfloat16 else 2e-3
+        assert ((out.double() - want).abs() <= tol * (1 + want.abs())).all()
+
+
+def paged_setup(lengths, nkv, hd, page, dtype, seed=0, extra_pages=3):
+    """Random K, V for sequences of the given lengths scattered over shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum(-(-n // page) for n in lengths) + extra_pages
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    k_pool = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=dtype)
+    v_pool = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=dtype)
+    max_entries = max(-(-n // page) for n in lengths)
+    table = torch.full((len(lengths), max_entries), -1, dtype=torch.int32)
+    ks, vs = [], []
+    for s, n in enumerate(lengths):
+        k = torch.randn(n, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(n, nkv, hd, generator=g).to(dtype)
+        ks.append(k)
+        vs.append(v)
+        for i in range(-(-n // page)):
+            p = perm.pop()
+            table[s, i] = p
+            rows = k[i * page:(i + 1) * page]
+            k_pool[p, :, :rows.shape[0]] = rows.transpose(0, 1)
+            v_pool[p, :, :rows.shape[0]] = v[i * page:(i + 1) * page].transpose(0, 1)
+    return k_pool.to(DEV), v_pool.to(DEV), table.to(DEV), ks, vs
+
+
+def plain_attention(q, k, v, qpos, window, scale):
+    """q: [T, nq, hd] at positions qpos; k, v: [S, nkv, hd] for positions 0..S-1."""
+    T, nq, hd = q.shape
+    group = nq // k.shape[1]
+    kpos = torch.arange(k.shape[0])
+    allowed = kpos[None, :] <= qpos[:, None]
+    if window:
+        allowed &= kpos[None, :] > qpos[:, None] - window
+    out = torch.empty(T, nq, hd, dtype=torch.float64)
+    for h in range(nq):
+        s = (q[:, h].double() @ k[:, h // group].double().t()) * scale
+        s = s.masked_fill(~allowed, float("-inf"))
+        out[:, h] = torch.softmax(s, -1) @ v[:, h // group].double()
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq, nkv, hd, page, window", [
+    (4, 2, 16, 16, 0), (6, 2, 32, 8, 20), (5, 5, 48, 4, 0), (12, 4, 80, 32, 37), (32, 8, 128, 64, 0),
+    (3, 1, 256, 16, 0), (7, 1, 112, 2, 5)])
+def test_attention_plain_over_pages(dtype, nq, nkv, hd, page, window):
+    """Portions of several sequences and single decoded tokens in one batch; NaN in every
+    slot of the pool that must not be read."""
+    dt = DT[dtype]
+    lengths = [70, 1, 33, 130]
+    new = [9, 1, 33, 1]                    # the last `new` tokens of each sequence are this step's queries
+    k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, dt, seed=hd)
+    qs, pos, sidx = [], [], []
+    for s, (n, c) in enumerate(zip(lengths, new)):
+        qs.append(torch.randn(c, nq, hd).to(dt))
+        pos += list(range(n - c, n))
+        sidx += [s] * c
+    q = torch.cat(qs).to(DEV)
+    positions = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    seq_index = torch.tensor(sidx, dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = hd ** -0.5
+    ops().attention_plain(q.reshape(-1, nq * hd), k_pool, v_pool, positions, seq_index, table, page, out.reshape(-1, nq * hd),
+                          nq, nkv, hd, window, scale, status)
+    assert status.item() == 0
+    at = 0
+    tol = 2e-5 if dtype == "float32" else 1e-2
+    for s, (n, c) in enumerate(zip(lengths, new)):
+        want = plain_attention(qs[s], ks[s], vs[s], torch.arange(n - c, n), window, scale)
+        got = out[at:at + c].double().cpu()
+        assert not torch.isnan(got).any()
+        assert (got - want).abs().max().item() < tol
+        at += c
+
+
+def test_attention_finds_a_far_key_among_hundreds():
+    """One key far back matches the query strongly: the output must be that key's value.
+    With random keys a kernel that skips or misplaces it would still pass a tolerance."""
+    nq, nkv, hd, page = 4, 2, 32, 8
+    n = 700
+    k_pool, v_pool, table, ks, vs = paged_setup([n], nkv, hd, page, torch.float32, seed=5)
+    for target in (0, 7, 8, 255, 256, 511, n - 1):
+        q = torch.randn(1, nq, hd) * 0.1
+        k = ks[0].clone()
+        k[target] = 0
+        k[target, :, 3] = 40.0
+        q[0, :, 3] = 40.0
+        pg, slot = table[0, target // page].item(), target % page
+        k_pool[pg, :, slot] = k[target].to(DEV)
+        out = torch.empty(1, nq * hd, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops().attention_plain(q.reshape(1, -1).to(DEV), k_pool, v_pool, torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                              torch.zeros(1, dtype=torch.int32, device=DEV), table, page, out, nq, nkv, hd, 0, hd ** -0.5, status)
+        want = vs[0][target].repeat_interleave(nq // nkv, 0).reshape(-1)
+        assert (out[0].cpu() - want).abs().max().item() < 1e-4, target
+        k_pool[pg, :, slot] = ks[0][target].to(DEV)
+
+
+def test_attention_window_edge():
+    """The key just outside the window carries a huge score: it must not be seen; the key
+    just inside must."""
+    nq, nkv, hd, page, window, n = 2, 1, 16, 4, 10, 50
+    k_pool, v_pool, table, ks, vs = paged_setup([n], nkv, hd, page, torch.float32, seed=6)
+    q = torch.zeros(1, nq, hd)
+    q[0, :, 0] = 30.0
+    for target, seen in ((n - window - 1, False), (n - window, True)):
+        kp = k_pool.clone()
+        kp[table[0, target // page].item(), :, target % page, 0] = 30.0
+        out = torch.empty(1, nq * hd, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops().attention_plain(q.reshape(1, -1).to(DEV), kp, v_pool, torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                              torch.zeros(1, dtype=torch.int32, device=DEV), table, page, out, nq, nkv, hd, window, hd ** -0.5, status)
+        hit = (out[0, :hd].cpu() - vs[0][target, 0]).abs().max().item() < 1e-3
+        assert hit == seen
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq, nkv, hd, rot, page, norm", [
+    (4, 2, 16, 16, 16, True), (6, 2, 32, 32, 8, True), (5, 5, 48, 24, 4, False), (32, 8, 128, 128, 64, True),
+    (3, 1, 80, 0, 2, True)])
+def test_qk_norm_rotation_and_cache_write(dtype, nq, nkv, hd, rot, page, norm):
+    dt = DT[dtype]
+    lengths, new = [21, 6, 40], [5, 6, 1]
+    n_tok = sum(new)
+    n_pages = sum(-(-n // page) for n in lengths) + 2
+    table = torch.full((3, max(-(-n // page) for n in lengths)), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages).tolist()
+    for s, n in enumerate(lengths):
+        for i in range(-(-n // page)):
+            table[s, i] = perm.pop()
+    pos, sidx = [], []
+    for s, (n, c) in enumerate(zip(lengths, new)):
+        pos += list(range(n - c, n))
+        sidx += [s] * c
+    qkv = rnd((n_tok, (nq + 2 * nkv) * hd), dt, 1.0, 3)
+    qn = (1 + 0.2 * torch.randn(hd)).to(DEV) if norm else None
+    kn = (1 + 0.2 * torch.randn(hd)).to(DEV) if norm else None
+    theta, eps = 10000.0, 1e-5
+    inv_freq = (theta ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(rot, 1))).float().to(DEV) if rot else None
+    k_pool = torch.zeros(n_pages, nkv, page, hd, dtype=dt, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.empty(n_tok, nq * hd, dtype=dt, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    positions = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    ops().qk_rope_cache(qkv, qn, kn, eps, inv_freq, rot, positions, torch.tensor(sidx, dtype=torch.int32, device=DEV),
+                        table.to(DEV), page, k_pool, v_pool, q_out, nq, nkv, hd, True, status)
+    assert status.item() == 0
+    x = qkv.double().cpu()
+    q = x[:, :nq * hd].reshape(n_tok, nq, hd)
+    k = x[:, nq * hd:(nq + nkv) * hd].reshape(n_tok, nkv, hd)
+    v = x[:, (nq + nkv) * hd:].reshape(n_tok, nkv, hd)
+
+    def normed(t, w):
+        if w is None:
+            return t
+        return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w.double().cpu()
+
+    def rotate(t):
+        if rot == 0:
+            return t
+        half = rot // 2
+        ang = (positions.cpu().float()[:, None] * inv_freq.cpu()[None, :]).double()[:, None, :]
+        a, b = t[..., :half], t[..., half:rot]
+        out = t.clone()
+        out[..., :half] = a * ang.cos() - b * ang.sin()
+        out[..., half:rot] = b * ang.cos() + a * ang.sin()
+        return out
+
+    tol = 1e-5 if dtype == "float32" else 3e-2
+    want_q = rotate(normed(q, qn))
+    assert (q_out.double().cpu().reshape(n_tok, nq, hd) - want_q).abs().max().item() < tol
+    want_k = rotate(normed(k, kn))
+    for t in range(n_tok):
+        pg, slot = table[sidx[t], pos[t] // page].item(), pos[t] % page
+        assert (k_pool[pg, :, slot].double().cpu() - want_k[t]).abs().max().item() < tol
+        assert torch.equal(v_pool[pg, :, slot].cpu(), qkv[t, (nq + nkv) * hd:].reshape(nkv, hd).cpu())
+    # nothing else was written
+    written = {(table[sidx[t], pos[t] // page].item(), pos[t] % page) for t in range(n_tok)}
+    mask = torch.ones(n_pages, page, dtype=torch.bool)
+    for pg, slot in written:
+        mask[pg, slot] = False
+    assert k_pool.cpu().transpose(1, 2)[mask].abs().max().item() == 0
+
+
+def test_cache_write_without_a_page_is_reported_not_done():
+    nq, nkv, hd, page = 2, 1, 16, 4
+    qkv = rnd((1, 4 * hd), torch.float32)
+    table = torch.full((1, 2), -1, dtype=torch.int32, device=DEV)
+    k_pool = torch.zeros(2, nkv, page, hd, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().qk_rope_cache(qkv, None, None, 0.0, None, 0, torch.tensor([5], dtype=torch.int32, device=DEV),
+                        torch.zeros(1, dtype=torch.int32, device=DEV), table, page, k_pool, v_pool,
+                        torch.empty(1, nq * hd, device=DEV), nq, nkv, hd, True, status)
+    assert status.item() == 1 and k_pool.abs().max().item() == 0
+
+
+@pytest.mark.parametrize("vocab", [3, 509, 151936])
+def test_greedy_takes_the_lowest_id_on_ties(vocab):
+    logits = torch.randn(5, vocab, device=DEV)
+    top = logits.max().item() + 1
+    logits[1, vocab - 1] = top
+    logits[1, vocab // 2] = top
+    logits[2, 0] = top
+    logits[3, :] = 0.25
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops().sample(logits, None, None, out)
+    want = [int(torch.nonzero(r == r.max())[0, 0]) for r in logits.cpu()]
+    assert out.tolist() == want and want[1] == vocab // 2 and want[3] == 0
+
+
+@pytest.mark.parametrize("vocab", [7, 509, 50000])
+def test_temperature_sampling_inverts_the_cumulative_sum(vocab):
+    torch.manual_seed(0)
+    logits = (torch.randn(64, vocab) * 3).to(DEV)
+    temps = torch.full((64,), 0.8, device=DEV)
+    temps[::7] = 0.0
+    u = torch.rand(64, device=DEV)
+    out = torch.empty(64, dtype=torch.int32, device=DEV)
+    ops().sample(logits, temps, u, out)
+    p = torch.softmax(logits.double().cpu() / 0.8, -1)
+    cdf = torch.cumsum(p, -1)
+    for r, t in enumerate(out.tolist()):
+        if r % 7 == 0:
+            assert t == int(logits[r].argmax())
+            continue
+        lo = cdf[r, t - 1].item() if t > 0 else 0.0
+        assert lo - 1e-5 <= u[r].item() <= cdf[r, t].item() + 1e-5
+    # rows do not depend on the batch
+    one = torch.empty(1, dtype=torch.int32, device=DEV)
+    ops().sample(logits[5:6], temps[5:6], u[5:6], one)
+    assert one.item() == out[5].item()
+    # frequencies follow the distribution
+    small = torch.tensor([[0.0, 1.0, 2.0, -1.0]], device=DEV).repeat(4000, 1)
+    draws = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops().sample(small, torch.ones(4000, device=DEV), torch.rand(4000, device=DEV), draws)
+    freq = torch.bincount(draws.long().cpu(), minlength=4).double() / 4000
+    assert (freq - torch.softmax(small[0].double().cpu(), -1)).abs().max().item() < 0.03
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from rust_mlx_b200.kernels.library import KernelError
+    o = ops()
+    with pytest.raises(KernelError, match="CUDA device"):
+        o.swiglu(torch.zeros(2, 8), torch.zeros(2, 4))
+    with pytest.raises(KernelError, match="dtype"):
+        o.swiglu(torch.zeros(2, 8, dtype=torch.float16, device=DEV), torch.zeros(2, 4, dtype=torch.float16, device=DEV))
+    q = torch.zeros(1, 66 * 16, device=DEV)
+    pool = torch.zeros(1, 1, 4, 16, device=DEV)
+    i32 = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="32 query heads"):
+        o.attention_plain(q, pool, pool, i32, i32, i32.view(1, 1), 4, q.clone(), 66, 1, 16, 0, 1.0, i32)
+    with pytest.raises(KernelError, match="rotary_dim"):
+        o.qk_rope_cache(torch.zeros(1, 48, device=DEV), None, None, 0.0, torch.zeros(8, device=DEV), 18, i32, i32,
+                        i32.view(1, 1), 4, pool, pool, torch.zeros(1, 16, device=DEV), 1, 1, 16, True, i32)

@@ -1,0 +1,138 @@
+"""Replay of the same requests cut in different ways, against the plain implementation.
+
+Both tiny configurations, float32 and bfloat16.  The model folders are sharpened
+(tiny.sharpen) so that a wrong, stale or missing key changes the logits by far more
+than the tolerance.  Tolerances, fixed before the first run: float32 2e-5 (logits are
+of order 1; sums of at most a few hundred float32 products), bfloat16 2e-2 against the
+plain implementation restated with bfloat16 roundings (a flipped last bit of a
+bfloat16 activation is 4e-3 of its value).  In float32 the four ways must agree bit
+for bit: every kernel of that path adds in an order that depends on the position only.
+"""
+import os
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import replay
+import tiny
+
+pytestmark = pytest.mark.gpu
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+LENGTHS = [5, 17, 33, 150, 41, 9, 64, 65]
+
+
+@pytest.fixture(scope="module")
+def workdir(tmp_path_factory):
+    return tmp_path_factory.mktemp("replay")
+
+
+def setup(workdir, name, dtype):
+    raw, page = tiny.CONFIGS[name]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=3, store="float32"))
+    reqs = {f"r{i}": p for i, p in enumerate(tiny.prompts(raw["vocab_size"], LENGTHS, seed=7))}
+    pm = plain.PlainModel(folder, rounding=None if dtype == "float32" else "bfloat16")
+    ref = {rid: pm.logits(t).float() for rid, t in reqs.items()}
+    return raw, page, folder, reqs, ref
+
+
+_cache = {}
+
+
+def cached_setup(workdir, name, dtype):
+    key = (name, dtype)
+    if key not in _cache:
+        _cache[key] = setup(workdir, name, dtype)
+    return _cache[key]
+
+
+def engine_for(folder, dtype, page, tokens):
+    from rust_mlx_b200.engine import Engine
+    return Engine(folder, dtype=dtype, max_tokens=tokens, page_size=page, max_requests=4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("way", ["whole", "tail_one_by_one", "portions", "mixed"])
+def test_every_way_of_cutting_matches_the_plain_implementation(workdir, name, dtype, way):
+    raw, page, folder, reqs, ref = cached_setup(workdir, name, dtype)
+    steps = getattr(replay, way)(reqs)
+    need = replay.tokens_needed(steps, page)
+    eng = engine_for(folder, dtype, page, need)   # exactly what the trace needs: pages are used again
+    got = replay.run_engine(eng, steps)
+    eng.pools.table.check()
+    assert eng.pools.table.live() == 0 and eng.pools.table.free_pages(0) == eng.pools.num_pages
+    for rid in reqs:
+        assert got[rid].shape == ref[rid].shape
+        assert tiny.max_abs(got[rid], ref[rid]) < TOL[dtype], (rid, way)
+    _cache[(name, dtype, way)] = got
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_float32_ways_agree_bit_for_bit(workdir, name):
+    raw, page, folder, reqs, ref = cached_setup(workdir, name, "float32")
+    results = []
+    for way in ("whole", "tail_one_by_one", "portions", "mixed"):
+        got = _cache.get((name, "float32", way))
+        if got is None:
+            steps = getattr(replay, way)(reqs)
+            got = replay.run_engine(engine_for(folder, "float32", page, replay.tokens_needed(steps, page)), steps)
+        results.append(got)
+    for other in results[1:]:
+        for rid in reqs:
+            assert torch.equal(other[rid], results[0][rid])
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_replay_uses_pages_again(workdir, name):
+    raw, page, folder, reqs, ref = cached_setup(workdir, name, "float32")
+    steps = replay.mixed(reqs)
+    eng = engine_for(folder, "float32", page, replay.tokens_needed(steps, page))
+    seen, again = {}, 0
+    for s in steps:
+        eng.step([(e["id"], e["tokens"], e["want"]) for e in s["entries"]])
+        for e in s["entries"]:
+            rid = eng._req_ids[e["id"]]
+            for p in eng.pools.table.table(rid, 0):
+                if p >= 0 and seen.setdefault(p, e["id"]) != e["id"]:
+                    again += 1
+                    seen[p] = e["id"]
+        for rid in s["end"]:
+            eng.release(rid)
+    assert again > 0, "the trace was meant to hand pages of finished requests to later ones"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(workdir, dtype):
+    """bin/trace_run as a child process: mixed trace, default page size, exactly --max-tokens of cache."""
+    raw, page, folder, reqs, ref = cached_setup(workdir, "B", dtype)
+    steps = replay.mixed(reqs)
+    out = os.path.join(str(workdir), f"trace_{dtype}")
+    got = replay.run_trace_tool(folder, dtype, steps, out, replay.tokens_needed(steps, 64), raw["vocab_size"])
+    for rid in reqs:
+        assert tiny.max_abs(got[rid], ref[rid]) < TOL[dtype], rid
+    # a step in which nothing is wanted writes no file; a request may end in a step without entries
+    steps2 = [{"step": 0, "entries": [{"id": "x", "tokens": reqs["r1"][:9], "want": []}], "end": []},
+              {"step": 1, "entries": [{"id": "x", "tokens": reqs["r1"][9:], "want": [len(reqs["r1"]) - 10]}], "end": []},
+              {"step": 2, "entries": [], "end": ["x"]}]
+    out2 = os.path.join(str(workdir), f"trace2_{dtype}")
+    got2 = replay.run_trace_tool(folder, dtype, steps2, out2, 64, raw["vocab_size"])
+    assert not os.path.exists(os.path.join(out2, "0.f32"))
+    assert tiny.max_abs(got2["x"][0], ref["r1"][-1]) < TOL[dtype]
+
+
+def test_out_of_pages_is_an_error_and_changes_nothing(workdir):
+    from rust_mlx_b200.cache import OutOfPages
+    raw, page, folder, reqs, ref = cached_setup(workdir, "A", "float32")
+    eng = engine_for(folder, "float32", page, 32)           # two pages of 16
+    eng.step([("a", reqs["r1"][:10], [])])
+    with pytest.raises(OutOfPages):
+        eng.step([("a", reqs["r1"][10:17], []), ("b", reqs["r2"][:20], [])])
+    assert eng.length("a") == 10 and eng.length("b") == 0
+    eng.pools.table.check()
+    assert eng.pools.table.free_pages(0) == 1
+    got = eng.step([("a", reqs["r1"][10:], [6])])
+    assert tiny.max_abs(got[0].cpu(), ref["r1"][-1]) < TOL["float32"]
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.step([("a", [3], []), ("c", [raw["vocab_size"]], [0])])
+    assert eng.length("c") == 0 and eng.length("a") == 17

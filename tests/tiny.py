@@ -43,3 +43,24 @@ def prompts(vocab: int, lengths, seed: int = 1) -> list:
 
 def max_abs(a: torch.Tensor, b: torch.Tensor) -> float:
     return (a.double() - b.double()).abs().max().item()
+
+
+def sharpen(folder: str, factor: float = 2.0) -> str:
+    """A copy of ``folder`` whose q_norm and k_norm weights are multiplied by ``factor``.
+
+    With N(0, 0.02) weights every score is near zero and attention is an average over all
+    keys: a key that is missing, stale or read from the wrong page changes the result by
+    about 1/length and hides in the tolerance.  Scaling both norms by 2 scales scores by
+    4, so a few keys carry most of the weight and any wrong key shows."""
+    from safetensors.torch import load_file, save_file
+    import shutil
+    out = folder + f"_sharp{factor}"
+    if not os.path.exists(os.path.join(out, "model.safetensors")):
+        os.makedirs(out, exist_ok=True)
+        shutil.copy(os.path.join(folder, "config.json"), os.path.join(out, "config.json"))
+        t = load_file(os.path.join(folder, "model.safetensors"))
+        for k in t:
+            if k.endswith("q_norm.weight") or k.endswith("k_norm.weight"):
+                t[k] = t[k] * factor
+        save_file(t, os.path.join(out, "model.safetensors"))
+    return out
