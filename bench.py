@@ -1,0 +1,283 @@
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+
+The default run has the layer sizes of the Qwen3-8B shape (BASELINE.json configs[2]) with
+random weights in bfloat16: decode at batch 8 from a context of 2,048 tokens per request.
+It prints ONE JSON line.  ``value`` is decoded tokens per second, timed on the device with
+CUDA events over exactly K steps (each step: upload of the step's ids and tables from
+pinned memory, the model, greedy sampling).  ``e2e`` is the same through the Python entry
+point (``Engine.generate``): host token ids in, host token ids out, one host
+synchronisation per step.  ``prefill`` is one 2,048-token prompt in one step; ``roofline``
+is the decode step's bytes (every weight once plus the live requests' cache) over its time.
+Weights (15 GB) are far larger than L2, so no flush is needed between steps.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                max_position_embeddings=4096)
+CONTEXT = 2048          # tokens each request holds when decoding starts
+MAX_CONTEXT = 4096
+PREFILL_TOKENS = 2048
+PAGE = 64
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(path):
+        try:
+            raw = json.load(open(path))
+            out["hbm_gbs"] = float(raw.get("hbm_gbs", out["hbm_gbs"]))
+            out["bf16_tflops"] = float(raw.get("bf16_tflops_sustained", raw.get("bf16_tflops", out["bf16_tflops"])))
+            out["source"] = "measured"
+        except Exception:
+            pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def model_bytes(cfg, layers):
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"] * h
+    o = cfg["num_attention_heads"] * cfg["head_dim"] * h
+    per_layer = qkv + o + 3 * h * i
+    params = layers * per_layer + v * h           # the head once; embedding rows are a few KB
+    return params * 2, per_layer, v * h
+
+
+def kv_bytes_per_token(cfg, layers):
+    return layers * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def prefill_flops(cfg, layers, tokens):
+    _, per_layer, head = model_bytes(cfg, layers)
+    gemm = 2.0 * tokens * layers * per_layer + 2.0 * head          # logits for the last row only
+    attn = 2.0 * tokens * tokens * cfg["head_dim"] * cfg["num_attention_heads"] * layers   # causal: half of 4 T^2 d
+    return gemm + attn
+
+
+class DecodeRun:
+    """B live requests holding CONTEXT tokens each (synthetic cache), stepped one token at a time."""
+
+    def __init__(self, engine, batch, context):
+        import torch
+        from rust_mlx_b200.sampling import Sampler
+        self.e, self.batch, self.context, self.torch = engine, batch, context, torch
+        self.rids = list(range(10_000, 10_000 + batch))
+        self.len = context
+        for r in self.rids:
+            engine.pools.open(r)
+            engine.pools.table.reserve(r, context)
+            engine.pools.table.commit(r, context)
+        self.sampler = Sampler(engine.device)
+        g = torch.Generator().manual_seed(batch)
+        self.ids = torch.randint(0, engine.vocab_size, (4096, batch), generator=g).tolist()
+        self.out = torch.empty(batch, dtype=torch.int32, device=engine.device)
+        self.n = 0
+
+    def step(self):
+        from rust_mlx_b200.engine.batch import SequenceInput, build_batch
+        e = self.e
+        for r in self.rids:
+            e.pools.table.reserve(r, self.len + 1)
+        toks = self.ids[self.n % len(self.ids)]
+        seqs = [SequenceInput(r, self.len, [toks[i]], [0]) for i, r in enumerate(self.rids)]
+        batch = build_batch(seqs, e.pools, e.device, e._status, e.vocab_size)
+        logits = e.forward(batch)
+        self.sampler.sample(logits, [0.0] * self.batch, 0, self.rids, [0] * self.batch, out=self.out)
+        self.len += 1
+        self.n += 1
+        for r in self.rids:
+            e.pools.table.commit(r, self.len)
+
+    def close(self):
+        for r in self.rids:
+            self.e.pools.table.close(r)
+
+
+def time_decode(engine, batch, steps, warmup, clocks=None):
+    import torch
+    from rust_mlx_b200.kernels import ops
+    run = DecodeRun(engine, batch, CONTEXT)
+    try:
+        for _ in range(warmup):
+            run.step()
+        torch.cuda.synchronize()
+        if clocks:
+            clocks.start()
+        launches0 = ops.launch_count
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            run.step()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / steps
+        engine.check_status()
+        return ms, ops.launch_count - launches0, (clocks.stop() if clocks else None)
+    finally:
+        run.close()
+
+
+def time_prefill(engine, tokens, reps=3):
+    import torch
+    from rust_mlx_b200.engine.batch import SequenceInput, build_batch
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, engine.vocab_size, (tokens,), generator=g).tolist()
+    best = None
+    for rep in range(reps + 1):
+        rid = 20_000 + rep
+        engine.pools.open(rid)
+        engine.pools.table.reserve(rid, tokens)
+        batch = build_batch([SequenceInput(rid, 0, ids, [tokens - 1])], engine.pools, engine.device, engine._status,
+                            engine.vocab_size)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.forward(batch)
+        stop.record()
+        torch.cuda.synchronize()
+        engine.pools.table.close(rid)
+        ms = start.elapsed_time(stop)
+        if rep > 0:                      # the first repetition warms up
+            best = ms if best is None else min(best, ms)
+    engine.check_status()
+    return best
+
+
+def time_e2e(engine, batch, new_tokens):
+    """Through the Python entry point: prompts of CONTEXT host token ids, ``new_tokens`` generated each."""
+    import torch
+    g = torch.Generator().manual_seed(7)
+    prompts = torch.randint(0, engine.vocab_size, (batch, CONTEXT), generator=g).tolist()
+    engine.generate(prompts[:1], max_tokens=2, ignore_eos=True, prefill_chunk=512)      # warm-up
+    r = engine.generate_detailed(prompts, max_tokens=new_tokens, ignore_eos=True, prefill_chunk=2048,
+                                 max_batch_tokens=2048 + batch)
+    decoded = r.generated_tokens - batch
+    # bytes per decode step: ids, positions, sequence indices, starts, lengths, slots, rows, block tables up; tokens + status down
+    entries = -(-(CONTEXT + new_tokens) // PAGE)
+    h2d = 4 * (3 * batch + (batch + 1) + 3 * batch + batch * entries)
+    d2h = 4 * (batch + 1)
+    return decoded / r.decode_seconds, h2d, d2h
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, prefill and e2e")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust/MLX/Metal program for Apple GPUs: no Rust toolchain, no MLX and no "
+                          "setup.py/pyproject.toml here (pip: 'not installable'), so it cannot be built or run on this box"}))
+        return 0
+    if a.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    a.warmup = max(a.warmup, 3)
+
+    import torch
+    from rust_mlx_b200.config import Qwen3Config
+    from rust_mlx_b200.engine import Engine
+
+    raw = dict(QWEN3_8B, num_hidden_layers=a.layers)
+    cfg = Qwen3Config.from_dict(raw)
+    biggest = 1 if a.no_points else max(64, a.batch)
+    cache_tokens = max(biggest, a.batch) * (CONTEXT + 2 * PAGE + a.steps + a.warmup + 64)
+    engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE,
+                    max_requests=max(biggest, a.batch) + 2)
+    for grp in engine.pools.paged_groups:      # synthetic cache contents for the requests that start at CONTEXT
+        grp.k_pool.normal_(0, 1)
+        grp.v_pool.normal_(0, 1)
+    pk = peaks()
+
+    clocks = ClockSampler()
+    ms, launches, clock_info = time_decode(engine, a.batch, a.steps, a.warmup, clocks)
+    value = a.batch * 1000.0 / ms
+    weight_bytes, _, _ = model_bytes(raw, a.layers)
+    step_bytes = weight_bytes + a.batch * (CONTEXT + a.warmup + a.steps / 2) * kv_bytes_per_token(raw, a.layers)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 8, context 2048 (Qwen3-8B shape, bf16)", "value": round(value, 2), "unit": "tok/s",
+        "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": "Qwen3-8B shape, random weights", "layers": a.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+                   "hidden": 4096, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288,
+                   "vocab": 151936, "global_batch": a.batch, "seq_len": CONTEXT, "max_context": MAX_CONTEXT,
+                   "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (15 GB of weights per step), no flush",
+                   "peaks": pk["source"]},
+        "gpu_launches": launches, "clocks": clock_info,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"]},
+    }
+    if not a.no_points:
+        points = {}
+        for b in (1, 64):
+            pms, _, _ = time_decode(engine, b, max(8, a.steps // 2), a.warmup)
+            points[f"decode_b{b}"] = round(b * 1000.0 / pms, 2)
+        line["points"] = points
+        pf_ms = time_prefill(engine, PREFILL_TOKENS)
+        flops = prefill_flops(raw, a.layers, PREFILL_TOKENS)
+        line["prefill"] = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
+                           "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"]}
+        e2e, h2d, d2h = time_e2e(engine, a.batch, max(16, a.steps // 2))
+        line["e2e"] = {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -45,7 +45,7 @@ def _digest(paths, flags) -> str:
     h.update(" ".join(flags).encode())
     for p in sorted(paths):
         with open(p, "rb") as fh:
-            h.update(p.encode())
+            h.update(os.path.basename(p).encode())
             h.update(fh.read())
     return h.hexdigest()
 
