@@ -1,0 +1,393 @@
+// Flash attention over the paged cache for bfloat16, on the tensor cores (mma.sync m16n8k16),
+// serving prompt portions and decoded tokens in one launch.
+//
+// A block takes one kv head and one tile of query rows of one sequence.  A row is a
+// (token, query head of the group) pair, so the heads that share a kv head share every key
+// and value the block loads: TQ = 64 / group tokens by `group` heads per tile.  Keys are
+// visited in tiles of 64 aligned to absolute positions, brought to shared memory with
+// cp.async (two stages), through the request's block table.  Scores, the running maximum,
+// the exponentials, their sum and the output accumulate in float.  A row at position p
+// sees keys lo .. p (lo = p - window + 1 or 0).  With n_splits > 1 (long contexts, few
+// rows: decoding) grid.z blocks share a tile's keys and write unnormalised partial
+// results, which attention_merge_kernel combines.
+#include "common.cuh"
+
+namespace {
+constexpr int BM = 64, BN = 64, NWARPS = 4, THREADS = NWARPS * 32;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct FlashParams {
+    const __nv_bfloat16* q;        // [tokens, nq, HD]
+    const __nv_bfloat16* k_pool;   // [pages, nkv, page_size, HD]
+    const __nv_bfloat16* v_pool;
+    const int* q_start;            // [seqs + 1] first flat token of every sequence
+    const int* positions;          // [tokens]
+    const int* block_table;        // [seqs, table_stride]
+    __nv_bfloat16* out;            // [tokens, nq, HD]
+    float* part_o;                 // [splits, tokens * nq, HD]   (splits > 1)
+    float* part_ml;                // [splits, tokens * nq, 2]
+    int* status;
+    int n_seqs, n_tokens, nq, nkv, group, tq, table_stride, page_size, window, n_splits;
+    float scale_log2;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashParams p) {
+    constexpr int STRIDE = HD + 8;          // 16 bytes of padding: ldmatrix rows fall into different banks
+    constexpr int CHUNKS = HD / 8;          // 16-byte chunks per row
+    constexpr int KSTEPS = HD / 16;
+    constexpr int DTILES = HD / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BM][STRIDE]
+    __nv_bfloat16* Ks = Qs + BM * STRIDE;                             // [2][BN][STRIDE]
+    __nv_bfloat16* Vs = Ks + 2 * BN * STRIDE;                         // [2][BN][STRIDE]
+    __shared__ int s_tile[3];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.y, split = blockIdx.z;
+
+    // which sequence and which of its tiles this block has: tiles are counted sequence by
+    // sequence; the threads scan the sequences' tile counts together
+    {
+        __shared__ int s_warp_total[NWARPS];
+        if (tid == 0) s_tile[0] = -1;
+        int base = 0;
+        for (int chunk = 0; chunk < p.n_seqs; chunk += THREADS) {
+            const int sq = chunk + tid;
+            int a = 0, n = 0, tiles = 0;
+            if (sq < p.n_seqs) {
+                a = p.q_start[sq];
+                n = p.q_start[sq + 1] - a;
+                tiles = (n + p.tq - 1) / p.tq;
+            }
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            __syncthreads();
+            if (lane == 31) s_warp_total[warp] = incl;
+            __syncthreads();
+            int before = base, total = 0;
+#pragma unroll
+            for (int w = 0; w < NWARPS; ++w) {
+                if (w < warp) before += s_warp_total[w];
+                total += s_warp_total[w];
+            }
+            const int first_tile = before + incl - tiles;
+            const int mine = (int)blockIdx.x - first_tile;
+            if (tiles > 0 && mine >= 0 && mine < tiles) {
+                s_tile[0] = sq;
+                s_tile[1] = a + mine * p.tq;
+                s_tile[2] = min(p.tq, n - mine * p.tq);
+            }
+            base += total;
+        }
+    }
+    __syncthreads();
+    const int seq = s_tile[0], tok0 = s_tile[1], n_tok = s_tile[2];
+    if (seq < 0) return;  // the grid is an upper bound
+    const int pos0 = p.positions[tok0];
+    const int rows_valid = n_tok * p.group;
+    const int* table = p.block_table + (size_t)seq * p.table_stride;
+
+    // keys this tile needs: from the first row's lower bound to the last row's position
+    const int lo_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int pos_last = pos0 + n_tok - 1;
+    const int kt_lo = lo_first / BN, kt_hi = pos_last / BN;
+    const int n_kt = kt_hi - kt_lo + 1;
+    const int per_split = (n_kt + p.n_splits - 1) / p.n_splits;
+    const int kt_begin = kt_lo + split * per_split;
+    const int kt_end = min(kt_hi + 1, kt_begin + per_split);
+
+    // ---- Q tile to shared memory (rows beyond the tile are zeros)
+    for (int idx = tid; idx < BM * CHUNKS; idx += THREADS) {
+        const int r = idx / CHUNKS, c = idx - r * CHUNKS;
+        const bool valid = r < rows_valid;
+        const int tok = valid ? r / p.group : 0, g = valid ? r - tok * p.group : 0;
+        const __nv_bfloat16* src = p.q + ((size_t)(tok0 + tok) * p.nq + kvh * p.group + g) * HD + c * 8;
+        cp_async16(Qs + r * STRIDE + c * 8, src, valid);
+    }
+    cp_async_commit();
+
+    auto load_kv = [&](int kt, int stage) {
+        __nv_bfloat16* kd = Ks + stage * BN * STRIDE;
+        __nv_bfloat16* vd = Vs + stage * BN * STRIDE;
+        for (int idx = tid; idx < BN * CHUNKS; idx += THREADS) {
+            const int j = idx / CHUNKS, c = idx - j * CHUNKS;
+            const int kp = kt * BN + j;
+            bool valid = kp >= lo_first && kp <= pos_last;
+            size_t off = 0;
+            if (valid) {
+                const int page = table[kp / p.page_size];
+                if (page < 0) {
+                    valid = false;
+                    if (c == 0) atomicExch(p.status, 2);
+                } else {
+                    off = (((size_t)page * p.nkv + kvh) * p.page_size + kp % p.page_size) * HD + c * 8;
+                }
+            }
+            cp_async16(kd + j * STRIDE + c * 8, p.k_pool + off, valid);
+            cp_async16(vd + j * STRIDE + c * 8, p.v_pool + off, valid);
+        }
+    };
+
+    if (kt_begin < kt_end) load_kv(kt_begin, 0);
+    cp_async_commit();
+
+    // ---- this warp's rows
+    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;  // the two rows this thread holds in C fragments
+    const bool warp_active = warp * 16 < rows_valid;
+    int row_pos[2], row_lo[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = i == 0 ? r_lo : r_hi;
+        row_ok[i] = r < rows_valid;
+        row_pos[i] = pos0 + (row_ok[i] ? r / p.group : 0);
+        row_lo[i] = p.window > 0 ? max(0, row_pos[i] - p.window + 1) : 0;
+    }
+
+    cp_async_wait<1>();  // Q has landed
+    __syncthreads();
+    uint32_t qf[KSTEPS][4];
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk)
+        ldmatrix_x4(qf[kk], Qs + (warp * 16 + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int kt = kt_begin; kt < kt_end; ++kt) {
+        const int stage = (kt - kt_begin) & 1;
+        if (kt + 1 < kt_end) load_kv(kt + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (warp_active) {
+            const __nv_bfloat16* kbase = Ks + stage * BN * STRIDE;
+            const __nv_bfloat16* vbase = Vs + stage * BN * STRIDE;
+            float s[BN / 8][4];
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+                for (int jp = 0; jp < BN / 16; ++jp) {
+                    uint32_t kf[4];
+                    const int key = jp * 16 + (lane & 7) + ((lane >> 4) << 3);
+                    const int dcol = kk * 16 + ((lane >> 3) & 1) * 8;
+                    ldmatrix_x4(kf, kbase + key * STRIDE + dcol);
+                    mma_bf16(s[2 * jp], qf[kk], kf[0], kf[1]);
+                    mma_bf16(s[2 * jp + 1], qf[kk], kf[2], kf[3]);
+                }
+            }
+            // mask, scale, online softmax (in base 2)
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int kp = kt * BN + j * 8 + (lane & 3) * 2 + (e & 1);
+                    const bool ok = row_ok[i] && kp <= row_pos[i] && kp >= row_lo[i];
+                    s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+                    mx[i] = fmaxf(mx[i], s[j][e]);
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                const float m_new = fmaxf(m[i], mx[i]);
+                corr[i] = m_new == -INFINITY ? 1.f : exp2f(m[i] - m_new);
+                m[i] = m_new;
+                l[i] *= corr[i];
+            }
+            const float mref[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const float pv = exp2f(s[j][e] - mref[i]);  // -inf -> 0
+                    s[j][e] = pv;
+                    l[i] += pv;
+                }
+            }
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d) {
+                o[d][0] *= corr[0]; o[d][1] *= corr[0];
+                o[d][2] *= corr[1]; o[d][3] *= corr[1];
+            }
+            // O += P V
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk) {
+                uint32_t pf[4];
+                pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pf[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pf[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < DTILES / 2; ++dp) {
+                    uint32_t vf[4];
+                    const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    const int dcol = dp * 16 + (lane >> 4) * 8;
+                    ldmatrix_x4_trans(vf, vbase + key * STRIDE + dcol);
+                    mma_bf16(o[2 * dp], pf, vf[0], vf[1]);
+                    mma_bf16(o[2 * dp + 1], pf, vf[2], vf[3]);
+                }
+            }
+        }
+        __syncthreads();  // the stage is free for the load after next
+    }
+    cp_async_wait<0>();
+
+    if (!warp_active) return;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = i == 0 ? r_lo : r_hi;
+        if (!row_ok[i]) continue;
+        const int tok = r / p.group, g = r - tok * p.group;
+        const size_t row = (size_t)(tok0 + tok) * p.nq + kvh * p.group + g;
+        if (p.n_splits == 1) {
+            const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+            __nv_bfloat16* dst = p.out + row * HD;
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d) {
+                const int col = d * 8 + (lane & 3) * 2;
+                *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(o[d][2 * i] * inv, o[d][2 * i + 1] * inv);
+            }
+        } else {
+            const size_t prow = (size_t)split * p.n_tokens * p.nq + row;
+            float* dst = p.part_o + prow * HD;
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d) {
+                const int col = d * 8 + (lane & 3) * 2;
+                *reinterpret_cast<float2*>(dst + col) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+            }
+            if ((lane & 3) == 0) {
+                p.part_ml[prow * 2] = m[i];
+                p.part_ml[prow * 2 + 1] = l[i];
+            }
+        }
+    }
+}
+
+// out[row] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the splits, in split order.
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       __nv_bfloat16* __restrict__ out, int rows, int hd, int n_splits) {
+    const int row = blockIdx.x;
+    float M = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((size_t)z * rows + row) * 2]);
+    float L = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+        const float mz = part_ml[((size_t)z * rows + row) * 2];
+        if (mz != -INFINITY) L += exp2f(mz - M) * part_ml[((size_t)z * rows + row) * 2 + 1];
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.f;
+        for (int z = 0; z < n_splits; ++z) {
+            const float mz = part_ml[((size_t)z * rows + row) * 2];
+            if (mz != -INFINITY) acc += exp2f(mz - M) * part_o[((size_t)z * rows + row) * hd + d];
+        }
+        out[(size_t)row * hd + d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int HD>
+int launch_flash(const FlashParams& p, int n_tiles, cudaStream_t s) {
+    constexpr size_t smem = (size_t)(BM + 4 * BN) * (HD + 8) * sizeof(__nv_bfloat16);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_flash_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RMX_FAIL("attention_flash: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
+    }
+    dim3 grid(n_tiles, p.nkv, p.n_splits);
+    attention_flash_kernel<HD><<<grid, THREADS, smem, s>>>(p);
+    RMX_CHECK_LAUNCH("attention_flash");
+    return 0;
+}
+}  // namespace
+
+// Which head sizes the tensor-core kernel is built for; others take attention_plain.
+RMX_API int rmx_attention_flash_supports(int hd, int group) {
+    const bool hd_ok = hd == 16 || hd == 32 || hd == 64 || hd == 96 || hd == 128;
+    return hd_ok && group >= 1 && group <= 16 ? 1 : 0;
+}
+
+// n_tiles: the number of query tiles of the batch, sum over sequences of ceil(tokens / (64 / group)).
+// part_o / part_ml are needed when n_splits > 1: [n_splits, tokens * nq, hd] and [n_splits, tokens * nq, 2] floats.
+RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v_pool, const int* q_start,
+                                const int* positions, const int* block_table, int table_stride, int page_size,
+                                void* out, float* part_o, float* part_ml, int n_seqs, int n_tokens, int n_tiles,
+                                int nq, int nkv, int hd, int window, float scale, int n_splits, int* status,
+                                void* stream) {
+    if (n_tokens == 0) return 0;
+    RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_flash: %d query heads over %d kv heads", nq, nkv);
+    const int group = nq / nkv;
+    RMX_REQUIRE(rmx_attention_flash_supports(hd, group), "attention_flash: head_dim %d with group %d is not built", hd, group);
+    RMX_REQUIRE(page_size > 0 && table_stride > 0 && window >= 0 && n_tiles > 0 && n_seqs > 0, "attention_flash: bad geometry");
+    RMX_REQUIRE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attention_flash: bad grid");
+    RMX_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_flash: splits need partial buffers");
+    FlashParams p;
+    p.q = (const __nv_bfloat16*)q; p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
+    p.q_start = q_start; p.positions = positions; p.block_table = block_table; p.out = (__nv_bfloat16*)out;
+    p.part_o = part_o; p.part_ml = part_ml; p.status = status;
+    p.n_seqs = n_seqs; p.n_tokens = n_tokens; p.nq = nq; p.nkv = nkv; p.group = group; p.tq = BM / group;
+    p.table_stride = table_stride; p.page_size = page_size; p.window = window; p.n_splits = n_splits;
+    p.scale_log2 = scale * LOG2E;
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc;
+    switch (hd) {
+        case 16: rc = launch_flash<16>(p, n_tiles, s); break;
+        case 32: rc = launch_flash<32>(p, n_tiles, s); break;
+        case 64: rc = launch_flash<64>(p, n_tiles, s); break;
+        case 96: rc = launch_flash<96>(p, n_tiles, s); break;
+        default: rc = launch_flash<128>(p, n_tiles, s); break;
+    }
+    if (rc != 0) return rc;
+    if (n_splits > 1) {
+        attention_merge_kernel<<<n_tokens * nq, hd >= 128 ? 128 : 64, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, n_tokens * nq, hd, n_splits);
+        RMX_CHECK_LAUNCH("attention_merge");
+    }
+    return 0;
+}
+
+RMX_API int rmx_attention_flash_tile_tokens(int group) { return BM / group; }

@@ -156,12 +156,60 @@ def linear(x, w, out):
 
 
 def linear_bf16(x, w, out):
+    """bfloat16 operands, float accumulation; the result in bfloat16 or (for logits) float32."""
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:
-        gemm_plain(x, w, out)
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
 
 
-def attention(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale):
+def attention(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=None):
+    if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, nq // nkv):
+        attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace)
+        return
     attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
                     window, scale, batch.status)
+
+
+def flash_supported(hd: int, group: int) -> bool:
+    return bool(kernels_library().rmx_attention_flash_supports(c_int(hd), c_int(group)))
+
+
+_SM_COUNT = None
+
+
+def _sm_count() -> int:
+    global _SM_COUNT
+    if _SM_COUNT is None:
+        _SM_COUNT = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _SM_COUNT
+
+
+def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
+                    n_splits=None):
+    """Tensor-core attention over pages for bfloat16 (prompt portions and decoded tokens alike)."""
+    lib = kernels_library()
+    group = nq // nkv
+    tq = 64 // group
+    starts = batch.q_start_host
+    n_tiles = sum(-(-(starts[i + 1] - starts[i]) // tq) for i in range(batch.n_seqs))
+    if n_splits is None:
+        # few rows and long contexts (decoding): share a tile's keys among blocks so that every SM has work
+        n_splits = 1
+        blocks = n_tiles * nkv
+        kv_tiles = -(-batch.max_seq_len // 64)
+        if blocks < 2 * _sm_count() and kv_tiles >= 4:
+            n_splits = max(1, min(-(-2 * _sm_count() // blocks), kv_tiles // 2, 64))
+    n = q.shape[0]
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = workspace.get("attn_part_o", (n_splits, n * nq, hd), torch.float32)
+        part_ml = workspace.get("attn_part_ml", (n_splits, n * nq, 2), torch.float32)
+    check(lib.rmx_attention_flash(
+        _ptr(q, torch.bfloat16, "q"), _ptr(k_pool, torch.bfloat16, "k_pool"), _ptr(v_pool, torch.bfloat16, "v_pool"),
+        _ptr(batch.q_start, torch.int32, "q_start"), _ptr(batch.positions, torch.int32, "positions"),
+        _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
+        _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml), c_int(batch.n_seqs), c_int(n), c_int(n_tiles),
+        c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(n_splits),
+        _ptr(batch.status, torch.int32, "status"), _stream()))
+    _launched(2 if n_splits > 1 else 1)

@@ -67,7 +67,7 @@ class AttentionMixer(Mixer):
                           batch.status)
         o = ws.get("attn_out", (n, nq * hd), dt)
         ops.attention(q, cache.k_pool, cache.v_pool, batch, cache.block_table, cache.page_size, o, nq, nkv, hd,
-                      cache.window, self.scale)
+                      cache.window, self.scale, ws)
         y = ws.get("mixer_out", (n, self.width), dt)
         ops.linear(o, self.w_o, y)
         return y

@@ -372,3 +372,91 @@ def test_kernels_refuse_what_they_cannot_do():
     with pytest.raises(KernelError, match="rotary_dim"):
         o.qk_rope_cache(torch.zeros(1, 48, device=DEV), None, None, 0.0, torch.zeros(8, device=DEV), 18, i32, i32,
                         i32.view(1, 1), 4, pool, pool, torch.zeros(1, 16, device=DEV), 1, 1, 16, True, i32)
+
+
+class _Batch:
+    """The few fields of a step's batch that the attention wrappers read."""
+
+    def __init__(self, lengths, new, status):
+        starts = [0]
+        for c in new:
+            starts.append(starts[-1] + c)
+        self.q_start_host, self.n_seqs, self.max_seq_len = starts, len(lengths), max(lengths)
+        self.q_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+        pos, sidx = [], []
+        for s, (n, c) in enumerate(zip(lengths, new)):
+            pos += list(range(n - c, n))
+            sidx += [s] * c
+        self.positions = torch.tensor(pos, dtype=torch.int32, device=DEV)
+        self.seq_index = torch.tensor(sidx, dtype=torch.int32, device=DEV)
+        self.status = status
+
+
+@pytest.mark.parametrize("splits", [None, 1, 3])
+@pytest.mark.parametrize("nq, nkv, hd, page, window", [
+    (4, 2, 16, 16, 0), (6, 2, 32, 8, 20), (5, 5, 64, 4, 0), (12, 4, 96, 32, 37), (32, 8, 128, 64, 0),
+    (16, 1, 128, 16, 0), (7, 7, 128, 2, 5), (8, 2, 64, 64, 100)])
+def test_attention_flash_over_pages(nq, nkv, hd, page, window, splits):
+    """Portions of several sequences (longer than one query tile, crossing key tiles) beside
+    single decoded tokens; NaN in every slot of the pool that must not be read."""
+    from rust_mlx_b200.engine.workspace import Workspace
+    lengths = [200, 1, 33, 130, 300, 64]
+    new = [70, 1, 33, 1, 1, 64]
+    k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, torch.bfloat16, seed=hd + nq)
+    qs = [torch.randn(c, nq, hd).to(torch.bfloat16) for c in new]
+    q = torch.cat(qs).to(DEV).reshape(-1, nq * hd)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    batch = _Batch(lengths, new, status)
+    out = torch.full_like(q, float("nan"))
+    scale = hd ** -0.5
+    ops().attention_flash(q, k_pool, v_pool, batch, table, page, out, nq, nkv, hd, window, scale, Workspace(DEV), n_splits=splits)
+    assert status.item() == 0
+    at = 0
+    for s, (n, c) in enumerate(zip(lengths, new)):
+        want = plain_attention(qs[s], ks[s], vs[s], torch.arange(n - c, n), window, scale)
+        got = out[at:at + c].double().cpu().reshape(c, nq, hd)
+        assert not torch.isnan(got).any()
+        assert (got - want).abs().max().item() < 1e-2, (s, n, c)
+        at += c
+
+
+@pytest.mark.parametrize("splits", [1, 5])
+def test_attention_flash_finds_a_far_key_and_respects_the_window_edge(splits):
+    from rust_mlx_b200.engine.workspace import Workspace
+    nq, nkv, hd, page, n = 8, 2, 64, 16, 900
+    k_pool, v_pool, table, ks, vs = paged_setup([n], nkv, hd, page, torch.bfloat16, seed=8)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    batch = _Batch([n], [1], status)
+    ws = Workspace(DEV)
+    for window, target, seen in ((0, 0, True), (0, 63, True), (0, 64, True), (0, 511, True), (0, n - 1, True),
+                                 (100, n - 101, False), (100, n - 100, True)):
+        q = torch.zeros(1, nq, hd)
+        q[0, :, 5] = 24.0
+        kp = k_pool.clone()
+        kp[table[0, target // page].item(), :, target % page, :] = 0
+        kp[table[0, target // page].item(), :, target % page, 5] = 24.0
+        out = torch.empty(1, nq * hd, dtype=torch.bfloat16, device=DEV)
+        ops().attention_flash(q.reshape(1, -1).to(torch.bfloat16).to(DEV), kp, v_pool, batch, table, page, out, nq, nkv, hd,
+                              window, hd ** -0.5, ws, n_splits=splits)
+        want = vs[0][target].float().repeat_interleave(nq // nkv, 0).reshape(-1)
+        hit = (out[0].float().cpu() - want).abs().max().item() < 2e-2
+        assert hit == seen, (window, target)
+
+
+def test_attention_flash_rows_do_not_depend_on_the_batch():
+    """The same token alone and inside a larger batch gives the same bits (one split)."""
+    from rust_mlx_b200.engine.workspace import Workspace
+    nq, nkv, hd, page = 8, 2, 128, 16
+    lengths, new = [150, 90], [40, 1]
+    k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, torch.bfloat16, seed=2)
+    qs = [torch.randn(c, nq, hd).to(torch.bfloat16) for c in new]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ws = Workspace(DEV)
+    q = torch.cat(qs).to(DEV).reshape(-1, nq * hd)
+    out = torch.empty_like(q)
+    ops().attention_flash(q, k_pool, v_pool, _Batch(lengths, new, status), table, page, out, nq, nkv, hd, 0, hd ** -0.5, ws, n_splits=1)
+    # the last 3 tokens of sequence 0 as a portion of their own
+    q2 = qs[0][-3:].to(DEV).reshape(-1, nq * hd)
+    out2 = torch.empty_like(q2)
+    ops().attention_flash(q2, k_pool, v_pool, _Batch([150], [3], status), table[:1], page, out2, nq, nkv, hd, 0, hd ** -0.5, ws, n_splits=1)
+    assert torch.equal(out2, out[37:40])
