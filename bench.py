@@ -129,9 +129,12 @@ class DecodeRun:
             e.pools.table.reserve(r, self.len + 1)
         toks = self.ids[self.n % len(self.ids)]
         seqs = [SequenceInput(r, self.len, [toks[i]], [0]) for i, r in enumerate(self.rids)]
-        batch = build_batch(seqs, e.pools, e.device, e._status, e.vocab_size)
-        logits = e.forward(batch)
-        self.sampler.sample(logits, [0.0] * self.batch, 0, self.rids, [0] * self.batch, out=self.out)
+        if e.graphs is not None:      # what generation does for a decode step: one captured graph
+            e.graphs.run(seqs, None, None)
+        else:
+            batch = build_batch(seqs, e.pools, e.device, e._status, e.vocab_size)
+            logits = e.forward(batch)
+            self.sampler.sample(logits, [0.0] * self.batch, 0, self.rids, [0] * self.batch, out=self.out)
         self.len += 1
         self.n += 1
         for r in self.rids:

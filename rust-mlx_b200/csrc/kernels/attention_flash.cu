@@ -10,6 +10,12 @@
 // sees keys lo .. p (lo = p - window + 1 or 0).  With n_splits > 1 (long contexts, few
 // rows: decoding) grid.z blocks share a tile's keys and write unnormalised partial
 // results, which attention_merge_kernel combines.
+//
+// Two arrangements of the four warps.  Rows: each warp owns 16 of the tile's 64 rows and
+// all 64 keys of a key tile (prompt portions).  Keys (KEYSPLIT, used when every tile has at
+// most 16 rows, i.e. decoding): all warps hold the same 16 rows and each takes 16 of the 64
+// keys, so that one token's work is spread over the block; the warps' partial results are
+// combined through shared memory at the end.
 #include "common.cuh"
 
 namespace {
@@ -58,8 +64,9 @@ struct FlashParams {
     float scale_log2;
 };
 
-template <int HD>
+template <int HD, bool KEYSPLIT>
 __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashParams p) {
+    constexpr int NT = KEYSPLIT ? 2 : BN / 8;   // score tiles of 8 keys per warp and key tile
     constexpr int STRIDE = HD + 8;          // 16 bytes of padding: ldmatrix rows fall into different banks
     constexpr int CHUNKS = HD / 8;          // 16-byte chunks per row
     constexpr int KSTEPS = HD / 16;
@@ -164,8 +171,10 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
     cp_async_commit();
 
     // ---- this warp's rows
-    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;  // the two rows this thread holds in C fragments
-    const bool warp_active = warp * 16 < rows_valid;
+    const int row_base = KEYSPLIT ? 0 : warp * 16;
+    const int key_base = KEYSPLIT ? warp * 16 : 0;              // this warp's keys inside a key tile
+    const int r_lo = row_base + (lane >> 2), r_hi = r_lo + 8;   // the two rows this thread holds in C fragments
+    const bool warp_active = row_base < rows_valid;
     int row_pos[2], row_lo[2];
     bool row_ok[2];
 #pragma unroll
@@ -181,7 +190,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
     uint32_t qf[KSTEPS][4];
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; ++kk)
-        ldmatrix_x4(qf[kk], Qs + (warp * 16 + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
+        ldmatrix_x4(qf[kk], Qs + (row_base + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
 
     float o[DTILES][4];
 #pragma unroll
@@ -197,15 +206,15 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
         if (warp_active) {
             const __nv_bfloat16* kbase = Ks + stage * BN * STRIDE;
             const __nv_bfloat16* vbase = Vs + stage * BN * STRIDE;
-            float s[BN / 8][4];
+            float s[NT][4];
 #pragma unroll
-            for (int j = 0; j < BN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
             for (int kk = 0; kk < KSTEPS; ++kk) {
 #pragma unroll
-                for (int jp = 0; jp < BN / 16; ++jp) {
+                for (int jp = 0; jp < NT / 2; ++jp) {
                     uint32_t kf[4];
-                    const int key = jp * 16 + (lane & 7) + ((lane >> 4) << 3);
+                    const int key = key_base + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
                     const int dcol = kk * 16 + ((lane >> 3) & 1) * 8;
                     ldmatrix_x4(kf, kbase + key * STRIDE + dcol);
                     mma_bf16(s[2 * jp], qf[kk], kf[0], kf[1]);
@@ -215,11 +224,11 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
             // mask, scale, online softmax (in base 2)
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < BN / 8; ++j) {
+            for (int j = 0; j < NT; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int i = e >> 1;
-                    const int kp = kt * BN + j * 8 + (lane & 3) * 2 + (e & 1);
+                    const int kp = kt * BN + key_base + j * 8 + (lane & 3) * 2 + (e & 1);
                     const bool ok = row_ok[i] && kp <= row_pos[i] && kp >= row_lo[i];
                     s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
                     mx[i] = fmaxf(mx[i], s[j][e]);
@@ -237,7 +246,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
             }
             const float mref[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
 #pragma unroll
-            for (int j = 0; j < BN / 8; ++j) {
+            for (int j = 0; j < NT; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int i = e >> 1;
@@ -253,7 +262,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
             }
             // O += P V
 #pragma unroll
-            for (int kk = 0; kk < BN / 16; ++kk) {
+            for (int kk = 0; kk < NT / 2; ++kk) {
                 uint32_t pf[4];
                 pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
                 pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -262,7 +271,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
 #pragma unroll
                 for (int dp = 0; dp < DTILES / 2; ++dp) {
                     uint32_t vf[4];
-                    const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    const int key = key_base + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
                     const int dcol = dp * 16 + (lane >> 4) * 8;
                     ldmatrix_x4_trans(vf, vbase + key * STRIDE + dcol);
                     mma_bf16(o[2 * dp], pf, vf[0], vf[1]);
@@ -274,12 +283,58 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
     }
     cp_async_wait<0>();
 
-    if (!warp_active) return;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
     }
+    if constexpr (KEYSPLIT) {
+        // the four warps hold partial results for the same rows: combine them in warp order
+        float* so = reinterpret_cast<float*>(Ks);             // [NWARPS][16][HD]   (key tiles are done)
+        float* sml = so + NWARPS * 16 * HD;                   // [NWARPS][16][2]
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = (lane >> 2) + 8 * i;
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d) {
+                const int col = d * 8 + (lane & 3) * 2;
+                *reinterpret_cast<float2*>(so + (warp * 16 + r) * HD + col) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+            }
+            if ((lane & 3) == 0) {
+                sml[(warp * 16 + r) * 2] = m[i];
+                sml[(warp * 16 + r) * 2 + 1] = l[i];
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < rows_valid * HD; idx += THREADS) {
+            const int r = idx / HD, d = idx - r * HD;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, sml[(w * 16 + r) * 2]);
+            float L = 0.f, acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < NWARPS; ++w) {
+                const float mw = sml[(w * 16 + r) * 2];
+                const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+                L += f * sml[(w * 16 + r) * 2 + 1];
+                acc += f * so[(w * 16 + r) * HD + d];
+            }
+            const int tok = r / p.group, g = r - tok * p.group;
+            const size_t row = (size_t)(tok0 + tok) * p.nq + kvh * p.group + g;
+            if (p.n_splits == 1) {
+                p.out[row * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            } else {
+                const size_t prow = (size_t)split * p.n_tokens * p.nq + row;
+                p.part_o[prow * HD + d] = acc;
+                if (d == 0) {
+                    p.part_ml[prow * 2] = M;
+                    p.part_ml[prow * 2 + 1] = L;
+                }
+            }
+        }
+        return;
+    }
+    if (!warp_active) return;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = i == 0 ? r_lo : r_hi;
@@ -332,17 +387,26 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     }
 }
 
-template <int HD>
-int launch_flash(const FlashParams& p, int n_tiles, cudaStream_t s) {
-    constexpr size_t smem = (size_t)(BM + 4 * BN) * (HD + 8) * sizeof(__nv_bfloat16);
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_flash_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+template <int HD, bool KEYSPLIT>
+int launch_flash_as(const FlashParams& p, int n_tiles, cudaStream_t s) {
+    constexpr size_t tiles = (size_t)(BM + 4 * BN) * (HD + 8) * sizeof(__nv_bfloat16);
+    constexpr size_t merge = (size_t)BM * (HD + 8) * sizeof(__nv_bfloat16) + (size_t)NWARPS * 16 * (HD + 2) * sizeof(float);
+    constexpr size_t smem = tiles > merge ? tiles : merge;
+    static bool raised = false;  // per instantiation: the attribute is set once
+    if (smem > 48 * 1024 && !raised) {
+        cudaError_t e = cudaFuncSetAttribute(attention_flash_kernel<HD, KEYSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RMX_FAIL("attention_flash: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
+        raised = true;
     }
     dim3 grid(n_tiles, p.nkv, p.n_splits);
-    attention_flash_kernel<HD><<<grid, THREADS, smem, s>>>(p);
+    attention_flash_kernel<HD, KEYSPLIT><<<grid, THREADS, smem, s>>>(p);
     RMX_CHECK_LAUNCH("attention_flash");
     return 0;
+}
+
+template <int HD>
+int launch_flash(const FlashParams& p, int n_tiles, bool keysplit, cudaStream_t s) {
+    return keysplit ? launch_flash_as<HD, true>(p, n_tiles, s) : launch_flash_as<HD, false>(p, n_tiles, s);
 }
 }  // namespace
 
@@ -352,13 +416,14 @@ RMX_API int rmx_attention_flash_supports(int hd, int group) {
     return hd_ok && group >= 1 && group <= 16 ? 1 : 0;
 }
 
+// max_q_len: the most tokens any sequence brings to this step (0: unknown).
 // n_tiles: the number of query tiles of the batch, sum over sequences of ceil(tokens / (64 / group)).
 // part_o / part_ml are needed when n_splits > 1: [n_splits, tokens * nq, hd] and [n_splits, tokens * nq, 2] floats.
 RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v_pool, const int* q_start,
                                 const int* positions, const int* block_table, int table_stride, int page_size,
                                 void* out, float* part_o, float* part_ml, int n_seqs, int n_tokens, int n_tiles,
-                                int nq, int nkv, int hd, int window, float scale, int n_splits, int* status,
-                                void* stream) {
+                                int nq, int nkv, int hd, int window, float scale, int n_splits, int max_q_len,
+                                int* status, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_flash: %d query heads over %d kv heads", nq, nkv);
     const int group = nq / nkv;
@@ -374,13 +439,15 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     p.table_stride = table_stride; p.page_size = page_size; p.window = window; p.n_splits = n_splits;
     p.scale_log2 = scale * LOG2E;
     cudaStream_t s = (cudaStream_t)stream;
+    // every tile has at most 16 rows (decoding, or very short portions): spread keys over the warps
+    const bool keysplit = max_q_len > 0 && max_q_len * group <= 16;
     int rc;
     switch (hd) {
-        case 16: rc = launch_flash<16>(p, n_tiles, s); break;
-        case 32: rc = launch_flash<32>(p, n_tiles, s); break;
-        case 64: rc = launch_flash<64>(p, n_tiles, s); break;
-        case 96: rc = launch_flash<96>(p, n_tiles, s); break;
-        default: rc = launch_flash<128>(p, n_tiles, s); break;
+        case 16: rc = launch_flash<16>(p, n_tiles, keysplit, s); break;
+        case 32: rc = launch_flash<32>(p, n_tiles, keysplit, s); break;
+        case 64: rc = launch_flash<64>(p, n_tiles, keysplit, s); break;
+        case 96: rc = launch_flash<96>(p, n_tiles, keysplit, s); break;
+        default: rc = launch_flash<128>(p, n_tiles, keysplit, s); break;
     }
     if (rc != 0) return rc;
     if (n_splits > 1) {

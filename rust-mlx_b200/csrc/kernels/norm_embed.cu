@@ -5,6 +5,28 @@
 // scaling are done in float and rounded once.
 #include "common.cuh"
 
+// Four consecutive numbers as floats (the address is 16-byte aligned for float, 8 for bfloat16).
+__device__ __forceinline__ void load4(const float* p, float4& v) { v = *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float4& v) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v = make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float4& v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a);
+    raw.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+// Threads of a block that takes one row: four numbers per thread, a whole number of warps.
+static inline int block_threads(int width) {
+    int t = ((width + 3) / 4 + 31) / 32 * 32;
+    return t < 32 ? 32 : (t > 1024 ? 1024 : t);
+}
+
 // h[t, :] = table[ids[t], :] as float.  An id outside the table writes zeros (the host
 // rejects such ids before the step; the kernel never reads outside the table).
 template <typename T>
@@ -15,14 +37,22 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     const bool ok = id >= 0 && id < vocab;
     const T* row = table + (size_t)(ok ? id : 0) * width;
     float* out = h + (size_t)t * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = ok ? to_float(row[i]) : 0.f;
+    if ((width & 3) == 0) {  // four numbers per thread and pass
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (ok) load4(row + i, v);
+            *reinterpret_cast<float4*>(out + i) = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = ok ? to_float(row[i]) : 0.f;
+    }
 }
 
 RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tokens, int width, int vocab,
                           int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embedding: bad sizes");
-    const int threads = width >= 1024 ? 256 : 128;
+    const int threads = block_threads(width);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_F32)
         embedding_kernel<float><<<n_tokens, threads, 0, s>>>(ids, (const float*)table, h, width, vocab);
@@ -44,23 +74,45 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
                                    const int* __restrict__ rows, const float* __restrict__ w, float eps,
                                    T* __restrict__ x, int width, int write_h) {
     __shared__ float scratch[32];
-    extern __shared__ float vals[];
+    extern __shared__ __align__(16) float vals[];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* hrow = h + (size_t)src * width;
     const T* drow = delta ? delta + (size_t)src * width : nullptr;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = hrow[i];
-        if (drow) v += to_float(drow[i]);
-        vals[i] = v;
-        if (write_h) hrow[i] = v;
-        ss += v * v;
-    }
-    const float total = block_sum(ss, scratch);
-    const float inv = rsqrtf(total / (float)width + eps);
     T* xrow = x + (size_t)r * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) xrow[i] = from_float<T>(vals[i] * inv * w[i]);
+    float ss = 0.f;
+    if ((width & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            float4 v = *reinterpret_cast<const float4*>(hrow + i);
+            if (drow) {
+                float4 d;
+                load4(drow + i, d);
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            }
+            *reinterpret_cast<float4*>(vals + i) = v;
+            if (write_h) *reinterpret_cast<float4*>(hrow + i) = v;
+            ss += v.x * v.x;
+            ss += v.y * v.y;
+            ss += v.z * v.z;
+            ss += v.w * v.w;
+        }
+        const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(vals + i);
+            const float4 g = *reinterpret_cast<const float4*>(w + i);
+            store4(xrow + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            float v = hrow[i];
+            if (drow) v += to_float(drow[i]);
+            vals[i] = v;
+            if (write_h) hrow[i] = v;
+            ss += v * v;
+        }
+        const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+        for (int i = threadIdx.x; i < width; i += blockDim.x) xrow[i] = from_float<T>(vals[i] * inv * w[i]);
+    }
 }
 
 RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const int* rows, const float* w, float eps, void* x,
@@ -69,7 +121,7 @@ RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const int* rows, const 
     RMX_REQUIRE(n_rows > 0 && width > 0, "add_rmsnorm: bad sizes");
     RMX_REQUIRE((size_t)width * 4 <= 160 * 1024, "add_rmsnorm: width %d is beyond 40960", width);
     RMX_REQUIRE(!(rows && write_h), "add_rmsnorm: rows and write_h do not go together");
-    const int threads = 256;
+    const int threads = block_threads(width);
     const size_t smem = (size_t)width * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_F32) {
@@ -90,6 +142,8 @@ RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const int* rows, const 
 
 // out[t, j] = silu(gate_up[t, j]) * gate_up[t, inter + j], silu(z) = z / (1 + exp(-z)),
 // in float with one rounding.
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
+
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -98,23 +152,40 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     const int j = (int)(idx - t * inter);
     const float g = to_float(gate_up[t * 2 * inter + j]);
     const float u = to_float(gate_up[t * 2 * inter + inter + j]);
-    const float sg = g / (1.f + expf(-g));
-    out[idx] = from_float<T>(sg * u);
+    out[idx] = from_float<T>(silu_mul(g, u));
+}
+
+// four outputs per thread; inter is a multiple of 4
+template <typename T>
+__global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total4) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total4) return;
+    const int per_row = inter >> 2;
+    const size_t t = idx / per_row;
+    const int j = (int)(idx - t * per_row) * 4;
+    float4 g, u;
+    load4(gate_up + t * 2 * inter + j, g);
+    load4(gate_up + t * 2 * inter + inter + j, u);
+    store4(out + t * inter + j, make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w)));
 }
 
 RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && inter > 0, "swiglu: bad sizes");
-    const size_t total = (size_t)n_tokens * inter;
+    const bool vec = (inter & 3) == 0;
+    const size_t total = (size_t)n_tokens * inter / (vec ? 4 : 1);
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == RMX_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
-    else if (dtype == RMX_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
-    else
+    if (dtype == RMX_F32) {
+        if (vec) swiglu_kernel4<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
+        else swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
+    } else if (dtype == RMX_BF16) {
+        if (vec) swiglu_kernel4<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+        else swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    } else {
         RMX_FAIL("swiglu: unknown dtype %d", dtype);
+    }
     RMX_CHECK_LAUNCH("swiglu");
     return 0;
 }

@@ -5,9 +5,10 @@ Per token: its id, its absolute position and the index of its sequence in the
 batch.  Per sequence: where its tokens start in the flat list (``q_start``), its
 length after this step (``seq_lens``), its state slot, and per paged cache group
 its block table.  ``logit_rows`` are the flat indices of the tokens whose logits
-are wanted.  The reference runs either one request's tokens or several requests'
-single tokens at one offset (src/dense.rs:371, src/batching.rs:34-53); here any mix
-is one batch.
+are wanted.  Two float rows (temperatures and uniform numbers for sampling) ride
+in the same buffer.  The reference runs either one request's tokens or several
+requests' single tokens at one offset (src/dense.rs:371, src/batching.rs:34-53);
+here any mix is one batch.
 """
 from __future__ import annotations
 
@@ -41,6 +42,8 @@ class StepBatch:
     logit_rows: torch.Tensor
     block_tables: list
     status: torch.Tensor
+    temperatures: torch.Tensor
+    uniforms: torch.Tensor
     q_start_host: list
     seq_lens_host: list
     start_host: list
@@ -53,61 +56,92 @@ class StepBatch:
         return self.max_q_len == 1
 
 
-def build_batch(seqs: list, pools, device, status: torch.Tensor, vocab_size: int) -> StepBatch:
-    """Lay out the metadata of ``seqs`` in one pinned buffer and copy it to the device."""
-    n_seqs = len(seqs)
-    counts = [len(s.tokens) for s in seqs]
-    n_tokens = sum(counts)
-    if n_tokens == 0:
+class BatchLayout:
+    """Where each array lies in the one int32 buffer of a batch of given sizes."""
+
+    def __init__(self, n_tokens: int, n_seqs: int, n_rows: int, entries: list):
+        self.n_tokens, self.n_seqs, self.n_rows, self.entries = n_tokens, n_seqs, n_rows, list(entries)
+        rows = max(n_rows, 1)
+        self.sizes = [n_tokens, n_tokens, n_tokens, n_seqs + 1, n_seqs, n_seqs, rows, rows, rows] + \
+                     [n_seqs * e for e in entries]
+        # every array starts on a 16-byte boundary
+        self.offsets, at = [], 0
+        for n in self.sizes:
+            self.offsets.append(at)
+            at += -(-n // 4) * 4
+        self.total = at
+
+    def part(self, buf, i, n=None):
+        return buf[self.offsets[i]:self.offsets[i] + (self.sizes[i] if n is None else n)]
+
+    def fill(self, buf: np.ndarray, seqs: list, pools, vocab_size: int, temperatures=None, uniforms=None) -> dict:
+        """Write the arrays of ``seqs`` into ``buf`` (int32, ``total`` long); returns host-side facts."""
+        counts = [len(s.tokens) for s in seqs]
+        q_start, rows = [0], []
+        for s, c in zip(seqs, counts):
+            for w in s.want:
+                if not 0 <= w < c:
+                    raise ValueError(f"request {s.req!r} wants logits at place {w} of {c} tokens")
+                rows.append(q_start[-1] + w)
+            q_start.append(q_start[-1] + c)
+        ids = np.fromiter((t for s in seqs for t in s.tokens), dtype=np.int64, count=self.n_tokens)
+        if ids.min() < 0 or ids.max() >= vocab_size:
+            raise ValueError("token outside vocabulary")
+        self.part(buf, 0)[:] = ids
+        pos, sidx = self.part(buf, 1), self.part(buf, 2)
+        for i, (s, c) in enumerate(zip(seqs, counts)):
+            pos[q_start[i]:q_start[i + 1]] = np.arange(s.start, s.start + c, dtype=np.int32)
+            sidx[q_start[i]:q_start[i + 1]] = i
+        self.part(buf, 3)[:] = q_start
+        seq_lens = [s.start + c for s, c in zip(seqs, counts)]
+        self.part(buf, 4)[:] = seq_lens
+        table = pools.table
+        slots = [table.slot(s.req) for s in seqs]
+        self.part(buf, 5)[:] = slots
+        self.part(buf, 6)[:len(rows)] = rows
+        fl = self.part(buf, 7).view(np.float32)
+        fl[:] = 0.0
+        if temperatures is not None:
+            fl[:len(temperatures)] = temperatures
+        fl = self.part(buf, 8).view(np.float32)
+        fl[:] = 0.0
+        if uniforms is not None:
+            fl[:len(uniforms)] = uniforms
+        for g, grp in enumerate(pools.paged_groups):
+            e = self.entries[g]
+            tab = self.part(buf, 9 + g).reshape(self.n_seqs, e)
+            tab[:] = -1
+            for i, s in enumerate(seqs):
+                table.table_into(s.req, grp.table_index, tab[i].ctypes.data, e)
+        return dict(q_start_host=q_start, seq_lens_host=seq_lens, start_host=[s.start for s in seqs],
+                    slots_host=slots, max_q_len=max(counts), max_seq_len=max(seq_lens))
+
+    def views(self, dev: torch.Tensor, status: torch.Tensor, host_facts: dict) -> StepBatch:
+        p = lambda i, n=None: self.part(dev, i, n)  # noqa: E731
+        return StepBatch(
+            n_tokens=self.n_tokens, n_seqs=self.n_seqs, n_rows=self.n_rows, token_ids=p(0), positions=p(1),
+            seq_index=p(2), q_start=p(3), seq_lens=p(4), slots=p(5), logit_rows=p(6, self.n_rows),
+            temperatures=p(7, self.n_rows).view(torch.float32), uniforms=p(8, self.n_rows).view(torch.float32),
+            block_tables=[p(9 + g).view(self.n_seqs, self.entries[g]) for g in range(len(self.entries))],
+            status=status, **host_facts)
+
+
+def check_sequences(seqs: list) -> None:
+    if not seqs or sum(len(s.tokens) for s in seqs) == 0:
         raise ValueError("a step needs at least one token")
-    rows = []
-    q_start = [0]
-    for s, c in zip(seqs, counts):
-        if c == 0:
+    for s in seqs:
+        if not s.tokens:
             raise ValueError(f"request {s.req!r} brings no tokens to the step")
-        for w in s.want:
-            if not 0 <= w < c:
-                raise ValueError(f"request {s.req!r} wants logits at place {w} of {c} tokens")
-            rows.append(q_start[-1] + w)
-        q_start.append(q_start[-1] + c)
-    n_rows = len(rows)
-    table = pools.table
-    groups = pools.paged_groups
-    entries = [max(1, -(-max(s.start + c for s, c in zip(seqs, counts)) // pools.page_size)) for _ in groups]
 
-    sizes = [n_tokens, n_tokens, n_tokens, n_seqs + 1, n_seqs, n_seqs, max(n_rows, 1)] + [n_seqs * e for e in entries]
-    offsets = np.concatenate([[0], np.cumsum(sizes)])
-    host = torch.empty(int(offsets[-1]), dtype=torch.int32, pin_memory=torch.cuda.is_available())
-    buf = host.numpy()
-    ids = np.fromiter((t for s in seqs for t in s.tokens), dtype=np.int64, count=n_tokens)
-    if ids.min() < 0 or ids.max() >= vocab_size:
-        raise ValueError("token outside vocabulary")
-    buf[offsets[0]:offsets[1]] = ids
-    pos = buf[offsets[1]:offsets[2]]
-    sidx = buf[offsets[2]:offsets[3]]
-    for i, (s, c) in enumerate(zip(seqs, counts)):
-        pos[q_start[i]:q_start[i + 1]] = np.arange(s.start, s.start + c, dtype=np.int32)
-        sidx[q_start[i]:q_start[i + 1]] = i
-    buf[offsets[3]:offsets[4]] = q_start
-    seq_lens = [s.start + c for s, c in zip(seqs, counts)]
-    buf[offsets[4]:offsets[5]] = seq_lens
-    slots_host = [table.slot(s.req) for s in seqs]
-    buf[offsets[5]:offsets[6]] = slots_host
-    buf[offsets[6]:offsets[7]] = rows if rows else [0]
-    for g, grp in enumerate(groups):
-        e = entries[g]
-        tab = buf[offsets[7 + g]:offsets[8 + g]].reshape(n_seqs, e)
-        tab[:] = -1
-        for i, s in enumerate(seqs):
-            table.table_into(s.req, grp.table_index, tab[i].ctypes.data, e)
+
+def build_batch(seqs: list, pools, device, status: torch.Tensor, vocab_size: int, temperatures=None,
+                uniforms=None) -> StepBatch:
+    """Lay out the metadata of ``seqs`` in one pinned buffer and copy it to the device."""
+    check_sequences(seqs)
+    longest = max(s.start + len(s.tokens) for s in seqs)
+    entries = [max(1, -(-longest // pools.page_size)) for _ in pools.paged_groups]
+    layout = BatchLayout(sum(len(s.tokens) for s in seqs), len(seqs), sum(len(s.want) for s in seqs), entries)
+    host = torch.empty(layout.total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+    facts = layout.fill(host.numpy(), seqs, pools, vocab_size, temperatures, uniforms)
     dev = host.to(device, non_blocking=True)
-
-    def part(i, n=None):
-        return dev[int(offsets[i]):int(offsets[i]) + (sizes[i] if n is None else n)]
-
-    return StepBatch(
-        n_tokens=n_tokens, n_seqs=n_seqs, n_rows=n_rows, token_ids=part(0), positions=part(1), seq_index=part(2),
-        q_start=part(3), seq_lens=part(4), slots=part(5), logit_rows=part(6, n_rows),
-        block_tables=[part(7 + g).view(n_seqs, entries[g]) for g in range(len(groups))], status=status,
-        q_start_host=q_start, seq_lens_host=seq_lens, start_host=[s.start for s in seqs], slots_host=slots_host,
-        max_q_len=max(counts), max_seq_len=max(seq_lens))
+    return layout.views(dev, status, facts)

@@ -50,7 +50,7 @@ class Engine:
 
     def __init__(self, model, *, dtype: str = "bfloat16", random_weights: bool = False, seed: int = 0,
                  max_tokens: int = 8192, page_size: int = 64, max_requests: int = 256, device: str = "cuda:0",
-                 verbose: bool = False):
+                 max_context: int = 0, cuda_graphs: bool = True, verbose: bool = False):
         if dtype not in _DTYPES:
             raise EngineError(f"dtype must be one of {sorted(set(_DTYPES))}, got {dtype!r}")
         if not torch.cuda.is_available():
@@ -96,6 +96,17 @@ class Engine:
             self._calls.append((call, call.cache in seen))
             seen.add(call.cache)
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # the longest sequence a request may reach: the cache's size, the model's stated limit, or the caller's
+        limit = self.pools.num_pages * page_size
+        stated = getattr(self.config, "max_position_embeddings", 0) or 0
+        if stated > 0:
+            limit = min(limit, stated)
+        self.max_context = min(limit, max_context) if max_context > 0 else limit
+        self.ops = _ops
+        self.max_kv_heads = max([s.kv_heads for s in self.spec.cache_specs().values() if s.kind == "paged"] or [1])
+        self._launches_per_graph = {}
+        from .graphs import DecodeGraphs
+        self.graphs = DecodeGraphs(self) if cuda_graphs and all(p.graph_safe for p in self.spec.all_parts()) else None
         self._req_ids = {}
         self._next_id = 0
         self.load_seconds = time.time() - t0

@@ -15,7 +15,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-from ..sampling.sampler import Sampler
+from ..sampling.rng import uniform
 from .batch import SequenceInput, build_batch
 from .scheduler import Scheduler
 
@@ -57,7 +57,6 @@ def generate(engine, prompts: list, *, max_tokens: int = 256, temperature: float
     budget = max_batch_tokens or max(prefill_chunk, max_seqs)
     sched = Scheduler(engine.pools.table, max_seqs=max_seqs, max_batch_tokens=budget, prefill_chunk=prefill_chunk,
                       max_context=max_context)
-    sampler = Sampler(engine.device)
     rids = [engine._rid(("generate", id(sched), i)) for i in range(n)]
     index = {rid: i for i, rid in enumerate(rids)}
     known = [list(p) for p in prompts]
@@ -84,13 +83,18 @@ def generate(engine, prompts: list, *, max_tokens: int = 256, temperature: float
                                           [e.count - 1] if e.wants_logits else []))
                 if e.wants_logits:
                     wanting.append(i)
-            batch = build_batch(seqs, engine.pools, engine.device, engine._status, engine.vocab_size)
-            logits = engine.forward(batch)
-            if wanting:
-                sampler.sample(logits, [temps[i] for i in wanting], seed, wanting, [len(out[i]) for i in wanting],
-                               out=result_buf[1:1 + len(wanting)])
-            result_buf[0:1].copy_(engine._status)
-            host = result_buf[:1 + len(wanting)].tolist()  # the step's one synchronisation
+            t_list = [temps[i] for i in wanting]
+            u_list = [uniform(seed, i, len(out[i])) if temps[i] > 0 else 0.0 for i in wanting]
+            if engine.graphs is not None and len(wanting) == len(entries) and all(e.count == 1 for e in entries):
+                result = engine.graphs.run(seqs, t_list, u_list)          # a decode step: one captured graph
+                host = result.tolist()                                    # the step's one synchronisation
+            else:
+                batch = build_batch(seqs, engine.pools, engine.device, engine._status, engine.vocab_size, t_list, u_list)
+                logits = engine.forward(batch)
+                if wanting:
+                    engine.ops.sample(logits, batch.temperatures, batch.uniforms, result_buf[1:1 + len(wanting)])
+                result_buf[0:1].copy_(engine._status)
+                host = result_buf[:1 + len(wanting)].tolist()             # the step's one synchronisation
             if host[0] != 0:
                 engine.check_status()
             sched.step_done()

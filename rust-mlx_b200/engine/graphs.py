@@ -1,0 +1,106 @@
+"""Decode steps as CUDA graphs.
+
+A decode step (every sequence brings one token and wants its logits) launches a
+few hundred small kernels; issuing them one by one costs more host time than
+the GPU needs to run them.  The step — embedding, every layer, final norm, head
+and sampling — is captured once per (batch size, attention split count) into a
+CUDA graph whose kernels read the step's ids, positions, block tables and
+sampling numbers from one device buffer of fixed address and layout; each later
+step of that shape copies its numbers into the buffer and launches the graph.
+Graphs are dropped when a workspace buffer they point into is reallocated.
+"""
+from __future__ import annotations
+
+import torch
+
+from .batch import BatchLayout, check_sequences
+
+
+class _Captured:
+    __slots__ = ("graph", "layout", "hosts", "events", "turn", "dev", "result", "generation", "batch")
+
+
+class DecodeGraphs:
+    def __init__(self, engine, max_graphs: int = 32):
+        self.engine = engine
+        self.max_graphs = max_graphs
+        self.graphs = {}
+        self.replays = 0
+        self.captures = 0
+
+    def entries(self) -> list:
+        e = self.engine
+        return [max(1, -(-e.max_context // e.pools.page_size)) for _ in e.pools.paged_groups]
+
+    def run(self, seqs: list, temperatures, uniforms) -> torch.Tensor:
+        """One decode step of ``seqs`` (one token each).  Returns the device tensor
+        [status, token_0, ...]; the caller copies it to the host."""
+        e = self.engine
+        check_sequences(seqs)
+        n = len(seqs)
+        longest = max(s.start + 1 for s in seqs)
+        if longest > e.max_context:
+            raise ValueError(f"a sequence of {longest} tokens exceeds the context limit {e.max_context}")
+        splits = e.ops.flash_splits(n, e.max_kv_heads, longest) if hasattr(e.ops, "flash_splits") else 1
+        key = (n, splits)
+        cap = self.graphs.get(key)
+        if cap is not None and cap.generation != e.workspace.generation:
+            del self.graphs[key]
+            cap = None
+        if cap is None:
+            cap = self._capture(seqs, temperatures, uniforms, key)
+        # staging buffers take turns, so that a caller who does not wait for each step's result
+        # never overwrites numbers whose copy to the device is still to come
+        cap.turn = (cap.turn + 1) % len(cap.hosts)
+        host, event = cap.hosts[cap.turn], cap.events[cap.turn]
+        event.synchronize()
+        facts = cap.layout.fill(host.numpy(), seqs, e.pools, e.vocab_size, temperatures, uniforms)
+        cap.batch.max_seq_len = facts["max_seq_len"]
+        cap.dev.copy_(host, non_blocking=True)
+        event.record()
+        cap.graph.replay()
+        self.replays += 1
+        e.ops.count_launches(e._launches_per_graph.get(key, 0))
+        return cap.result
+
+    def _capture(self, seqs, temperatures, uniforms, key) -> _Captured:
+        e = self.engine
+        n = len(seqs)
+        if len(self.graphs) >= self.max_graphs:
+            self.graphs.pop(next(iter(self.graphs)))
+        cap = _Captured()
+        cap.layout = BatchLayout(n, n, n, self.entries())
+        cap.hosts = [torch.empty(cap.layout.total, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        cap.events = [torch.cuda.Event() for _ in cap.hosts]
+        cap.turn = 0
+        cap.dev = torch.zeros(cap.layout.total, dtype=torch.int32, device=e.device)
+        cap.result = torch.zeros(n + 1, dtype=torch.int32, device=e.device)
+        facts = cap.layout.fill(cap.hosts[0].numpy(), seqs, e.pools, e.vocab_size, temperatures, uniforms)
+        cap.dev.copy_(cap.hosts[0], non_blocking=True)
+        cap.events[0].record()
+        cap.batch = cap.layout.views(cap.dev, e._status, facts)
+        cap.batch.forced_splits = key[1]
+        # once eagerly: buffers reach their size, kernels' attributes are set, libraries warm up.
+        # It writes this step's keys and values, which the replay below writes again, the same.
+        self._step(cap)
+        torch.cuda.synchronize()
+        cap.generation = e.workspace.generation
+        e.workspace.frozen = True
+        try:
+            before = e.ops.launch_count
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._step(cap)
+            e._launches_per_graph[key] = e.ops.launch_count - before
+        finally:
+            e.workspace.frozen = False
+        cap.graph = graph
+        self.graphs[key] = cap
+        self.captures += 1
+        return cap
+
+    def _step(self, cap) -> None:
+        e = self.engine
+        logits = e.forward(cap.batch)
+        e.ops.sample(logits, cap.batch.temperatures, cap.batch.uniforms, cap.result[1:])
+        cap.result[0:1].copy_(e._status)

@@ -16,6 +16,7 @@ class Workspace:
         self.device = device
         self.buffers = {}
         self.frozen = False
+        self.generation = 0   # counts reallocations: who holds addresses compares it
 
     def get(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
         numel = math.prod(shape)
@@ -24,6 +25,8 @@ class Workspace:
         if buf is None or buf.numel() < numel:
             if self.frozen:
                 raise RuntimeError(f"workspace buffer {name} would have to grow to {numel} while frozen")
+            if buf is not None:
+                self.generation += 1
             buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
             self.buffers[key] = buf
         return buf[:numel].view(shape)

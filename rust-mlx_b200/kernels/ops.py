@@ -48,6 +48,11 @@ def _launched(n=1):
     launch_count += n
 
 
+def count_launches(n: int) -> None:
+    """Kernels of this package launched by replaying a captured graph."""
+    _launched(n)
+
+
 def embedding(ids, table, h_out):
     """h_out[t] = table[ids[t]] as float32 (the residual stream)."""
     lib = kernels_library()
@@ -185,6 +190,16 @@ def _sm_count() -> int:
     return _SM_COUNT
 
 
+def flash_splits(n_tiles: int, nkv: int, max_seq_len: int) -> int:
+    """Few rows and long contexts (decoding): share a tile's keys among blocks so that every
+    SM has work.  Two blocks fit an SM: fill them once, not one and a bit."""
+    blocks = n_tiles * nkv
+    kv_tiles = -(-max_seq_len // 64)
+    if blocks < 2 * _sm_count() and kv_tiles >= 4:
+        return max(1, min(2 * _sm_count() // blocks, kv_tiles // 2, 64))
+    return 1
+
+
 def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
                     n_splits=None):
     """Tensor-core attention over pages for bfloat16 (prompt portions and decoded tokens alike)."""
@@ -194,12 +209,7 @@ def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
     starts = batch.q_start_host
     n_tiles = sum(-(-(starts[i + 1] - starts[i]) // tq) for i in range(batch.n_seqs))
     if n_splits is None:
-        # few rows and long contexts (decoding): share a tile's keys among blocks so that every SM has work
-        n_splits = 1
-        blocks = n_tiles * nkv
-        kv_tiles = -(-batch.max_seq_len // 64)
-        if blocks < 2 * _sm_count() and kv_tiles >= 4:
-            n_splits = max(1, min(-(-2 * _sm_count() // blocks), kv_tiles // 2, 64))
+        n_splits = getattr(batch, "forced_splits", None) or flash_splits(n_tiles, nkv, batch.max_seq_len)
     n = q.shape[0]
     part_o = part_ml = None
     if n_splits > 1:
@@ -211,5 +221,5 @@ def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
         _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml), c_int(batch.n_seqs), c_int(n), c_int(n_tiles),
         c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(n_splits),
-        _ptr(batch.status, torch.int32, "status"), _stream()))
+        c_int(getattr(batch, "max_q_len", 0)), _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched(2 if n_splits > 1 else 1)

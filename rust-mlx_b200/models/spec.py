@@ -23,8 +23,18 @@ class ModelSpec(Part):
     vocab_size: int = 0
     eos_token_ids: tuple = ()
 
+    graph_safe = True
+
     def children(self) -> list:
         return [self.embedding, *self.blocks, self.final_norm, self.head]
+
+    def all_parts(self) -> list:
+        out, todo = [], [self]
+        while todo:
+            part = todo.pop()
+            out.append(part)
+            todo.extend(part.children())
+        return out
 
     def cache_specs(self) -> dict:
         """cache id -> CacheSpec of the run that writes it (the first that names it)."""

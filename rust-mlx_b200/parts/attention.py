@@ -15,6 +15,8 @@ from .base import CacheSpec, Mixer, ParamSpec
 
 
 class AttentionMixer(Mixer):
+    graph_safe = True
+
     def __init__(self, prefix: str, width: int, heads: int, kv_heads: int, head_dim: int, position,
                  qk_norm_eps: float | None = None, window: int = 0, scale: float | None = None):
         if heads % kv_heads:

@@ -71,7 +71,15 @@ class BuildContext:
 
 
 class Part:
-    """Base of mixers, feed-forwards, norms, position encodings, embeddings and heads."""
+    """Base of mixers, feed-forwards, norms, position encodings, embeddings and heads.
+
+    ``graph_safe``: the part's ``forward`` may be captured in a CUDA graph and replayed for
+    later steps of the same shape: it launches the same kernels with the same addresses
+    and takes everything that changes from step to step (positions, block tables, slots)
+    from the batch's device tensors, never from its host-side lists.  Off unless a part
+    says so; one part that is not keeps the whole model on plain launches."""
+
+    graph_safe = False
 
     def param_specs(self) -> list:
         return []

@@ -12,6 +12,8 @@ from .base import Part
 
 
 class PreNormBlock(Part):
+    graph_safe = True
+
     def __init__(self, norm1, mixer, norm2, ffn):
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
 

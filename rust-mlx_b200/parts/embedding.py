@@ -12,6 +12,8 @@ from .base import ParamSpec, Part
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, name: str, vocab: int, width: int):
         self.name, self.vocab, self.width = name, int(vocab), int(width)
         self.weight = None
@@ -30,6 +32,8 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
+    graph_safe = True
+
     """``name`` of its own weight, or ``tied_to`` an embedding whose table it reads."""
 
     def __init__(self, vocab: int, width: int, name: str | None = None, tied_to: TokenEmbedding | None = None):

@@ -12,6 +12,8 @@ from .base import FeedForward, ParamSpec
 
 
 class SwiGLUFeedForward(FeedForward):
+    graph_safe = True
+
     def __init__(self, prefix: str, width: int, inner: int):
         self.prefix, self.width, self.inner = prefix, int(width), int(inner)
         self.w_gate_up = self.w_down = None

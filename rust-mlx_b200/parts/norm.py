@@ -12,6 +12,8 @@ from .base import Norm, ParamSpec
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, name: str, width: int, eps: float):
         self.name, self.width, self.eps = name, int(width), float(eps)
         self.weight = None

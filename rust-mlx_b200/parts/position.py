@@ -15,6 +15,8 @@ from .base import PositionEncoding
 
 
 class RotaryEmbedding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None):
         self.head_dim = int(head_dim)
         self.rotary_dim = int(head_dim if rotary_dim is None else rotary_dim)
@@ -31,5 +33,7 @@ class RotaryEmbedding(PositionEncoding):
 
 
 class NoPositionEncoding(PositionEncoding):
+    graph_safe = True
+
     rotary_dim = 0
     inv_freq = None

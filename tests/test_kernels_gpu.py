@@ -381,7 +381,7 @@ class _Batch:
         starts = [0]
         for c in new:
             starts.append(starts[-1] + c)
-        self.q_start_host, self.n_seqs, self.max_seq_len = starts, len(lengths), max(lengths)
+        self.q_start_host, self.n_seqs, self.max_seq_len, self.max_q_len = starts, len(lengths), max(lengths), max(new)
         self.q_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
         pos, sidx = [], []
         for s, (n, c) in enumerate(zip(lengths, new)):
@@ -455,8 +455,35 @@ def test_attention_flash_rows_do_not_depend_on_the_batch():
     q = torch.cat(qs).to(DEV).reshape(-1, nq * hd)
     out = torch.empty_like(q)
     ops().attention_flash(q, k_pool, v_pool, _Batch(lengths, new, status), table, page, out, nq, nkv, hd, 0, hd ** -0.5, ws, n_splits=1)
-    # the last 3 tokens of sequence 0 as a portion of their own
-    q2 = qs[0][-3:].to(DEV).reshape(-1, nq * hd)
+    # the last 7 tokens of sequence 0 as a portion of their own (the same arrangement of warps)
+    q2 = qs[0][-7:].to(DEV).reshape(-1, nq * hd)
     out2 = torch.empty_like(q2)
-    ops().attention_flash(q2, k_pool, v_pool, _Batch([150], [3], status), table[:1], page, out2, nq, nkv, hd, 0, hd ** -0.5, ws, n_splits=1)
-    assert torch.equal(out2, out[37:40])
+    ops().attention_flash(q2, k_pool, v_pool, _Batch([150], [7], status), table[:1], page, out2, nq, nkv, hd, 0, hd ** -0.5, ws, n_splits=1)
+    assert torch.equal(out2, out[33:40])
+
+
+@pytest.mark.parametrize("splits", [None, 1, 4])
+@pytest.mark.parametrize("nq, nkv, hd, page, window, new_len", [
+    (4, 2, 16, 16, 0, 1), (6, 2, 32, 8, 20, 1), (32, 8, 128, 64, 0, 1), (16, 1, 128, 16, 0, 1), (8, 2, 64, 4, 50, 4),
+    (5, 5, 96, 2, 0, 16), (64, 8, 128, 64, 0, 2)])
+def test_attention_flash_decoding_arrangement(nq, nkv, hd, page, window, new_len, splits):
+    """Every sequence brings so few tokens that a tile has at most 16 rows: the kernel then
+    spreads a tile's keys over its warps and combines them."""
+    from rust_mlx_b200.engine.workspace import Workspace
+    lengths = [200, 17, 33, 130, 700, 64, 65, 16]
+    new = [new_len] * len(lengths)
+    k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, torch.bfloat16, seed=hd + nq)
+    qs = [torch.randn(c, nq, hd).to(torch.bfloat16) for c in new]
+    q = torch.cat(qs).to(DEV).reshape(-1, nq * hd)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    batch = _Batch(lengths, new, status)
+    out = torch.full_like(q, float("nan"))
+    ops().attention_flash(q, k_pool, v_pool, batch, table, page, out, nq, nkv, hd, window, hd ** -0.5, Workspace(DEV), n_splits=splits)
+    assert status.item() == 0
+    at = 0
+    for s, (n, c) in enumerate(zip(lengths, new)):
+        want = plain_attention(qs[s], ks[s], vs[s], torch.arange(n - c, n), window, hd ** -0.5)
+        got = out[at:at + c].double().cpu().reshape(c, nq, hd)
+        assert not torch.isnan(got).any()
+        assert (got - want).abs().max().item() < 1e-2, (s, n, c)
+        at += c
