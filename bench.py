@@ -200,7 +200,8 @@ def time_e2e(engine, batch, new_tokens):
     import torch
     g = torch.Generator().manual_seed(7)
     prompts = torch.randint(0, engine.vocab_size, (batch, CONTEXT), generator=g).tolist()
-    engine.generate(prompts[:1], max_tokens=2, ignore_eos=True, prefill_chunk=512)      # warm-up
+    # warm-up with the same shapes: the decode step of this batch size is captured into its graph here
+    engine.generate(prompts, max_tokens=3, ignore_eos=True, prefill_chunk=2048, max_batch_tokens=2048 + batch)
     r = engine.generate_detailed(prompts, max_tokens=new_tokens, ignore_eos=True, prefill_chunk=2048,
                                  max_batch_tokens=2048 + batch)
     decoded = r.generated_tokens - batch

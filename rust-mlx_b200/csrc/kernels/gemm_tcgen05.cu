@@ -1,0 +1,356 @@
+// bfloat16 matrix product on the Blackwell tensor cores for few rows (decoding):
+//   C[M, N] = A[M, K] . W[N, K]^T,  M <= 64 rows of activations against a large weight.
+//
+// With so few rows the product is bound by reading W once.  The kernel swaps the roles of
+// the operands so that the weight fills the 128-row side of the tensor-core instruction:
+//   D[128 weight rows, MPAD tokens] += Wtile[128, 64] . Atile[MPAD, 64]^T     (tcgen05.mma, kind::f16)
+// A block owns one tile of 128 weight rows (and, with split-K, one slice of K).  One thread
+// streams W and A tiles of 64 k into a ring of shared-memory stages with TMA (128-byte
+// swizzle); one thread issues the MMAs, whose accumulator lives in tensor memory; when
+// the last MMA has completed, the four warps read the accumulator (tcgen05.ld, one weight
+// row per thread) and write C, coalesced over the weight rows.  With split-K the slices
+// leave float partial sums in a scratch buffer and the last block to finish a tile adds
+// them in slice order (a counter per tile says who is last), so the result does not
+// depend on the order in which blocks run.
+//
+// Every wait on a barrier gives up after a bounded number of polls, records an error in
+// the status word and lets the block run to its end (tensor memory is always freed).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+constexpr int TILE_N = 128;   // weight rows per block: the M side of the instruction
+constexpr int TILE_K = 64;    // 64 bfloat16 = 128 bytes: one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 128;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+// Polls until the phase with the given parity has completed; false if it gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_addr(smem)), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(map) : "memory");
+}
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, groups of
+// 8 rows 1024 bytes apart.  `addr` may be advanced by 32 bytes per UMMA_K step inside a swizzle row.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);      // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                      // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset: 8 rows * 128 bytes
+    d |= (uint64_t)1 << 46;                      // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                      // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
+}
+__device__ __forceinline__ void umma_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+}
+// Arrives on the barrier when all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+struct GemmParams {
+    void* c;                 // [M, ldc] bfloat16 or float
+    float* partial;          // [splits, MPAD, n_tiles * 128] floats (splits > 1)
+    unsigned int* counters;  // [n_tiles], zero between launches (splits > 1)
+    int* status;
+    int M, N, K, ldc, splits, k_blocks, out_float;
+};
+
+template <int MPAD, int STAGES>
+__global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                              const __grid_constant__ CUtensorMap map_a,
+                                                              const GemmParams p) {
+    constexpr int W_BYTES = TILE_N * TILE_K * 2, A_BYTES = MPAD * TILE_K * 2;
+    constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+    constexpr int TMEM_COLS = MPAD < 32 ? 32 : MPAD;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // tiles must sit on 1024-byte boundaries for the 128-byte swizzle
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int s_failed, s_last;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, split = blockIdx.y;
+    const int per_split = (p.k_blocks + p.splits - 1) / p.splits;
+    const int kb_begin = split * per_split, kb_end = min(p.k_blocks, kb_begin + per_split);
+    const int n_kb = max(0, kb_end - kb_begin);
+
+    if (tid == 0) {
+        s_failed = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_a);
+    }
+    if (warp == 1) {  // one warp allocates the accumulator's columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_smem)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_acc = tmem_base_smem;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: stream W and A tiles through the ring
+        for (int i = 0; i < n_kb; ++i) {
+            const int s = i % STAGES, round = i / STAGES;
+            if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) { atomicExch(&s_failed, 1); break; }
+            unsigned char* dst = tiles + s * STAGE_BYTES;
+            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            const int k0 = (kb_begin + i) * TILE_K;
+            tma_load_2d(dst, &map_w, &full_bar[s], k0, tile * TILE_N);
+            tma_load_2d(dst + W_BYTES, &map_a, &full_bar[s], k0, 0);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        const uint32_t idesc = umma_idesc(MPAD);
+        for (int i = 0; i < n_kb; ++i) {
+            const int s = i % STAGES, round = i / STAGES;
+            if (!mbar_wait(&full_bar[s], round & 1)) { atomicExch(&s_failed, 1); break; }
+            tcgen05_fence_after();
+            const uint32_t w_addr = smem_addr(tiles + s * STAGE_BYTES), a_addr = w_addr + W_BYTES;
+#pragma unroll
+            for (int k = 0; k < TILE_K / UMMA_K; ++k)
+                umma_mma(tmem_acc, umma_desc(w_addr + k * UMMA_K * 2), umma_desc(a_addr + k * UMMA_K * 2), idesc, i > 0 || k > 0);
+            umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
+        }
+        umma_commit(&acc_bar);            // the accumulator is complete once every MMA has finished
+    }
+    __syncwarp();
+
+    // ---- epilogue: every thread owns one weight row of the tile
+    bool ok = n_kb == 0 || mbar_wait(&acc_bar, 0);
+    if (!ok) atomicExch(&s_failed, 1);
+    tcgen05_fence_after();
+    const int n = tile * TILE_N + warp * 32 + lane;
+    float acc[MPAD];
+    if (n_kb > 0 && ok) {
+#pragma unroll
+        for (int c = 0; c < MPAD; c += 16) {
+            uint32_t r[16];
+            tmem_ld16(tmem_acc + ((uint32_t)(warp * 32) << 16) + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[c + j] = __uint_as_float(r[j]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < MPAD; ++j) acc[j] = 0.f;
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_acc), "r"(TMEM_COLS));
+    if (s_failed) {
+        if (tid == 0) atomicExch(p.status, 3);
+        return;
+    }
+
+    if (p.splits > 1) {
+        // leave this slice's sums, then the last block of the tile adds the slices in order
+        const size_t ldp = (size_t)gridDim.x * TILE_N;
+        float* mine = p.partial + (size_t)split * MPAD * ldp;
+#pragma unroll
+        for (int t = 0; t < MPAD; ++t)
+            if (t < p.M) mine[(size_t)t * ldp + n] = acc[t];
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_last = atomicAdd(&p.counters[tile], 1u) == (unsigned)p.splits - 1;
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+#pragma unroll
+        for (int t = 0; t < MPAD; ++t) acc[t] = 0.f;
+        for (int z = 0; z < p.splits; ++z) {
+            const float* src = p.partial + (size_t)z * MPAD * ldp;
+#pragma unroll
+            for (int t = 0; t < MPAD; ++t)
+                if (t < p.M) acc[t] += __ldcg(src + (size_t)t * ldp + n);
+        }
+        if (tid == 0) p.counters[tile] = 0;  // ready for the next launch
+    }
+    if (n < p.N) {
+        if (p.out_float) {
+            float* c = reinterpret_cast<float*>(p.c);
+#pragma unroll
+            for (int t = 0; t < MPAD; ++t)
+                if (t < p.M) c[(size_t)t * p.ldc + n] = acc[t];
+        } else {
+            __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.c);
+#pragma unroll
+            for (int t = 0; t < MPAD; ++t)
+                if (t < p.M) c[(size_t)t * p.ldc + n] = __float2bfloat16_rn(acc[t]);
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)ptr;
+    }
+    return fn;
+}
+
+// A [rows, cols] row-major bfloat16 matrix with leading dimension ld, copied in boxes of [box_rows, 64] with
+// the 128-byte swizzle; rows and columns outside the matrix read as zeros.
+struct MapKey {
+    const void* base;
+    int rows, cols, ld, box_rows;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.base);
+        for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ std::hash<int>()(v);
+        return h;
+    }
+};
+
+int encode_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows);
+
+// Tensor maps depend on the address and the shape only; weights keep theirs, so encoded maps are kept.
+int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+    static std::mutex lock;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{base, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> guard(lock);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *map = it->second;
+        return 0;
+    }
+    if (encode_map(map, base, rows, cols, ld, box_rows) != 0) return -1;
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *map);
+    return 0;
+}
+
+int encode_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+    EncodeTiled fn = encode_tiled();
+    if (!fn) RMX_FAIL("gemm_tcgen05: the driver has no cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) RMX_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+template <int MPAD, int STAGES>
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int n_tiles, cudaStream_t s) {
+    constexpr size_t smem = (size_t)STAGES * (TILE_N * TILE_K * 2 + MPAD * TILE_K * 2) + 1024;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_swapab_kernel<MPAD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RMX_FAIL("gemm_tcgen05: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        raised = true;
+    }
+    gemm_swapab_kernel<MPAD, STAGES><<<dim3(n_tiles, p.splits), THREADS, smem, s>>>(mw, ma, p);
+    RMX_CHECK_LAUNCH("gemm_tcgen05");
+    return 0;
+}
+}  // namespace
+
+// What the kernel takes: up to 64 rows, K a multiple of 8 (TMA rows are 16-byte multiples), 16-byte aligned bases.
+RMX_API int rmx_gemm_tcgen05_supports(int M, int N, int K) { return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0; }
+
+// Scratch for split-K: floats for partial sums and one counter per tile of 128 weight rows.
+RMX_API long long rmx_gemm_tcgen05_scratch_floats(int M, int N, int splits) {
+    const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    return splits <= 1 ? 0 : (long long)splits * mpad * ((N + TILE_N - 1) / TILE_N) * TILE_N;
+}
+
+// C[M, N] = A[M, K] . W[N, K]^T.  out_float: C is float (logits), else bfloat16.  With splits > 1, `partial` holds
+// rmx_gemm_tcgen05_scratch_floats floats and `counters` ceil(N / 128) zeroed unsigned ints (left zero again).
+RMX_API int rmx_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
+                             int out_float, int splits, float* partial, unsigned int* counters, int* status,
+                             void* stream) {
+    if (M == 0 || N == 0) return 0;
+    RMX_REQUIRE(rmx_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05: M=%d N=%d K=%d is outside 1..64 rows, K %% 8 == 0", M, N, K);
+    RMX_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0,
+                "gemm_tcgen05: operands must be 16-byte aligned with leading dimensions that are multiples of 8");
+    const int k_blocks = (K + TILE_K - 1) / TILE_K;
+    RMX_REQUIRE(splits >= 1 && splits <= k_blocks && splits <= 65535, "gemm_tcgen05: %d splits for %d k-blocks", splits, k_blocks);
+    RMX_REQUIRE(splits == 1 || (partial && counters), "gemm_tcgen05: split-K needs scratch");
+    const int n_tiles = (N + TILE_N - 1) / TILE_N;
+    const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    CUtensorMap mw, ma;
+    if (make_map(&mw, W, N, K, ldw, TILE_N) != 0) return -1;
+    if (make_map(&ma, A, M, K, lda, mpad) != 0) return -1;
+    GemmParams p;
+    p.c = C; p.partial = partial; p.counters = counters; p.status = status;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
+    cudaStream_t s = (cudaStream_t)stream;
+    // stages sized so that two blocks fit an SM: more blocks in flight smooth the last wave
+    if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s);
+    if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s);
+    return launch<64, 4>(mw, ma, p, n_tiles, s);
+}

@@ -189,7 +189,7 @@ class Engine:
         if batch.n_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         x = spec.final_norm.forward_rows(h, pending, batch.logit_rows)
-        return spec.head.forward(x)
+        return spec.head.forward(x, batch)
 
     def generate(self, prompts: list, **options):
         """Token ids in, token ids out: see ``engine.generate.generate``.  Returns the list of
@@ -207,5 +207,6 @@ class Engine:
         if code != 0:
             self._status.zero_()
             what = {1: "a key was to be written to a position without a page",
-                    2: "a key was to be read from a position without a page"}.get(code, f"code {code}")
+                    2: "a key was to be read from a position without a page",
+                    3: "a matrix product gave up waiting for its own copies or tensor-core operations"}.get(code, f"code {code}")
             raise EngineError(f"a kernel refused its input: {what}")

@@ -31,6 +31,21 @@ class Workspace:
             self.buffers[key] = buf
         return buf[:numel].view(shape)
 
+    def get_zeroed(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        """Like ``get``, but the buffer is zero when it is first made (or made again, larger);
+        whoever uses it leaves it zero."""
+        numel = math.prod(shape)
+        key = (name, dtype)
+        buf = self.buffers.get(key)
+        if buf is None or buf.numel() < numel:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name} would have to grow to {numel} while frozen")
+            if buf is not None:
+                self.generation += 1
+            buf = torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
+            self.buffers[key] = buf
+        return buf[:numel].view(shape)
+
     def reserve(self, name: str, shape: tuple, dtype: torch.dtype) -> None:
         self.get(name, shape, dtype)
 

@@ -28,6 +28,7 @@ def kernels_library() -> ctypes.CDLL:
         path = _build_module().build_kernels()
         lib = ctypes.CDLL(path)
         lib.rmx_last_error.restype = ctypes.c_char_p
+        lib.rmx_gemm_tcgen05_scratch_floats.restype = ctypes.c_longlong
         _kernels = lib
     return _kernels
 

@@ -152,17 +152,29 @@ def sample(logits, temperature, uniform, out):
 # Dispatch: which kernel serves a call.  float32 always takes the plain kernels (fixed
 # order of summation, no tensor cores); bfloat16 takes the fast ones where they apply.
 
-def linear(x, w, out):
+def linear(x, w, out, workspace=None, status=None):
     """out = x . w^T.  w is [out_features, in_features] as stored in the checkpoint."""
     if x.dtype == torch.float32:
         gemm_plain(x, w, out)
     else:
-        linear_bf16(x, w, out)
+        linear_bf16(x, w, out, workspace, status)
 
 
-def linear_bf16(x, w, out):
+def prefers_tcgen05(m: int, n: int, k: int) -> bool:
+    """Where this package's tensor-core kernel is measured faster than the library's product:
+    few rows against a very large weight (the output head) or a long reduction (the
+    feed-forward's down projection)."""
+    if not tcgen05_supported(m, n, k):
+        return False
+    return n * k >= (1 << 28) or (k >= 8192 and m <= 32)
+
+
+def linear_bf16(x, w, out, workspace=None, status=None):
     """bfloat16 operands, float accumulation; the result in bfloat16 or (for logits) float32."""
-    if out.dtype == torch.bfloat16:
+    m, k = x.shape
+    if prefers_tcgen05(m, w.shape[0], k) and x.stride(1) == 1 and w.stride(1) == 1:
+        gemm_tcgen05(x, w, out, workspace, status)
+    elif out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
@@ -223,3 +235,66 @@ def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
         c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(n_splits),
         c_int(getattr(batch, "max_q_len", 0)), _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched(2 if n_splits > 1 else 1)
+
+
+_scratch = None
+
+
+def _own_workspace():
+    """Scratch for kernels called without an engine's workspace (tests, single calls)."""
+    global _scratch
+    if _scratch is None:
+        from ..engine.workspace import Workspace
+        _scratch = Workspace(torch.device("cuda", torch.cuda.current_device()))
+    return _scratch
+
+
+def tcgen05_supported(m: int, n: int, k: int) -> bool:
+    return bool(kernels_library().rmx_gemm_tcgen05_supports(c_int(m), c_int(n), c_int(k)))
+
+
+def tcgen05_splits(m: int, n: int, k: int) -> int:
+    """How many slices of K share a tile of 128 weight rows.  More slices fill the SMs' block
+    slots (two per SM) more evenly but leave float partial sums to be written and read again;
+    the choice minimises (weight bytes + partial bytes) / (share of slots busy), keeping at
+    least 8 k-blocks of 64 per slice."""
+    tiles = -(-n // 128)
+    k_blocks = -(-k // 64)
+    slots = 2 * _sm_count()
+    mpad = 16 if m <= 16 else (32 if m <= 32 else 64)
+    best, best_cost = 1, None
+    for s in range(1, max(1, k_blocks // 8) + 1):
+        blocks = tiles * s
+        eff = blocks / (-(-blocks // slots) * slots)
+        cost = (n * k * 2 + (s * mpad * n * 8 if s > 1 else 0)) / eff
+        if best_cost is None or cost < best_cost * 0.97:
+            best, best_cost = s, cost
+    return best
+
+
+def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None):
+    """out[M, N] = a[M, K] . w[N, K]^T for M <= 64 on the tcgen05 tensor cores (bfloat16 in,
+    float accumulation, bfloat16 or float out)."""
+    lib = kernels_library()
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_tcgen05: {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} of {a.dtype}")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_tcgen05: the result is bfloat16 or float32")
+    ws = workspace if workspace is not None else _own_workspace()
+    if splits is None:
+        splits = tcgen05_splits(m, n, k)
+    partial = counters = None
+    if splits > 1:
+        need = lib.rmx_gemm_tcgen05_scratch_floats(c_int(m), c_int(n), c_int(splits))
+        partial = ws.get("gemm_partial", (need,), torch.float32)
+        counters = ws.get_zeroed("gemm_counters", (max(4096, -(-n // 128)),), torch.int32)
+    if status is None:
+        status = ws.get_zeroed("gemm_status", (1,), torch.int32)
+    check(lib.rmx_gemm_tcgen05(
+        _ptr(a, name="a"), _ptr(w, name="w"), _ptr(out, name="out"), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
+        c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0), c_int(splits),
+        _ptr(partial), _ptr(counters), _ptr(status, torch.int32, "status"), _stream()))
+    _launched()
+    return status

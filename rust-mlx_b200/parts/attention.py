@@ -61,7 +61,7 @@ class AttentionMixer(Mixer):
         n = x.shape[0]
         nq, nkv, hd = self.heads, self.kv_heads, self.head_dim
         qkv = ws.get("qkv", (n, (nq + 2 * nkv) * hd), dt)
-        ops.linear(x, self.w_qkv, qkv)
+        ops.linear(x, self.w_qkv, qkv, ws, batch.status)
         q = ws.get("q_rot", (n, nq * hd), dt)
         ops.qk_rope_cache(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.position.inv_freq,
                           self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
@@ -71,5 +71,5 @@ class AttentionMixer(Mixer):
         ops.attention(q, cache.k_pool, cache.v_pool, batch, cache.block_table, cache.page_size, o, nq, nkv, hd,
                       cache.window, self.scale, ws)
         y = ws.get("mixer_out", (n, self.width), dt)
-        ops.linear(o, self.w_o, y)
+        ops.linear(o, self.w_o, y, ws, batch.status)
         return y

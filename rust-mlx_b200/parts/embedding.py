@@ -49,7 +49,7 @@ class OutputHead(Part):
         super().bind(tensors, ctx)
         self.weight = self.tied_to.weight if self.name is None else tensors[self.name].contiguous()
 
-    def forward(self, x):
+    def forward(self, x, batch=None):
         logits = self.ctx.workspace.get("logits", (x.shape[0], self.vocab), torch.float32)
-        self.ctx.ops.linear(x, self.weight, logits)
+        self.ctx.ops.linear(x, self.weight, logits, self.ctx.workspace, batch.status if batch is not None else None)
         return logits

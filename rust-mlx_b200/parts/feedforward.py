@@ -35,9 +35,9 @@ class SwiGLUFeedForward(FeedForward):
         ops, ws, dt = self.ctx.ops, self.ctx.workspace, self.ctx.dtype
         n = x.shape[0]
         gu = ws.get("gate_up", (n, 2 * self.inner), dt)
-        ops.linear(x, self.w_gate_up, gu)
+        ops.linear(x, self.w_gate_up, gu, ws, batch.status if batch is not None else None)
         act = ws.get("ffn_act", (n, self.inner), dt)
         ops.swiglu(gu, act)
         y = ws.get("ffn_out", (n, self.width), dt)
-        ops.linear(act, self.w_down, y)
+        ops.linear(act, self.w_down, y, ws, batch.status if batch is not None else None)
         return y

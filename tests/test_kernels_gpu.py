@@ -487,3 +487,45 @@ def test_attention_flash_decoding_arrangement(nq, nkv, hd, page, window, new_len
         assert not torch.isnan(got).any()
         assert (got - want).abs().max().item() < 1e-2, (s, n, c)
         at += c
+
+
+@pytest.mark.parametrize("m, n, k, splits", [
+    (1, 128, 64, 1), (16, 128, 128, 1), (1, 6144, 4096, None), (8, 4096, 4096, 4), (8, 24576, 4096, None),
+    (3, 509, 96, 1), (17, 1000, 136, 2), (33, 4096, 12288, None), (64, 2048, 4096, 1), (64, 1100, 520, 3),
+    (5, 130, 8, 1), (40, 96, 264, 1)])
+def test_gemm_tcgen05(m, n, k, splits):
+    """The tcgen05/TMA product for few rows: sizes that are no multiple of the 128-row tile
+    or the 64-wide k block, with and without split-K, bfloat16 and float results."""
+    a, w = rnd((m, k), torch.bfloat16, 1.0, 1), rnd((n, k), torch.bfloat16, 0.05, 2)
+    want = a.double() @ w.double().t()
+    for odt in (torch.float32, torch.bfloat16):
+        out = torch.full((m, n), float("nan"), dtype=odt, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops().gemm_tcgen05(a, w, out, status=status, splits=splits)
+        assert status.item() == 0
+        tol = 1e-2 if odt == torch.bfloat16 else 1e-4
+        assert ((out.double() - want).abs() <= tol * (1 + want.abs())).all()
+    # split-K leaves its counters at zero: a second call gives the same bits
+    out2 = torch.empty_like(out)
+    ops().gemm_tcgen05(a, w, out2, status=status, splits=splits)
+    assert torch.equal(out, out2)
+
+
+def test_gemm_tcgen05_rows_do_not_depend_on_the_batch():
+    a, w = rnd((8, 4096), torch.bfloat16, 1.0, 1), rnd((1024, 4096), torch.bfloat16, 0.05, 2)
+    out8 = torch.empty(8, 1024, device=DEV)
+    out1 = torch.empty(1, 1024, device=DEV)
+    ops().gemm_tcgen05(a, w, out8, splits=2)
+    ops().gemm_tcgen05(a[3:4].contiguous(), w, out1, splits=2)
+    assert torch.equal(out8[3], out1[0])
+
+
+def test_gemm_tcgen05_refuses_what_it_cannot_do():
+    from rust_mlx_b200.kernels.library import KernelError
+    a, w = rnd((65, 64), torch.bfloat16), rnd((128, 64), torch.bfloat16)
+    with pytest.raises(KernelError, match="1..64 rows"):
+        ops().gemm_tcgen05(a, w, torch.empty(65, 128, dtype=torch.bfloat16, device=DEV))
+    a, w = rnd((4, 60), torch.bfloat16), rnd((128, 60), torch.bfloat16)
+    with pytest.raises(KernelError, match="K % 8"):
+        ops().gemm_tcgen05(a, w, torch.empty(4, 128, dtype=torch.bfloat16, device=DEV))
+    assert not ops().prefers_tcgen05(4, 128, 60)
