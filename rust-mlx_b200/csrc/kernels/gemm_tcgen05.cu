@@ -354,3 +354,98 @@ RMX_API int rmx_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N
     if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s);
     return launch<64, 4>(mw, ma, p, n_tiles, s);
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same product for callers that cannot allocate: scratch in the library's own memory.
+// See rmx_no_alloc.h for who needs this and what it promises.
+#include "rmx_no_alloc.h"
+
+namespace {
+// File-scope device memory: loaded with the library on every GPU that uses it and kept until exit.
+static __device__ __align__(256) float g_static_partial[RMX_STATIC_SCRATCH_FLOATS];
+static __device__ __align__(256) unsigned int g_static_counters[RMX_STATIC_SCRATCH_TILES];
+static __device__ __align__(256) int g_static_status[64];
+
+constexpr int MAX_DEVICES = 64;
+struct StaticScratch {
+    float* partial = nullptr;
+    unsigned int* counters = nullptr;
+    int* status = nullptr;
+};
+StaticScratch g_scratch[MAX_DEVICES];
+std::mutex g_scratch_lock;
+
+// In host code the arrays' names stand for the symbols, not for device addresses: ask the runtime for
+// the addresses once per device, with that device current.
+int static_scratch(StaticScratch* out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) RMX_FAIL("gemm_tcgen05_static: no current device: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= MAX_DEVICES) RMX_FAIL("gemm_tcgen05_static: device %d is beyond %d", dev, MAX_DEVICES);
+    std::lock_guard<std::mutex> guard(g_scratch_lock);
+    StaticScratch& s = g_scratch[dev];
+    if (!s.partial) {
+        void *p = nullptr, *c = nullptr, *st = nullptr;
+        if ((e = cudaGetSymbolAddress(&p, g_static_partial)) != cudaSuccess ||
+            (e = cudaGetSymbolAddress(&c, g_static_counters)) != cudaSuccess ||
+            (e = cudaGetSymbolAddress(&st, g_static_status)) != cudaSuccess)
+            RMX_FAIL("gemm_tcgen05_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        s.partial = (float*)p;
+        s.counters = (unsigned int*)c;
+        s.status = (int*)st;
+    }
+    *out = s;
+    return 0;
+}
+}  // namespace
+
+RMX_API int rmx_gemm_tcgen05_static(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw,
+                                    int ldc, int out_float, int splits, void* stream) {
+    if (M == 0 || N == 0) return 0;
+    RMX_REQUIRE(rmx_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05_static: M=%d N=%d K=%d is outside 1..64 rows, K %% 8 == 0", M, N, K);
+    RMX_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0,
+                "gemm_tcgen05_static: operands must be 16-byte aligned with leading dimensions that are multiples of 8");
+    const int k_blocks = (K + TILE_K - 1) / TILE_K;
+    const int n_tiles = (N + TILE_N - 1) / TILE_N;
+    RMX_REQUIRE(n_tiles <= RMX_STATIC_SCRATCH_TILES, "gemm_tcgen05_static: N=%d is beyond the %d rows the library's scratch covers",
+                N, RMX_STATIC_SCRATCH_TILES * TILE_N);
+    const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    if (splits <= 0) {  // as many slices as fit the scratch, up to one block per SM slot, at least 8 k-blocks each
+        const long long room = RMX_STATIC_SCRATCH_FLOATS / ((long long)mpad * n_tiles * TILE_N);
+        long long pick = room;
+        if (pick > k_blocks / 8) pick = k_blocks / 8;
+        if (pick > 296 / n_tiles) pick = 296 / n_tiles;
+        splits = pick < 1 ? 1 : (int)pick;
+    }
+    RMX_REQUIRE(splits >= 1 && splits <= k_blocks && splits <= 65535, "gemm_tcgen05_static: %d splits for %d k-blocks", splits, k_blocks);
+    const long long need = splits <= 1 ? 0 : rmx_gemm_tcgen05_scratch_floats(M, N, splits);
+    RMX_REQUIRE(need <= RMX_STATIC_SCRATCH_FLOATS,
+                "gemm_tcgen05_static: %d splits of M=%d N=%d need %lld floats of scratch, the library holds %d; use fewer splits",
+                splits, M, N, need, RMX_STATIC_SCRATCH_FLOATS);
+    StaticScratch scratch;
+    if (static_scratch(&scratch) != 0) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    // what must start at zero: the tiles' counters (a call that was cut short may have left some set) and the status word
+    cudaError_t e = cudaMemsetAsync(scratch.counters, 0, sizeof(unsigned int) * n_tiles, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(scratch.status, 0, sizeof(int), s);
+    if (e != cudaSuccess) RMX_FAIL("gemm_tcgen05_static: clearing the scratch failed: %s", cudaGetErrorString(e));
+    CUtensorMap mw, ma;
+    if (encode_map(&mw, W, N, K, ldw, TILE_N) != 0) return -1;
+    if (encode_map(&ma, A, M, K, lda, mpad) != 0) return -1;
+    GemmParams p;
+    p.c = C; p.partial = scratch.partial; p.counters = scratch.counters; p.status = scratch.status;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
+    if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s);
+    if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s);
+    return launch<64, 4>(mw, ma, p, n_tiles, s);
+}
+
+RMX_API int rmx_gemm_tcgen05_static_status(void* stream) {
+    StaticScratch scratch;
+    if (static_scratch(&scratch) != 0) return -1;
+    int host = 0;
+    cudaError_t e = cudaMemcpyAsync(&host, scratch.status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) RMX_FAIL("gemm_tcgen05_static_status: %s", cudaGetErrorString(e));
+    return host;
+}
