@@ -201,13 +201,13 @@ def time_e2e(engine, batch, new_tokens):
     g = torch.Generator().manual_seed(7)
     prompts = torch.randint(0, engine.vocab_size, (batch, CONTEXT), generator=g).tolist()
     # warm-up with the same shapes: the decode step of this batch size is captured into its graph here
-    engine.generate(prompts, max_tokens=3, ignore_eos=True, prefill_chunk=2048, max_batch_tokens=2048 + batch)
+    engine.generate(prompts, max_tokens=3, ignore_eos=True, prefill_chunk=2048, max_batch_tokens=batch * CONTEXT)
     r = engine.generate_detailed(prompts, max_tokens=new_tokens, ignore_eos=True, prefill_chunk=2048,
-                                 max_batch_tokens=2048 + batch)
+                                 max_batch_tokens=batch * CONTEXT)
     decoded = r.generated_tokens - batch
     # bytes per decode step: ids, positions, sequence indices, starts, lengths, slots, rows, block tables up; tokens + status down
-    entries = -(-(CONTEXT + new_tokens) // PAGE)
-    h2d = 4 * (3 * batch + (batch + 1) + 3 * batch + batch * entries)
+    entries = MAX_CONTEXT // PAGE   # a captured decode step carries block tables of the context limit
+    h2d = 4 * (3 * batch + (batch + 1) + 5 * batch + batch * entries)
     d2h = 4 * (batch + 1)
     return decoded / r.decode_seconds, h2d, d2h
 

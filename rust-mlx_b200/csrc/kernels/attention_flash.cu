@@ -60,21 +60,23 @@ struct FlashParams {
     float* part_o;                 // [splits, tokens * nq, HD]   (splits > 1)
     float* part_ml;                // [splits, tokens * nq, 2]
     int* status;
-    int n_seqs, n_tokens, nq, nkv, group, tq, table_stride, page_size, window, n_splits;
+    int n_seqs, n_tokens, nq, nkv, group, tq, table_stride, page_size, page_shift, window, n_splits;
     float scale_log2;
 };
 
 template <int HD, bool KEYSPLIT>
 __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashParams p) {
     constexpr int NT = KEYSPLIT ? 2 : BN / 8;   // score tiles of 8 keys per warp and key tile
+    constexpr int QROWS = KEYSPLIT ? 16 : BM;   // query rows kept in shared memory
+    constexpr int STAGES = KEYSPLIT ? 3 : 2;    // key tiles in the ring: decoding is bound by loads in flight
     constexpr int STRIDE = HD + 8;          // 16 bytes of padding: ldmatrix rows fall into different banks
     constexpr int CHUNKS = HD / 8;          // 16-byte chunks per row
     constexpr int KSTEPS = HD / 16;
     constexpr int DTILES = HD / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BM][STRIDE]
-    __nv_bfloat16* Ks = Qs + BM * STRIDE;                             // [2][BN][STRIDE]
-    __nv_bfloat16* Vs = Ks + 2 * BN * STRIDE;                         // [2][BN][STRIDE]
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [QROWS][STRIDE]
+    __nv_bfloat16* Ks = Qs + QROWS * STRIDE;                          // [STAGES][BN][STRIDE]
+    __nv_bfloat16* Vs = Ks + STAGES * BN * STRIDE;                    // [STAGES][BN][STRIDE]
     __shared__ int s_tile[3];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
     const int kt_end = min(kt_hi + 1, kt_begin + per_split);
 
     // ---- Q tile to shared memory (rows beyond the tile are zeros)
-    for (int idx = tid; idx < BM * CHUNKS; idx += THREADS) {
+    for (int idx = tid; idx < QROWS * CHUNKS; idx += THREADS) {
         const int r = idx / CHUNKS, c = idx - r * CHUNKS;
         const bool valid = r < rows_valid;
         const int tok = valid ? r / p.group : 0, g = valid ? r - tok * p.group : 0;
@@ -145,6 +147,9 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
     }
     cp_async_commit();
 
+    const int page_mask = p.page_size - 1;
+    const size_t head_off = (size_t)kvh * p.page_size * HD;
+    const size_t page_elems = (size_t)p.nkv * p.page_size * HD;
     auto load_kv = [&](int kt, int stage) {
         __nv_bfloat16* kd = Ks + stage * BN * STRIDE;
         __nv_bfloat16* vd = Vs + stage * BN * STRIDE;
@@ -154,12 +159,12 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
             bool valid = kp >= lo_first && kp <= pos_last;
             size_t off = 0;
             if (valid) {
-                const int page = table[kp / p.page_size];
+                const int page = table[kp >> p.page_shift];
                 if (page < 0) {
                     valid = false;
                     if (c == 0) atomicExch(p.status, 2);
                 } else {
-                    off = (((size_t)page * p.nkv + kvh) * p.page_size + kp % p.page_size) * HD + c * 8;
+                    off = (size_t)page * page_elems + head_off + (size_t)((kp & page_mask) * HD + c * 8);
                 }
             }
             cp_async16(kd + j * STRIDE + c * 8, p.k_pool + off, valid);
@@ -167,8 +172,11 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
         }
     };
 
-    if (kt_begin < kt_end) load_kv(kt_begin, 0);
-    cp_async_commit();
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (kt_begin + st < kt_end) load_kv(kt_begin + st, st);
+        cp_async_commit();
+    }
 
     // ---- this warp's rows
     const int row_base = KEYSPLIT ? 0 : warp * 16;
@@ -185,7 +193,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
         row_lo[i] = p.window > 0 ? max(0, row_pos[i] - p.window + 1) : 0;
     }
 
-    cp_async_wait<1>();  // Q has landed
+    cp_async_wait<STAGES - 1>();  // Q has landed (the oldest group)
     __syncthreads();
     uint32_t qf[KSTEPS][4];
 #pragma unroll
@@ -198,10 +206,10 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     for (int kt = kt_begin; kt < kt_end; ++kt) {
-        const int stage = (kt - kt_begin) & 1;
-        if (kt + 1 < kt_end) load_kv(kt + 1, stage ^ 1);
+        const int stage = (kt - kt_begin) % STAGES;
+        if (kt + STAGES - 1 < kt_end) load_kv(kt + STAGES - 1, (kt - kt_begin + STAGES - 1) % STAGES);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<STAGES - 1>();
         __syncthreads();
         if (warp_active) {
             const __nv_bfloat16* kbase = Ks + stage * BN * STRIDE;
@@ -282,6 +290,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
         __syncthreads();  // the stage is free for the load after next
     }
     cp_async_wait<0>();
+    allow_dependents();   // what follows may start fetching its weights while the results are written
 
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -368,6 +377,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
 // out[row] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the splits, in split order.
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        __nv_bfloat16* __restrict__ out, int rows, int hd, int n_splits) {
+    allow_dependents();
     const int row = blockIdx.x;
     float M = -INFINITY;
     for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((size_t)z * rows + row) * 2]);
@@ -389,8 +399,9 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 
 template <int HD, bool KEYSPLIT>
 int launch_flash_as(const FlashParams& p, int n_tiles, cudaStream_t s) {
-    constexpr size_t tiles = (size_t)(BM + 4 * BN) * (HD + 8) * sizeof(__nv_bfloat16);
-    constexpr size_t merge = (size_t)BM * (HD + 8) * sizeof(__nv_bfloat16) + (size_t)NWARPS * 16 * (HD + 2) * sizeof(float);
+    constexpr int QROWS = KEYSPLIT ? 16 : BM, STAGES = KEYSPLIT ? 3 : 2;
+    constexpr size_t tiles = (size_t)(QROWS + 2 * STAGES * BN) * (HD + 8) * sizeof(__nv_bfloat16);
+    constexpr size_t merge = (size_t)QROWS * (HD + 8) * sizeof(__nv_bfloat16) + (size_t)NWARPS * 16 * (HD + 2) * sizeof(float);
     constexpr size_t smem = tiles > merge ? tiles : merge;
     static bool raised = false;  // per instantiation: the attribute is set once
     if (smem > 48 * 1024 && !raised) {
@@ -429,6 +440,7 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     const int group = nq / nkv;
     RMX_REQUIRE(rmx_attention_flash_supports(hd, group), "attention_flash: head_dim %d with group %d is not built", hd, group);
     RMX_REQUIRE(page_size > 0 && table_stride > 0 && window >= 0 && n_tiles > 0 && n_seqs > 0, "attention_flash: bad geometry");
+    RMX_REQUIRE((page_size & (page_size - 1)) == 0, "attention_flash: page size %d is no power of two", page_size);
     RMX_REQUIRE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attention_flash: bad grid");
     RMX_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_flash: splits need partial buffers");
     FlashParams p;
@@ -437,6 +449,8 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     p.part_o = part_o; p.part_ml = part_ml; p.status = status;
     p.n_seqs = n_seqs; p.n_tokens = n_tokens; p.nq = nq; p.nkv = nkv; p.group = group; p.tq = BM / group;
     p.table_stride = table_stride; p.page_size = page_size; p.window = window; p.n_splits = n_splits;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2 = scale * LOG2E;
     cudaStream_t s = (cudaStream_t)stream;
     // every tile has at most 16 rows (decoding, or very short portions): spread keys over the warps

@@ -58,3 +58,8 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     for (int w = 0; w < nwarps; ++w) total += scratch[w];
     return total;
 }
+
+// Programmatic dependent launch: a kernel that is launched as a dependent of the one before it may start
+// (and do what does not need that kernel's results, such as fetching weights) once every block of that
+// kernel has called this or has ended.  It has no effect when the next kernel is launched the usual way.
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }

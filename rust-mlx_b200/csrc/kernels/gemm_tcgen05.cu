@@ -103,9 +103,27 @@ struct GemmParams {
     unsigned int* counters;  // [n_tiles], zero between launches (splits > 1)
     int* status;
     int M, N, K, ldc, splits, k_blocks, out_float;
+    int dependent;           // launched as a programmatic dependent: wait for the grid before before reading A
 };
 
-template <int MPAD, int STAGES>
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// Store a float into the shared memory of another block of the cluster, at the place that `local` has here.
+__device__ __forceinline__ void st_cluster(float* local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(remote), "f"(v) : "memory");
+}
+
+// CLUSTER: the slices of K of one tile form a thread-block cluster (grid.y == cluster size == splits); they
+// hand their partial sums to the first block through distributed shared memory, no global scratch.
+template <int MPAD, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_constant__ CUtensorMap map_w,
                                                               const __grid_constant__ CUtensorMap map_a,
                                                               const GemmParams p) {
@@ -135,6 +153,8 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         prefetch_tensormap(&map_w);
         prefetch_tensormap(&map_a);
+        // the kernels that follow may be launched now: they wait for this grid before they read its output
+        asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     }
     if (warp == 1) {  // one warp allocates the accumulator's columns of tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_smem)), "r"(TMEM_COLS));
@@ -146,10 +166,19 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
     const uint32_t tmem_acc = tmem_base_smem;
 
     if (warp == 0 && lane == 0) {
-        // ---- producer: stream W and A tiles through the ring
-        for (int i = 0; i < n_kb; ++i) {
+        // ---- producer: stream W and A tiles through the ring.  The weights do not depend on the kernel
+        // before this one, so the first stages' W tiles are on their way before the wait for that kernel.
+        const int ahead = n_kb < STAGES ? n_kb : STAGES;
+        for (int i = 0; i < ahead; ++i) {
+            mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+            tma_load_2d(tiles + i * STAGE_BYTES, &map_w, &full_bar[i], (kb_begin + i) * TILE_K, tile * TILE_N);
+        }
+        if (p.dependent) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        for (int i = 0; i < ahead; ++i)
+            tma_load_2d(tiles + i * STAGE_BYTES + W_BYTES, &map_a, &full_bar[i], (kb_begin + i) * TILE_K, 0);
+        for (int i = ahead; i < n_kb; ++i) {
             const int s = i % STAGES, round = i / STAGES;
-            if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) { atomicExch(&s_failed, 1); break; }
+            if (!mbar_wait(&empty_bar[s], (round - 1) & 1)) { atomicExch(&s_failed, 1); break; }
             unsigned char* dst = tiles + s * STAGE_BYTES;
             mbar_expect_tx(&full_bar[s], STAGE_BYTES);
             const int k0 = (kb_begin + i) * TILE_K;
@@ -195,12 +224,29 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_acc), "r"(TMEM_COLS));
-    if (s_failed) {
-        if (tid == 0) atomicExch(p.status, 3);
-        return;
-    }
+    const bool failed = s_failed != 0;
+    if (failed && tid == 0) atomicExch(p.status, 3);
+    if (!CLUSTER && failed) return;   // (inside a cluster a block that failed still joins the barriers below)
 
-    if (p.splits > 1) {
+    if constexpr (CLUSTER) {
+        // every block's MMAs are done (its shared-memory stages are free); the slices hand their sums to the
+        // first block of the cluster, which adds them in slice order
+        float* slots = reinterpret_cast<float*>(tiles);   // [splits - 1][MPAD][128] in the first block
+        const uint32_t rank = cluster_ctarank();
+        cluster_sync();
+        if (rank != 0) {
+#pragma unroll
+            for (int t = 0; t < MPAD; ++t)
+                if (t < p.M) st_cluster(slots + ((rank - 1) * MPAD + t) * TILE_N + tid, 0, acc[t]);
+        }
+        cluster_sync();
+        if (rank != 0 || failed) return;
+        for (int z = 1; z < p.splits; ++z) {
+#pragma unroll
+            for (int t = 0; t < MPAD; ++t)
+                if (t < p.M) acc[t] += slots[((z - 1) * MPAD + t) * TILE_N + tid];
+        }
+    } else if (p.splits > 1) {
         // leave this slice's sums, then the last block of the tile adds the slices in order
         const size_t ldp = (size_t)gridDim.x * TILE_N;
         float* mine = p.partial + (size_t)split * MPAD * ldp;
@@ -304,18 +350,49 @@ int encode_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, i
     return 0;
 }
 
-template <int MPAD, int STAGES>
-int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int n_tiles, cudaStream_t s) {
+template <int MPAD, int STAGES, bool CLUSTER>
+int launch_as(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int n_tiles, bool dependent, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * (TILE_N * TILE_K * 2 + MPAD * TILE_K * 2) + 1024;
     static bool raised = false;
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_swapab_kernel<MPAD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_swapab_kernel<MPAD, STAGES, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RMX_FAIL("gemm_tcgen05: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
-    gemm_swapab_kernel<MPAD, STAGES><<<dim3(n_tiles, p.splits), THREADS, smem, s>>>(mw, ma, p);
-    RMX_CHECK_LAUNCH("gemm_tcgen05");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles, p.splits);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attrs[2];
+    int n_attrs = 0;
+    if (CLUSTER) {
+        attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+        attrs[n_attrs].val.clusterDim.x = 1;
+        attrs[n_attrs].val.clusterDim.y = p.splits;
+        attrs[n_attrs].val.clusterDim.z = 1;
+        ++n_attrs;
+    }
+    if (dependent) {
+        attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attrs;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n_attrs;
+    GemmParams q = p;
+    q.dependent = dependent ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_swapab_kernel<MPAD, STAGES, CLUSTER>, mw, ma, q);
+    if (e != cudaSuccess) RMX_FAIL("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
     return 0;
+}
+
+// cluster: reduce split-K through distributed shared memory (2..8 slices whose sums fit the first block's stages)
+template <int MPAD, int STAGES>
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int n_tiles, cudaStream_t s,
+           bool cluster = false, bool dependent = false) {
+    if (cluster) return launch_as<MPAD, STAGES, true>(mw, ma, p, n_tiles, dependent, s);
+    return launch_as<MPAD, STAGES, false>(mw, ma, p, n_tiles, dependent, s);
 }
 }  // namespace
 
@@ -332,27 +409,33 @@ RMX_API long long rmx_gemm_tcgen05_scratch_floats(int M, int N, int splits) {
 // rmx_gemm_tcgen05_scratch_floats floats and `counters` ceil(N / 128) zeroed unsigned ints (left zero again).
 RMX_API int rmx_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
                              int out_float, int splits, float* partial, unsigned int* counters, int* status,
-                             void* stream) {
+                             int flags, void* stream) {
     if (M == 0 || N == 0) return 0;
     RMX_REQUIRE(rmx_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05: M=%d N=%d K=%d is outside 1..64 rows, K %% 8 == 0", M, N, K);
     RMX_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0,
                 "gemm_tcgen05: operands must be 16-byte aligned with leading dimensions that are multiples of 8");
     const int k_blocks = (K + TILE_K - 1) / TILE_K;
     RMX_REQUIRE(splits >= 1 && splits <= k_blocks && splits <= 65535, "gemm_tcgen05: %d splits for %d k-blocks", splits, k_blocks);
-    RMX_REQUIRE(splits == 1 || (partial && counters), "gemm_tcgen05: split-K needs scratch");
     const int n_tiles = (N + TILE_N - 1) / TILE_N;
     const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    // flags: 1 = reduce split-K inside a cluster when it can be (no scratch needed); 2 = programmatic dependent launch
+    const int stages = mpad == 64 ? 4 : 5;
+    const bool fits = (size_t)(splits - 1) * mpad * TILE_N * 4 <= (size_t)stages * (TILE_N * TILE_K * 2 + mpad * TILE_K * 2);
+    const bool cluster = (flags & 1) && splits >= 2 && splits <= 8 && fits;
+    const bool dependent = (flags & 2) != 0;
+    RMX_REQUIRE(splits == 1 || cluster || (partial && counters), "gemm_tcgen05: split-K needs scratch");
     CUtensorMap mw, ma;
     if (make_map(&mw, W, N, K, ldw, TILE_N) != 0) return -1;
     if (make_map(&ma, A, M, K, lda, mpad) != 0) return -1;
     GemmParams p;
     p.c = C; p.partial = partial; p.counters = counters; p.status = status;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
+    p.dependent = 0;
     cudaStream_t s = (cudaStream_t)stream;
     // stages sized so that two blocks fit an SM: more blocks in flight smooth the last wave
-    if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s);
-    if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s);
-    return launch<64, 4>(mw, ma, p, n_tiles, s);
+    if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s, cluster, dependent);
+    if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s, cluster, dependent);
+    return launch<64, 4>(mw, ma, p, n_tiles, s, cluster, dependent);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -435,6 +518,7 @@ RMX_API int rmx_gemm_tcgen05_static(const void* A, const void* W, void* C, int M
     GemmParams p;
     p.c = C; p.partial = scratch.partial; p.counters = scratch.counters; p.status = scratch.status;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
+    p.dependent = 0;
     if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s);
     if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s);
     return launch<64, 4>(mw, ma, p, n_tiles, s);

@@ -75,6 +75,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
                                    T* __restrict__ x, int width, int write_h) {
     __shared__ float scratch[32];
     extern __shared__ __align__(16) float vals[];
+    allow_dependents();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* hrow = h + (size_t)src * width;
@@ -158,6 +159,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 // four outputs per thread; inter is a multiple of 4
 template <typename T>
 __global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total4) {
+    allow_dependents();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total4) return;
     const int per_row = inter >> 2;

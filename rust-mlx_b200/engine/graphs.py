@@ -16,6 +16,19 @@ import torch
 from .batch import BatchLayout, check_sequences
 
 
+# Batch sizes that graphs exist for: a step of n sequences runs in the next size up, the spare
+# places repeating the first sequence (the same token to the same position: the same numbers
+# are written twice and the spare results are ignored).  At most half as many places again.
+_BUCKETS = [1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512]
+
+
+def bucket(n: int) -> int:
+    for b in _BUCKETS:
+        if n <= b:
+            return b
+    return n
+
+
 class _Captured:
     __slots__ = ("graph", "layout", "hosts", "events", "turn", "dev", "result", "generation", "batch")
 
@@ -34,9 +47,15 @@ class DecodeGraphs:
 
     def run(self, seqs: list, temperatures, uniforms) -> torch.Tensor:
         """One decode step of ``seqs`` (one token each).  Returns the device tensor
-        [status, token_0, ...]; the caller copies it to the host."""
+        [status, token_0, ...] (it may be longer than the batch: spare places follow the
+        real ones); the caller copies it to the host."""
         e = self.engine
         check_sequences(seqs)
+        spare = min(bucket(len(seqs)), e.pools.max_requests + len(seqs)) - len(seqs)
+        if spare > 0:
+            seqs = list(seqs) + [seqs[0]] * spare
+            temperatures = list(temperatures) + [0.0] * spare if temperatures is not None else None
+            uniforms = list(uniforms) + [0.0] * spare if uniforms is not None else None
         n = len(seqs)
         longest = max(s.start + 1 for s in seqs)
         if longest > e.max_context:

@@ -160,12 +160,19 @@ def linear(x, w, out, workspace=None, status=None):
         linear_bf16(x, w, out, workspace, status)
 
 
+# Which products of few rows take this package's tcgen05 kernel: "all" (every one it supports),
+# "measured" (only where it beats the library's product when each runs alone: the output head and
+# long reductions), "none".  Launched as programmatic dependents the kernel fetches weights while
+# the kernel before it ends, which the library's kernels do not.
+tcgen05_policy = "all"
+dependent_launch = True
+
+
 def prefers_tcgen05(m: int, n: int, k: int) -> bool:
-    """Where this package's tensor-core kernel is measured faster than the library's product:
-    few rows against a very large weight (the output head) or a long reduction (the
-    feed-forward's down projection)."""
-    if not tcgen05_supported(m, n, k):
+    if tcgen05_policy == "none" or not tcgen05_supported(m, n, k):
         return False
+    if tcgen05_policy == "all":
+        return True
     return n * k >= (1 << 28) or (k >= 8192 and m <= 32)
 
 
@@ -173,7 +180,7 @@ def linear_bf16(x, w, out, workspace=None, status=None):
     """bfloat16 operands, float accumulation; the result in bfloat16 or (for logits) float32."""
     m, k = x.shape
     if prefers_tcgen05(m, w.shape[0], k) and x.stride(1) == 1 and w.stride(1) == 1:
-        gemm_tcgen05(x, w, out, workspace, status)
+        gemm_tcgen05(x, w, out, workspace, status, dependent=dependent_launch)
     elif out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:
@@ -272,9 +279,12 @@ def tcgen05_splits(m: int, n: int, k: int) -> int:
     return best
 
 
-def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None):
+def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False):
     """out[M, N] = a[M, K] . w[N, K]^T for M <= 64 on the tcgen05 tensor cores (bfloat16 in,
-    float accumulation, bfloat16 or float out)."""
+    float accumulation, bfloat16 or float out).  ``cluster``: split-K slices of a tile form a
+    thread-block cluster and add their sums through distributed shared memory (up to 8 slices),
+    else through scratch in global memory.  ``dependent``: launch as a programmatic dependent of
+    the kernel before it on the stream, so that its weight loads start while that kernel ends."""
     lib = kernels_library()
     m, k = a.shape
     n = w.shape[0]
@@ -285,6 +295,8 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None):
     ws = workspace if workspace is not None else _own_workspace()
     if splits is None:
         splits = tcgen05_splits(m, n, k)
+        if cluster:
+            splits = min(splits, 8 if m <= 32 else 4)
     partial = counters = None
     if splits > 1:
         need = lib.rmx_gemm_tcgen05_scratch_floats(c_int(m), c_int(n), c_int(splits))
@@ -295,6 +307,7 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None):
     check(lib.rmx_gemm_tcgen05(
         _ptr(a, name="a"), _ptr(w, name="w"), _ptr(out, name="out"), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
         c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0), c_int(splits),
-        _ptr(partial), _ptr(counters), _ptr(status, torch.int32, "status"), _stream()))
+        _ptr(partial), _ptr(counters), _ptr(status, torch.int32, "status"),
+        c_int((1 if cluster else 0) | (2 if dependent else 0)), _stream()))
     _launched()
     return status
