@@ -109,6 +109,9 @@ class Engine:
         self.graphs = DecodeGraphs(self) if cuda_graphs and all(p.graph_safe for p in self.spec.all_parts()) else None
         self._req_ids = {}
         self._next_id = 0
+        if self.dtype == torch.bfloat16 and _ops.tcgen05_policy == "auto":
+            weights = [w for part in self.spec.all_parts() for w in part.linear_weights()]
+            _ops.autotune_linears(weights, self.workspace, log=_log if verbose else None)
         self.load_seconds = time.time() - t0
         if verbose:
             _log(f"model ready in {self.load_seconds:.1f}s: {len(self.spec.blocks)} layers, {self.dtype_name}, "

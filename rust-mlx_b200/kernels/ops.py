@@ -160,12 +160,19 @@ def linear(x, w, out, workspace=None, status=None):
         linear_bf16(x, w, out, workspace, status)
 
 
-# Which products of few rows take this package's tcgen05 kernel: "all" (every one it supports),
-# "measured" (only where it beats the library's product when each runs alone: the output head and
-# long reductions), "none".  Launched as programmatic dependents the kernel fetches weights while
-# the kernel before it ends, which the library's kernels do not.
-tcgen05_policy = "all"
+# Which products of few rows (up to 64) take this package's tcgen05 kernel rather than the library's
+# product: "auto" (whichever was faster when the engine timed both on the model's own weights, see
+# ``autotune_linears``; shapes that were not timed follow "measured"), "all" (every product the kernel
+# supports), "measured" (the output head and long reductions, where it won on Qwen3-8B shapes), "none".
+tcgen05_policy = "auto"
+# Launch the tcgen05 product as a programmatic dependent of the kernel before it, so that its weight
+# loads start while that kernel ends.
 dependent_launch = True
+_tuned = {}   # (n, k, padded rows) -> True if the tcgen05 kernel was faster
+
+
+def _mpad(m: int) -> int:
+    return 16 if m <= 16 else (32 if m <= 32 else 64)
 
 
 def prefers_tcgen05(m: int, n: int, k: int) -> bool:
@@ -173,7 +180,55 @@ def prefers_tcgen05(m: int, n: int, k: int) -> bool:
         return False
     if tcgen05_policy == "all":
         return True
+    if tcgen05_policy == "auto" and (n, k, _mpad(m)) in _tuned:
+        return _tuned[(n, k, _mpad(m))]
     return n * k >= (1 << 28) or (k >= 8192 and m <= 32)
+
+
+def _graph_time(fn, calls: int, reps: int = 3) -> float:
+    """Microseconds per call of ``fn(i)``, timed on the device inside a captured graph."""
+    fn(0)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(calls):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        g.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / reps / calls * 1e3
+
+
+def autotune_linears(weights: list, workspace=None, rows=(8, 32, 64), log=None) -> dict:
+    """Time the tcgen05 product against the library's on the model's own bfloat16 weights, per
+    shape and per padded row count, and remember the faster.  Weights of one shape take turns so
+    that none is served from L2 (a lone small weight would be: its timing then says little and
+    the rule of "measured" stands for it)."""
+    groups = {}
+    for w in weights:
+        if w is not None and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_cuda:
+            groups.setdefault((w.shape[0], w.shape[1]), []).append(w)
+    for (n, k), ws in groups.items():
+        if not tcgen05_supported(1, n, k) or len(ws) * n * k * 2 < 256e6:
+            continue
+        for m in rows:
+            key = (n, k, _mpad(m))
+            if key in _tuned:
+                continue
+            a = torch.randn(m, k, device=ws[0].device).to(torch.bfloat16)
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=ws[0].device)
+            calls = max(4, min(len(ws), 12))
+            mine = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], out, workspace), calls)
+            lib = _graph_time(lambda i: torch.mm(a, ws[i % len(ws)].t(), out=out), calls)
+            _tuned[key] = mine < lib
+            if log is not None:
+                log(f"product [{m} x {k}] . [{n} x {k}]^T: tcgen05 {mine:.1f} us, library {lib:.1f} us")
+    return dict(_tuned)
 
 
 def linear_bf16(x, w, out, workspace=None, status=None):

@@ -56,6 +56,9 @@ class AttentionMixer(Mixer):
             self.q_norm = tensors[f"{p}.q_norm.weight"].contiguous()
             self.k_norm = tensors[f"{p}.k_norm.weight"].contiguous()
 
+    def linear_weights(self):
+        return [self.w_qkv, self.w_o]
+
     def forward(self, x, batch, cache):
         ops, ws, dt = self.ctx.ops, self.ctx.workspace, self.ctx.dtype
         n = x.shape[0]

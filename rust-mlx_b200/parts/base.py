@@ -91,6 +91,10 @@ class Part:
     def children(self) -> list:
         return []
 
+    def linear_weights(self) -> list:
+        """The bound matrices this part multiplies activations with (for timing product kernels)."""
+        return []
+
     def all_param_specs(self) -> list:
         specs = list(self.param_specs())
         for c in self.children():

@@ -49,6 +49,9 @@ class OutputHead(Part):
         super().bind(tensors, ctx)
         self.weight = self.tied_to.weight if self.name is None else tensors[self.name].contiguous()
 
+    def linear_weights(self):
+        return [self.weight]
+
     def forward(self, x, batch=None):
         logits = self.ctx.workspace.get("logits", (x.shape[0], self.vocab), torch.float32)
         self.ctx.ops.linear(x, self.weight, logits, self.ctx.workspace, batch.status if batch is not None else None)

@@ -31,6 +31,9 @@ class SwiGLUFeedForward(FeedForward):
                                    dim=0).contiguous()
         self.w_down = tensors[f"{p}.down_proj.weight"].contiguous()
 
+    def linear_weights(self):
+        return [self.w_gate_up, self.w_down]
+
     def forward(self, x, batch=None):
         ops, ws, dt = self.ctx.ops, self.ctx.workspace, self.ctx.dtype
         n = x.shape[0]
