@@ -16,6 +16,11 @@
 // most 16 rows, i.e. decoding): all warps hold the same 16 rows and each takes 16 of the 64
 // keys, so that one token's work is spread over the block; the warps' partial results are
 // combined through shared memory at the end.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace {
@@ -374,6 +379,298 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decoding with TMA: every tile has at most 16 rows (one or a few tokens by the heads of a group), so
+// the work is reading keys and values.  A fifth warp is the producer: one thread fetches a key tile
+// with a few tensor-map copies (cp.async.bulk.tensor, boxes of up to 64 rows by 64 columns, 128-byte
+// swizzle, completion on an mbarrier) into a ring of DSTAGES stages; the four computing warps each
+// take 16 of the tile's 64 keys, read them with ldmatrix at the swizzled places, and never spend an
+// instruction on addresses.  Built for head sizes 64 and 128 and pages of at least 8 positions.
+constexpr int DSTAGES = 3;
+constexpr int DTHREADS = (NWARPS + 1) * 32;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// Polls until the phase with the given parity has completed; gives up after a bounded number of polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_box(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// Element (row, col) of a key or value tile held as HD/64 blocks of [64 rows][64 columns], rows of 128
+// bytes whose 16-byte chunks are exchanged by the row's low three bits (the 128-byte swizzle of TMA).
+template <int HD>
+__device__ __forceinline__ const __nv_bfloat16* swz(const __nv_bfloat16* tile, int row, int col) {
+    return tile + (col >> 6) * (64 * 64) + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(DTHREADS) attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                       const __grid_constant__ CUtensorMap map_v,
+                                                                       const FlashParams p, int box_rows) {
+    constexpr int STRIDE = HD + 8, CHUNKS = HD / 8, KSTEPS = HD / 16, DTILES = HD / 8;
+    constexpr int TILE_ELEMS = 64 * HD;                    // one key tile (or value tile)
+    extern __shared__ unsigned char smem_decode_raw[];
+    // the stages sit on a 1024-byte boundary, as the 128-byte swizzle asks
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_decode_raw) + 1023) & ~(uintptr_t)1023);
+    __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(base);                        // [DSTAGES][K tile | V tile]
+    __nv_bfloat16* Qs = KV + DSTAGES * 2 * TILE_ELEMS;                                 // [16][STRIDE]
+    __shared__ __align__(8) uint64_t full_bar[DSTAGES], empty_bar[DSTAGES];
+    __shared__ int s_failed;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;   // one tile per sequence
+    if (tid == 0) {
+        s_failed = 0;
+        for (int st = 0; st < DSTAGES; ++st) {
+            mbar_init(&full_bar[st], 1);
+            mbar_init(&empty_bar[st], NWARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
+    }
+    const int tok0 = p.q_start[seq], n_tok = p.q_start[seq + 1] - tok0;
+    const int pos0 = p.positions[tok0];
+    const int rows_valid = n_tok * p.group;                 // at most 16
+    const int* table = p.block_table + (size_t)seq * p.table_stride;
+    const int lo_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int pos_last = pos0 + n_tok - 1;
+    const int kt_lo = lo_first / BN, kt_hi = pos_last / BN;
+    const int per_split = (kt_hi - kt_lo + 1 + p.n_splits - 1) / p.n_splits;
+    const int kt_begin = kt_lo + split * per_split;
+    const int kt_end = min(kt_hi + 1, kt_begin + per_split);
+    const int n_mine = kt_begin < kt_end ? kt_end - kt_begin : 0;
+
+    // Q rows (zeros beyond the tile's rows); the stages start as zeros so that a part of a tile that is never
+    // fetched (a page the request does not hold) has finite numbers in it
+    for (int idx = tid; idx < 16 * CHUNKS; idx += DTHREADS) {
+        const int r = idx / CHUNKS, c = idx - r * CHUNKS;
+        const bool valid = r < rows_valid;
+        const int tok = valid ? r / p.group : 0, g = valid ? r - tok * p.group : 0;
+        cp_async16(Qs + r * STRIDE + c * 8, p.q + ((size_t)(tok0 + tok) * p.nq + kvh * p.group + g) * HD + c * 8, valid);
+    }
+    cp_async_commit();
+    for (int idx = tid; idx < DSTAGES * 2 * TILE_ELEMS / 8; idx += DTHREADS)
+        reinterpret_cast<uint4*>(KV)[idx] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    cp_async_wait<0>();
+    __syncthreads();
+
+    if (warp == NWARPS) {
+        if (lane == 0) {
+            // ---- producer: per tile, 64 / box_rows boxes of rows by HD / 64 boxes of columns, for K and for V
+            const int boxes = BN / box_rows;
+            for (int i = 0; i < n_mine; ++i) {
+                const int st = i % DSTAGES, round = i / DSTAGES, kt = kt_begin + i;
+                if (round > 0 && !mbar_wait(&empty_bar[st], (round - 1) & 1)) { atomicExch(&s_failed, 1); break; }
+                uint32_t bytes = 0;
+                for (int b = 0; b < boxes; ++b) {
+                    const int kp = kt * BN + b * box_rows;
+                    if (kp > pos_last || kp + box_rows <= lo_first) continue;
+                    if (table[kp >> p.page_shift] >= 0) bytes += 2u * box_rows * HD * 2u;
+                    else atomicExch(p.status, 2);
+                }
+                mbar_expect_tx(&full_bar[st], bytes);
+                __nv_bfloat16* kd = KV + st * 2 * TILE_ELEMS;
+                __nv_bfloat16* vd = kd + TILE_ELEMS;
+                for (int b = 0; b < boxes; ++b) {
+                    const int kp = kt * BN + b * box_rows;
+                    if (kp > pos_last || kp + box_rows <= lo_first) continue;
+                    const int page = table[kp >> p.page_shift];
+                    if (page < 0) continue;
+                    const int row = (page * p.nkv + kvh) * p.page_size + (kp & (p.page_size - 1));
+#pragma unroll
+                    for (int cb = 0; cb < HD / 64; ++cb) {
+                        tma_box(kd + cb * 64 * 64 + b * box_rows * 64, &map_k, &full_bar[st], cb * 64, row);
+                        tma_box(vd + cb * 64 * 64 + b * box_rows * 64, &map_v, &full_bar[st], cb * 64, row);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    // ---- computing warps: the same 16 rows, 16 keys of every tile each
+    const int key_base = (warp & 3) * 16;
+    int row_pos[2], row_lo[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = (lane >> 2) + 8 * i;
+        row_ok[i] = r < rows_valid;
+        row_pos[i] = pos0 + (row_ok[i] ? r / p.group : 0);
+        row_lo[i] = p.window > 0 ? max(0, row_pos[i] - p.window + 1) : 0;
+    }
+    uint32_t qf[KSTEPS][4];
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk)
+        ldmatrix_x4(qf[kk], Qs + (lane & 15) * STRIDE + kk * 16 + (lane >> 4) * 8);
+    float o[DTILES][4];
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int i = 0; i < n_mine && warp < NWARPS; ++i) {
+        const int kt = kt_begin + i, stage = i % DSTAGES;
+        if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], (i / DSTAGES) & 1))) { atomicExch(&s_failed, 1); break; }
+        const __nv_bfloat16* kbase = KV + stage * 2 * TILE_ELEMS;
+        const __nv_bfloat16* vbase = kbase + TILE_ELEMS;
+        float s[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            uint32_t kf[4];
+            const int key = key_base + (lane & 7) + ((lane >> 4) << 3);
+            const int dcol = kk * 16 + ((lane >> 3) & 1) * 8;
+            ldmatrix_x4(kf, swz<HD>(kbase, key, dcol));
+            mma_bf16(s[0], qf[kk], kf[0], kf[1]);
+            mma_bf16(s[1], qf[kk], kf[2], kf[3]);
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+        bool any_masked = false;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const int kp = kt * BN + key_base + j * 8 + (lane & 3) * 2 + (e & 1);
+                const bool ok = row_ok[r] && kp <= row_pos[r] && kp >= row_lo[r];
+                any_masked |= kp > pos_last;
+                s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+                mx[r] = fmaxf(mx[r], s[j][e]);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m[r], mx[r]);
+            corr[r] = m_new == -INFINITY ? 1.f : exp2f(m[r] - m_new);
+            m[r] = m_new;
+            l[r] *= corr[r];
+        }
+        const float mref[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(s[j][e] - mref[e >> 1]);
+                s[j][e] = pv;
+                l[e >> 1] += pv;
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) {
+            o[d][0] *= corr[0]; o[d][1] *= corr[0];
+            o[d][2] *= corr[1]; o[d][3] *= corr[1];
+        }
+        uint32_t pf[4];
+        pf[0] = pack_bf16(s[0][0], s[0][1]);
+        pf[1] = pack_bf16(s[0][2], s[0][3]);
+        pf[2] = pack_bf16(s[1][0], s[1][1]);
+        pf[3] = pack_bf16(s[1][2], s[1][3]);
+        // positions past the sequence's end lie in a fetched page but were never written: whatever is there
+        // must not reach the sum, not even multiplied by zero
+        const bool tail = __any_sync(0xffffffffu, any_masked);
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {
+            uint32_t vf[4];
+            const int key = key_base + (lane & 7) + ((lane >> 3) & 1) * 8;
+            const int dcol = dp * 16 + (lane >> 4) * 8;
+            ldmatrix_x4_trans(vf, swz<HD>(vbase, key, dcol));
+            if (tail) {
+                // value fragment registers hold keys key_base + 2 * (lane % 4) + {0, 1} (+ 8 for the odd registers)
+                const int k0 = kt * BN + key_base + (lane & 3) * 2;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int ka = k0 + (q & 1) * 8;
+                    if (ka > pos_last) vf[q] &= 0xffff0000u;
+                    if (ka + 1 > pos_last) vf[q] &= 0x0000ffffu;
+                }
+            }
+            mma_bf16(o[2 * dp], pf, vf[0], vf[1]);
+            mma_bf16(o[2 * dp + 1], pf, vf[2], vf[3]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    }
+    allow_dependents();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    if (tid == 0 && s_failed) atomicExch(p.status, 3);
+    // combine the four warps' partial results in warp order
+    float* so = reinterpret_cast<float*>(KV);             // [NWARPS][16][HD]
+    float* sml = so + NWARPS * 16 * HD;                   // [NWARPS][16][2]
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2 && warp < NWARPS; ++i) {
+        const int r = (lane >> 2) + 8 * i;
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) {
+            const int col = d * 8 + (lane & 3) * 2;
+            *reinterpret_cast<float2*>(so + (warp * 16 + r) * HD + col) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+        }
+        if ((lane & 3) == 0) {
+            sml[(warp * 16 + r) * 2] = m[i];
+            sml[(warp * 16 + r) * 2 + 1] = l[i];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows_valid * HD; idx += DTHREADS) {
+        const int r = idx / HD, d = idx - r * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, sml[(w * 16 + r) * 2]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) {
+            const float mw = sml[(w * 16 + r) * 2];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            L += f * sml[(w * 16 + r) * 2 + 1];
+            acc += f * so[(w * 16 + r) * HD + d];
+        }
+        const int tok = r / p.group, g = r - tok * p.group;
+        const size_t row = (size_t)(tok0 + tok) * p.nq + kvh * p.group + g;
+        if (p.n_splits == 1) {
+            p.out[row * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            const size_t prow = (size_t)split * p.n_tokens * p.nq + row;
+            p.part_o[prow * HD + d] = acc;
+            if (d == 0) {
+                p.part_ml[prow * 2] = M;
+                p.part_ml[prow * 2 + 1] = L;
+            }
+        }
+    }
+}
+
 // out[row] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the splits, in split order.
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        __nv_bfloat16* __restrict__ out, int rows, int hd, int n_splits) {
@@ -419,6 +716,72 @@ template <int HD>
 int launch_flash(const FlashParams& p, int n_tiles, bool keysplit, cudaStream_t s) {
     return keysplit ? launch_flash_as<HD, true>(p, n_tiles, s) : launch_flash_as<HD, false>(p, n_tiles, s);
 }
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// A pool of one layer seen as [pages * kv_heads * page_size rows, hd columns]; boxes of [box_rows, 64], 128-byte swizzle.
+// Maps depend on the address and the geometry only, and pools keep theirs: encoded maps are kept.
+int pool_map(CUtensorMap* map, const void* base, long long rows, int hd, int box_rows) {
+    struct Key {
+        const void* base; long long rows; int hd, box_rows;
+        bool operator==(const Key& o) const { return base == o.base && rows == o.rows && hd == o.hd && box_rows == o.box_rows; }
+    };
+    struct Hash {
+        size_t operator()(const Key& k) const {
+            return std::hash<const void*>()(k.base) ^ (std::hash<long long>()(k.rows) * 31) ^ (size_t)(k.hd * 7 + k.box_rows);
+        }
+    };
+    static std::mutex lock;
+    static std::unordered_map<Key, CUtensorMap, Hash> cache;
+    static EncodeTiled fn = nullptr;
+    std::lock_guard<std::mutex> guard(lock);
+    const Key key{base, rows, hd, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *map = it->second;
+        return 0;
+    }
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            RMX_FAIL("attention_decode: the driver has no cuTensorMapEncodeTiled");
+        fn = (EncodeTiled)ptr;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) RMX_FAIL("attention_decode: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *map);
+    return 0;
+}
+
+template <int HD>
+int launch_decode_tma(const FlashParams& p, long long pool_rows, cudaStream_t s) {
+    const int box_rows = p.page_size < BN ? p.page_size : BN;
+    CUtensorMap mk, mv;
+    if (pool_map(&mk, p.k_pool, pool_rows, HD, box_rows) != 0) return -1;
+    if (pool_map(&mv, p.v_pool, pool_rows, HD, box_rows) != 0) return -1;
+    constexpr size_t smem = 1024 + (size_t)DSTAGES * 2 * 64 * HD * 2 + (size_t)16 * (HD + 8) * 2;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RMX_FAIL("attention_decode: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
+        raised = true;
+    }
+    dim3 grid(p.n_seqs, p.nkv, p.n_splits);
+    attention_decode_tma_kernel<HD><<<grid, DTHREADS, smem, s>>>(mk, mv, p, box_rows);
+    RMX_CHECK_LAUNCH("attention_decode");
+    return 0;
+}
 }  // namespace
 
 // Which head sizes the tensor-core kernel is built for; others take attention_plain.
@@ -427,14 +790,15 @@ RMX_API int rmx_attention_flash_supports(int hd, int group) {
     return hd_ok && group >= 1 && group <= 16 ? 1 : 0;
 }
 
-// max_q_len: the most tokens any sequence brings to this step (0: unknown).
+// max_q_len: the most tokens any sequence brings to this step (0: unknown).  pool_pages: pages in k_pool / v_pool
+// (0: unknown; the TMA path for decoding is then not taken).
 // n_tiles: the number of query tiles of the batch, sum over sequences of ceil(tokens / (64 / group)).
 // part_o / part_ml are needed when n_splits > 1: [n_splits, tokens * nq, hd] and [n_splits, tokens * nq, 2] floats.
 RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v_pool, const int* q_start,
                                 const int* positions, const int* block_table, int table_stride, int page_size,
                                 void* out, float* part_o, float* part_ml, int n_seqs, int n_tokens, int n_tiles,
                                 int nq, int nkv, int hd, int window, float scale, int n_splits, int max_q_len,
-                                int* status, void* stream) {
+                                int pool_pages, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_flash: %d query heads over %d kv heads", nq, nkv);
     const int group = nq / nkv;
@@ -456,6 +820,12 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     // every tile has at most 16 rows (decoding, or very short portions): spread keys over the warps
     const bool keysplit = max_q_len > 0 && max_q_len * group <= 16;
     int rc;
+    // decoding at the head sizes of real models: keys and values come by TMA (pool_pages tells the pool's extent)
+    if (keysplit && pool_pages > 0 && page_size >= 8 && (hd == 64 || hd == 128) && n_tiles == n_seqs &&
+        ((uintptr_t)k_pool & 127) == 0 && ((uintptr_t)v_pool & 127) == 0) {
+        const long long pool_rows = (long long)pool_pages * nkv * page_size;
+        rc = hd == 64 ? launch_decode_tma<64>(p, pool_rows, s) : launch_decode_tma<128>(p, pool_rows, s);
+    } else
     switch (hd) {
         case 16: rc = launch_flash<16>(p, n_tiles, keysplit, s); break;
         case 32: rc = launch_flash<32>(p, n_tiles, keysplit, s); break;

@@ -274,6 +274,9 @@ def flash_splits(n_tiles: int, nkv: int, max_seq_len: int) -> int:
     return 1
 
 
+use_tma = True   # decoding fetches keys and values by TMA where the kernel is built for it
+
+
 def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
                     n_splits=None):
     """Tensor-core attention over pages for bfloat16 (prompt portions and decoded tokens alike)."""
@@ -295,7 +298,7 @@ def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
         _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml), c_int(batch.n_seqs), c_int(n), c_int(n_tiles),
         c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(n_splits),
-        c_int(getattr(batch, "max_q_len", 0)), _ptr(batch.status, torch.int32, "status"), _stream()))
+        c_int(getattr(batch, "max_q_len", 0)), c_int(k_pool.shape[0] if use_tma else 0), _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched(2 if n_splits > 1 else 1)
 
 

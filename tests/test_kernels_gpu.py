@@ -398,8 +398,10 @@ class _Batch:
     (16, 1, 128, 16, 0), (7, 7, 128, 2, 5), (8, 2, 64, 64, 100)])
 def test_attention_flash_over_pages(nq, nkv, hd, page, window, splits):
     """Portions of several sequences (longer than one query tile, crossing key tiles) beside
-    single decoded tokens; NaN in every slot of the pool that must not be read."""
+    single decoded tokens; NaN in every slot of the pool that must not be read.  Outputs are
+    bfloat16: the bound is 1e-2 * (1 + |value|), half a last bit at the largest values."""
     from rust_mlx_b200.engine.workspace import Workspace
+    torch.manual_seed(nq * 1000 + hd)
     lengths = [200, 1, 33, 130, 300, 64]
     new = [70, 1, 33, 1, 1, 64]
     k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, torch.bfloat16, seed=hd + nq)
@@ -416,7 +418,7 @@ def test_attention_flash_over_pages(nq, nkv, hd, page, window, splits):
         want = plain_attention(qs[s], ks[s], vs[s], torch.arange(n - c, n), window, scale)
         got = out[at:at + c].double().cpu().reshape(c, nq, hd)
         assert not torch.isnan(got).any()
-        assert (got - want).abs().max().item() < 1e-2, (s, n, c)
+        assert ((got - want).abs() <= 1e-2 * (1 + want.abs())).all(), (s, n, c)
         at += c
 
 
@@ -465,11 +467,13 @@ def test_attention_flash_rows_do_not_depend_on_the_batch():
 @pytest.mark.parametrize("splits", [None, 1, 4])
 @pytest.mark.parametrize("nq, nkv, hd, page, window, new_len", [
     (4, 2, 16, 16, 0, 1), (6, 2, 32, 8, 20, 1), (32, 8, 128, 64, 0, 1), (16, 1, 128, 16, 0, 1), (8, 2, 64, 4, 50, 4),
-    (5, 5, 96, 2, 0, 16), (64, 8, 128, 64, 0, 2)])
+    (5, 5, 96, 2, 0, 16), (64, 8, 128, 64, 0, 2), (6, 3, 64, 8, 70, 3), (12, 4, 128, 32, 33, 1), (4, 4, 64, 128, 0, 2),
+    (40, 8, 128, 16, 0, 1)])
 def test_attention_flash_decoding_arrangement(nq, nkv, hd, page, window, new_len, splits):
     """Every sequence brings so few tokens that a tile has at most 16 rows: the kernel then
     spreads a tile's keys over its warps and combines them."""
     from rust_mlx_b200.engine.workspace import Workspace
+    torch.manual_seed(nq * 1000 + hd + new_len)
     lengths = [200, 17, 33, 130, 700, 64, 65, 16]
     new = [new_len] * len(lengths)
     k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, torch.bfloat16, seed=hd + nq)
@@ -485,7 +489,7 @@ def test_attention_flash_decoding_arrangement(nq, nkv, hd, page, window, new_len
         want = plain_attention(qs[s], ks[s], vs[s], torch.arange(n - c, n), window, hd ** -0.5)
         got = out[at:at + c].double().cpu().reshape(c, nq, hd)
         assert not torch.isnan(got).any()
-        assert (got - want).abs().max().item() < 1e-2, (s, n, c)
+        assert ((got - want).abs() <= 1e-2 * (1 + want.abs())).all(), (s, n, c)
         at += c
 
 
