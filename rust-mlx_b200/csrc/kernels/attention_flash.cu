@@ -64,6 +64,7 @@ struct FlashParams {
     __nv_bfloat16* out;            // [tokens, nq, HD]
     float* part_o;                 // [splits, tokens * nq, HD]   (splits > 1)
     float* part_ml;                // [splits, tokens * nq, 2]
+    unsigned int* counters;        // [seqs * nkv] zeros, or null: who is the last split of a (sequence, kv head)
     int* status;
     int n_seqs, n_tokens, nq, nkv, group, tq, table_stride, page_size, page_shift, window, n_splits;
     float scale_log2;
@@ -669,6 +670,33 @@ __global__ void __launch_bounds__(DTHREADS) attention_decode_tma_kernel(const __
             }
         }
     }
+    if (p.n_splits == 1 || p.counters == nullptr) return;
+    // the last split of this (sequence, kv head) to finish combines all of them, in split order
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(&p.counters[seq * p.nkv + kvh], 1u) == (unsigned)p.n_splits - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const size_t rows_all = (size_t)p.n_tokens * p.nq;
+    for (int idx = tid; idx < rows_valid * HD; idx += DTHREADS) {
+        const int r = idx / HD, d = idx - r * HD;
+        const int tok = r / p.group, g = r - tok * p.group;
+        const size_t row = (size_t)(tok0 + tok) * p.nq + kvh * p.group + g;
+        float M = -INFINITY;
+        for (int z = 0; z < p.n_splits; ++z) M = fmaxf(M, __ldcg(p.part_ml + (z * rows_all + row) * 2));
+        float L = 0.f, acc = 0.f;
+        for (int z = 0; z < p.n_splits; ++z) {
+            const float mz = __ldcg(p.part_ml + (z * rows_all + row) * 2);
+            if (mz == -INFINITY) continue;
+            const float f = exp2f(mz - M);
+            L += f * __ldcg(p.part_ml + (z * rows_all + row) * 2 + 1);
+            acc += f * __ldcg(p.part_o + (z * rows_all + row) * HD + d);
+        }
+        p.out[row * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+    if (tid == 0) p.counters[seq * p.nkv + kvh] = 0;   // zero again for the next launch
 }
 
 // out[row] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the splits, in split order.
@@ -793,10 +821,11 @@ RMX_API int rmx_attention_flash_supports(int hd, int group) {
 // max_q_len: the most tokens any sequence brings to this step (0: unknown).  pool_pages: pages in k_pool / v_pool
 // (0: unknown; the TMA path for decoding is then not taken).
 // n_tiles: the number of query tiles of the batch, sum over sequences of ceil(tokens / (64 / group)).
+// counters: seqs * nkv zeroed unsigned ints (left zero), or null; lets the decoding kernel combine its splits itself.
 // part_o / part_ml are needed when n_splits > 1: [n_splits, tokens * nq, hd] and [n_splits, tokens * nq, 2] floats.
 RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v_pool, const int* q_start,
                                 const int* positions, const int* block_table, int table_stride, int page_size,
-                                void* out, float* part_o, float* part_ml, int n_seqs, int n_tokens, int n_tiles,
+                                void* out, float* part_o, float* part_ml, unsigned int* counters, int n_seqs, int n_tokens, int n_tiles,
                                 int nq, int nkv, int hd, int window, float scale, int n_splits, int max_q_len,
                                 int pool_pages, int* status, void* stream) {
     if (n_tokens == 0) return 0;
@@ -810,7 +839,7 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     FlashParams p;
     p.q = (const __nv_bfloat16*)q; p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
     p.q_start = q_start; p.positions = positions; p.block_table = block_table; p.out = (__nv_bfloat16*)out;
-    p.part_o = part_o; p.part_ml = part_ml; p.status = status;
+    p.part_o = part_o; p.part_ml = part_ml; p.status = status; p.counters = nullptr;
     p.n_seqs = n_seqs; p.n_tokens = n_tokens; p.nq = nq; p.nkv = nkv; p.group = group; p.tq = BM / group;
     p.table_stride = table_stride; p.page_size = page_size; p.window = window; p.n_splits = n_splits;
     p.page_shift = 0;
@@ -824,7 +853,9 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     if (keysplit && pool_pages > 0 && page_size >= 8 && (hd == 64 || hd == 128) && n_tiles == n_seqs &&
         ((uintptr_t)k_pool & 127) == 0 && ((uintptr_t)v_pool & 127) == 0) {
         const long long pool_rows = (long long)pool_pages * nkv * page_size;
+        p.counters = counters;   // with counters the kernel combines its splits itself
         rc = hd == 64 ? launch_decode_tma<64>(p, pool_rows, s) : launch_decode_tma<128>(p, pool_rows, s);
+        if (rc == 0 && counters) return 0;
     } else
     switch (hd) {
         case 16: rc = launch_flash<16>(p, n_tiles, keysplit, s); break;

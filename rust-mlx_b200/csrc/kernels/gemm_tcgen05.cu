@@ -104,6 +104,8 @@ struct GemmParams {
     int* status;
     int M, N, K, ldc, splits, k_blocks, out_float;
     int dependent;           // launched as a programmatic dependent: wait for the grid before before reading A
+    int epilogue;            // 0: C = product.  1: the tile's rows are 64 gate rows then their 64 up rows;
+                             //    C[M, N / 2] = silu(gate) * up, formed in float and rounded once
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -269,6 +271,30 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
         }
         if (tid == 0) p.counters[tile] = 0;  // ready for the next launch
     }
+    if (p.epilogue == 1) {
+        // the upper half of the block (up rows) hands its sums to the lower half (gate rows) through the
+        // shared-memory stages, which are free by now
+        float* ex = reinterpret_cast<float*>(tiles);   // [MPAD][64]
+        if (CLUSTER) __syncthreads();                  // the first block has read the other slices' sums from there
+        if (tid >= 64) {
+#pragma unroll
+            for (int t = 0; t < MPAD; ++t) ex[t * 64 + tid - 64] = acc[t];
+        }
+        __syncthreads();
+        const int col = tile * 64 + tid;
+        if (tid < 64 && col < p.N / 2) {
+#pragma unroll
+            for (int t = 0; t < MPAD; ++t) {
+                if (t < p.M) {
+                    const float g = acc[t], u = ex[t * 64 + tid];
+                    const float v = g / (1.f + expf(-g)) * u;
+                    if (p.out_float) reinterpret_cast<float*>(p.c)[(size_t)t * p.ldc + col] = v;
+                    else reinterpret_cast<__nv_bfloat16*>(p.c)[(size_t)t * p.ldc + col] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+        return;
+    }
     if (n < p.N) {
         if (p.out_float) {
             float* c = reinterpret_cast<float*>(p.c);
@@ -423,6 +449,8 @@ RMX_API int rmx_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N
     const bool fits = (size_t)(splits - 1) * mpad * TILE_N * 4 <= (size_t)stages * (TILE_N * TILE_K * 2 + mpad * TILE_K * 2);
     const bool cluster = (flags & 1) && splits >= 2 && splits <= 8 && fits;
     const bool dependent = (flags & 2) != 0;
+    const int epilogue = (flags & 4) ? 1 : 0;   // flags: 4 = SwiGLU over blocks of 64 gate rows and 64 up rows
+    RMX_REQUIRE(!epilogue || N % 128 == 0, "gemm_tcgen05: the SwiGLU epilogue needs N to be a multiple of 128, got %d", N);
     RMX_REQUIRE(splits == 1 || cluster || (partial && counters), "gemm_tcgen05: split-K needs scratch");
     CUtensorMap mw, ma;
     if (make_map(&mw, W, N, K, ldw, TILE_N) != 0) return -1;
@@ -430,7 +458,7 @@ RMX_API int rmx_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N
     GemmParams p;
     p.c = C; p.partial = partial; p.counters = counters; p.status = status;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
-    p.dependent = 0;
+    p.dependent = 0; p.epilogue = epilogue;
     cudaStream_t s = (cudaStream_t)stream;
     // stages sized so that two blocks fit an SM: more blocks in flight smooth the last wave
     if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s, cluster, dependent);
@@ -518,7 +546,7 @@ RMX_API int rmx_gemm_tcgen05_static(const void* A, const void* W, void* C, int M
     GemmParams p;
     p.c = C; p.partial = scratch.partial; p.counters = scratch.counters; p.status = scratch.status;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
-    p.dependent = 0;
+    p.dependent = 0; p.epilogue = 0;
     if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s);
     if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s);
     return launch<64, 4>(mw, ma, p, n_tiles, s);

@@ -145,46 +145,63 @@ RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const int* rows, const 
 // in float with one rounding.
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
 
+// Where gate j and up j lie in a row of 2 * inter numbers: concatenated [gate | up] (block == 0), or in blocks of
+// `block` gate numbers followed by their `block` up numbers.
+__device__ __forceinline__ void gate_up_at(int j, int inter, int block, int& gi, int& ui) {
+    if (block == 0) {
+        gi = j;
+        ui = inter + j;
+    } else {
+        gi = (j / block) * 2 * block + j % block;
+        ui = gi + block;
+    }
+}
+
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / inter;
     const int j = (int)(idx - t * inter);
-    const float g = to_float(gate_up[t * 2 * inter + j]);
-    const float u = to_float(gate_up[t * 2 * inter + inter + j]);
+    int gi, ui;
+    gate_up_at(j, inter, block, gi, ui);
+    const float g = to_float(gate_up[t * 2 * inter + gi]);
+    const float u = to_float(gate_up[t * 2 * inter + ui]);
     out[idx] = from_float<T>(silu_mul(g, u));
 }
 
 // four outputs per thread; inter is a multiple of 4
 template <typename T>
-__global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total4) {
+__global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total4) {
     allow_dependents();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total4) return;
     const int per_row = inter >> 2;
     const size_t t = idx / per_row;
     const int j = (int)(idx - t * per_row) * 4;
+    int gi, ui;
+    gate_up_at(j, inter, block, gi, ui);   // four neighbours stay together: block is a multiple of 4
     float4 g, u;
-    load4(gate_up + t * 2 * inter + j, g);
-    load4(gate_up + t * 2 * inter + inter + j, u);
+    load4(gate_up + t * 2 * inter + gi, g);
+    load4(gate_up + t * 2 * inter + ui, u);
     store4(out + t * inter + j, make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w)));
 }
 
-RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int dtype, void* stream) {
+RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int block, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && inter > 0, "swiglu: bad sizes");
-    const bool vec = (inter & 3) == 0;
+    RMX_REQUIRE(block == 0 || (block > 0 && inter % block == 0), "swiglu: blocks of %d do not divide %d", block, inter);
+    const bool vec = (inter & 3) == 0 && (block & 3) == 0;
     const size_t total = (size_t)n_tokens * inter / (vec ? 4 : 1);
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_F32) {
-        if (vec) swiglu_kernel4<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
-        else swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
+        if (vec) swiglu_kernel4<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, block, total);
+        else swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, block, total);
     } else if (dtype == RMX_BF16) {
-        if (vec) swiglu_kernel4<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
-        else swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+        if (vec) swiglu_kernel4<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total);
+        else swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total);
     } else {
         RMX_FAIL("swiglu: unknown dtype %d", dtype);
     }

@@ -112,6 +112,8 @@ class Engine:
         if self.dtype == torch.bfloat16 and _ops.tcgen05_policy == "auto":
             weights = [w for part in self.spec.all_parts() for w in part.linear_weights()]
             _ops.autotune_linears(weights, self.workspace, log=_log if verbose else None)
+            fused = [w for part in self.spec.all_parts() for w in part.gate_up_weights()]
+            _ops.autotune_fused_swiglu(fused, self.workspace, log=_log if verbose else None)
         self.load_seconds = time.time() - t0
         if verbose:
             _log(f"model ready in {self.load_seconds:.1f}s: {len(self.spec.blocks)} layers, {self.dtype_name}, "

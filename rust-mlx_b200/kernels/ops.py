@@ -84,12 +84,14 @@ def add_residual(h, delta):
     _launched()
 
 
-def swiglu(gate_up, out):
+def swiglu(gate_up, out, block=0):
+    """out = silu(gate) * up.  A row of ``gate_up`` is [gate | up] (block 0) or blocks of ``block``
+    gate numbers each followed by its ``block`` up numbers."""
     lib = kernels_library()
     n, inter = out.shape
     if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype:
         raise KernelError("swiglu: gate_up must be [tokens, 2 * inter] of the output's dtype")
-    check(lib.rmx_swiglu(_ptr(gate_up, name="gate_up"), _ptr(out, name="out"), c_int(n), c_int(inter),
+    check(lib.rmx_swiglu(_ptr(gate_up, name="gate_up"), _ptr(out, name="out"), c_int(n), c_int(inter), c_int(block),
                          c_int(dtype_code(out)), _stream()))
     _launched()
 
@@ -231,6 +233,36 @@ def autotune_linears(weights: list, workspace=None, rows=(8, 32, 64), log=None) 
     return dict(_tuned)
 
 
+def autotune_fused_swiglu(weights: list, workspace=None, rows=(8, 32, 64), log=None) -> dict:
+    """The same for gate/up weights in blocks of 64: the tcgen05 product with the SwiGLU epilogue
+    against the library's product followed by the pointwise kernel."""
+    groups = {}
+    for w in weights:
+        if w is not None and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_cuda and w.shape[0] % 128 == 0:
+            groups.setdefault((w.shape[0], w.shape[1]), []).append(w)
+    for (n, k), ws in groups.items():
+        if not tcgen05_supported(1, n, k) or len(ws) * n * k * 2 < 256e6:
+            continue
+        for m in rows:
+            key = (n, k, _mpad(m), "swiglu")
+            if key in _tuned:
+                continue
+            a = torch.randn(m, k, device=ws[0].device).to(torch.bfloat16)
+            gu = torch.empty(m, n, dtype=torch.bfloat16, device=ws[0].device)
+            act = torch.empty(m, n // 2, dtype=torch.bfloat16, device=ws[0].device)
+            calls = max(4, min(len(ws), 12))
+            mine = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], act, workspace, swiglu=True), calls)
+
+            def lib_pair(i):
+                torch.mm(a, ws[i % len(ws)].t(), out=gu)
+                swiglu(gu, act, 64)
+            lib = _graph_time(lib_pair, calls)
+            _tuned[key] = mine < lib
+            if log is not None:
+                log(f"gate/up [{m} x {k}] . [{n} x {k}]^T + SwiGLU: fused tcgen05 {mine:.1f} us, library + pointwise {lib:.1f} us")
+    return dict(_tuned)
+
+
 def linear_bf16(x, w, out, workspace=None, status=None):
     """bfloat16 operands, float accumulation; the result in bfloat16 or (for logits) float32."""
     m, k = x.shape
@@ -288,15 +320,17 @@ def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
     if n_splits is None:
         n_splits = getattr(batch, "forced_splits", None) or flash_splits(n_tiles, nkv, batch.max_seq_len)
     n = q.shape[0]
-    part_o = part_ml = None
+    part_o = part_ml = counters = None
     if n_splits > 1:
         part_o = workspace.get("attn_part_o", (n_splits, n * nq, hd), torch.float32)
         part_ml = workspace.get("attn_part_ml", (n_splits, n * nq, 2), torch.float32)
+        counters = workspace.get_zeroed("attn_counters", (max(4096, batch.n_seqs * nkv),), torch.int32)
     check(lib.rmx_attention_flash(
         _ptr(q, torch.bfloat16, "q"), _ptr(k_pool, torch.bfloat16, "k_pool"), _ptr(v_pool, torch.bfloat16, "v_pool"),
         _ptr(batch.q_start, torch.int32, "q_start"), _ptr(batch.positions, torch.int32, "positions"),
         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
-        _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml), c_int(batch.n_seqs), c_int(n), c_int(n_tiles),
+        _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml), _ptr(counters), c_int(batch.n_seqs), c_int(n),
+        c_int(n_tiles),
         c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(n_splits),
         c_int(getattr(batch, "max_q_len", 0)), c_int(k_pool.shape[0] if use_tma else 0), _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched(2 if n_splits > 1 else 1)
@@ -319,25 +353,19 @@ def tcgen05_supported(m: int, n: int, k: int) -> bool:
 
 
 def tcgen05_splits(m: int, n: int, k: int) -> int:
-    """How many slices of K share a tile of 128 weight rows.  More slices fill the SMs' block
-    slots (two per SM) more evenly but leave float partial sums to be written and read again;
-    the choice minimises (weight bytes + partial bytes) / (share of slots busy), keeping at
-    least 8 k-blocks of 64 per slice."""
+    """How many slices of K share a tile of 128 weight rows.  The product is bound by reading the
+    weight: what matters is that enough blocks are resident to keep loads in flight on every SM
+    (about one block per SM; measured on Qwen3-8B shapes), not that the last wave is full.  So:
+    the fewest slices that give at least 128 blocks, at most 8 (a cluster), each slice keeping at
+    least 4 k-blocks of 64."""
     tiles = -(-n // 128)
     k_blocks = -(-k // 64)
-    slots = 2 * _sm_count()
-    mpad = 16 if m <= 16 else (32 if m <= 32 else 64)
-    best, best_cost = 1, None
-    for s in range(1, max(1, k_blocks // 8) + 1):
-        blocks = tiles * s
-        eff = blocks / (-(-blocks // slots) * slots)
-        cost = (n * k * 2 + (s * mpad * n * 8 if s > 1 else 0)) / eff
-        if best_cost is None or cost < best_cost * 0.97:
-            best, best_cost = s, cost
-    return best
+    if tiles >= 128:
+        return 1
+    return max(1, min(-(-128 // tiles), 8, k_blocks // 4))
 
 
-def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False):
+def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False, swiglu=False):
     """out[M, N] = a[M, K] . w[N, K]^T for M <= 64 on the tcgen05 tensor cores (bfloat16 in,
     float accumulation, bfloat16 or float out).  ``cluster``: split-K slices of a tile form a
     thread-block cluster and add their sums through distributed shared memory (up to 8 slices),
@@ -346,7 +374,9 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
     lib = kernels_library()
     m, k = a.shape
     n = w.shape[0]
-    if w.shape[1] != k or out.shape != (m, n) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+    # swiglu: w's rows come in blocks of 64 gate rows and their 64 up rows; out is silu(gate) * up, [m, n / 2]
+    want_shape = (m, n // 2) if swiglu else (m, n)
+    if w.shape[1] != k or out.shape != want_shape or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm_tcgen05: {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} of {a.dtype}")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("gemm_tcgen05: the result is bfloat16 or float32")
@@ -366,6 +396,18 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
         _ptr(a, name="a"), _ptr(w, name="w"), _ptr(out, name="out"), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
         c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0), c_int(splits),
         _ptr(partial), _ptr(counters), _ptr(status, torch.int32, "status"),
-        c_int((1 if cluster else 0) | (2 if dependent else 0)), _stream()))
+        c_int((1 if cluster else 0) | (2 if dependent else 0) | (4 if swiglu else 0)), _stream()))
     _launched()
     return status
+
+
+fused_swiglu = True   # the gate/up product of few rows forms silu(gate) * up in its epilogue
+
+
+def prefers_fused_swiglu(m: int, n: int, k: int) -> bool:
+    """The fused product saves a kernel and the round trip of the [m, n] intermediate; it is taken
+    wherever the tcgen05 kernel runs at all, unless timing said the library's product plus the
+    pointwise kernel is faster for this shape."""
+    if not fused_swiglu or tcgen05_policy == "none" or not tcgen05_supported(m, n, k) or n % 128:
+        return False
+    return _tuned.get((n, k, _mpad(m), "swiglu"), True)

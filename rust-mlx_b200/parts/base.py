@@ -95,6 +95,10 @@ class Part:
         """The bound matrices this part multiplies activations with (for timing product kernels)."""
         return []
 
+    def gate_up_weights(self) -> list:
+        """Fused gate/up matrices in blocks of 64 rows (for timing the product with the SwiGLU epilogue)."""
+        return []
+
     def all_param_specs(self) -> list:
         specs = list(self.param_specs())
         for c in self.children():

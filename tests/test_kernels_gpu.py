@@ -81,6 +81,20 @@ def test_swiglu(dtype, n, inter):
     assert ((out.double() - want).abs() <= tol * (1 + want.abs())).all()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n, inter, block", [(3, 128, 64), (70, 192, 64), (5, 24, 8), (9, 30, 6)])
+def test_swiglu_over_blocks_of_gate_and_up(dtype, n, inter, block):
+    dt = DT[dtype]
+    gu = rnd((n, 2 * inter), dt, 3.0, 4)
+    out = torch.empty(n, inter, dtype=dt, device=DEV)
+    ops().swiglu(gu, out, block)
+    v = gu.double().reshape(n, inter // block, 2, block)
+    g, u = v[:, :, 0].reshape(n, inter), v[:, :, 1].reshape(n, inter)
+    want = g * torch.sigmoid(g) * u
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    assert ((out.double() - want).abs() <= tol * (1 + want.abs())).all()
+
+
 @pytest.mark.parametrize("m, n, k", [(1, 16, 16), (3, 509, 96), (70, 130, 257), (128, 64, 4096), (200, 1000, 33)])
 def test_gemm_plain_float32(m, n, k):
     a, w = rnd((m, k), torch.float32, 1.0, 1), rnd((n, k), torch.float32, 1.0, 2)
@@ -513,6 +527,26 @@ def test_gemm_tcgen05(m, n, k, splits):
     out2 = torch.empty_like(out)
     ops().gemm_tcgen05(a, w, out2, status=status, splits=splits)
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("m, inter, k, splits", [(1, 64, 64, 1), (8, 12288, 4096, None), (20, 192, 520, 2), (64, 1024, 4096, 1),
+                                                  (33, 640, 1032, 4)])
+def test_gemm_tcgen05_with_swiglu_epilogue(m, inter, k, splits):
+    """Weights in blocks of 64 gate rows and their 64 up rows: the product's epilogue gives
+    silu(gate) * up, [m, inter], in float and rounded once."""
+    a = rnd((m, k), torch.bfloat16, 1.0, 1)
+    gate, up = rnd((inter, k), torch.bfloat16, 0.05, 2), rnd((inter, k), torch.bfloat16, 0.05, 3)
+    w = torch.stack([gate.view(inter // 64, 64, k), up.view(inter // 64, 64, k)], dim=1).reshape(2 * inter, k).contiguous()
+    g, u = a.double() @ gate.double().t(), a.double() @ up.double().t()
+    want = g * torch.sigmoid(g) * u
+    for cluster in (True, False):
+        for odt in (torch.bfloat16, torch.float32):
+            out = torch.full((m, inter), float("nan"), dtype=odt, device=DEV)
+            status = torch.zeros(1, dtype=torch.int32, device=DEV)
+            ops().gemm_tcgen05(a, w, out, status=status, splits=splits, cluster=cluster, swiglu=True)
+            assert status.item() == 0
+            tol = 1e-2 if odt == torch.bfloat16 else 2e-4
+            assert ((out.double() - want).abs() <= tol * (1 + want.abs())).all()
 
 
 def test_gemm_tcgen05_rows_do_not_depend_on_the_batch():

@@ -42,14 +42,31 @@ def test_rmsnorm_part():
     assert tiny.max_abs(xr.cpu(), want[[8, 2]]) < 1e-5
 
 
-def test_swiglu_part():
+@pytest.mark.parametrize("inner", [200, 192])   # 192: gate and up rows fused in blocks of 64
+def test_swiglu_part(inner):
     from rust_mlx_b200.parts.feedforward import SwiGLUFeedForward
-    ff = SwiGLUFeedForward("mlp", 72, 200)
+    ff = SwiGLUFeedForward("mlp", 72, inner)
     w = bind(ff, seed=2)
+    assert ff.block == (64 if inner % 64 == 0 else 0)
     x = torch.randn(11, 72, device=DEV)
     y = ff.forward(x)
     want = plain.swiglu_mlp(x.double().cpu(), {k.replace("mlp", "m"): v for k, v in w.items()}, "m", lambda t: t)
     assert tiny.max_abs(y.cpu(), want) < 1e-6
+
+
+def test_swiglu_part_bfloat16_takes_the_fused_product():
+    from rust_mlx_b200.kernels import ops
+    from rust_mlx_b200.parts.feedforward import SwiGLUFeedForward
+    ff = SwiGLUFeedForward("mlp", 256, 640)
+    w = bind(ff, seed=3, dtype=torch.bfloat16)
+    x = torch.randn(9, 256, device=DEV).to(torch.bfloat16)
+    assert ops.prefers_fused_swiglu(9, 1280, 256)
+    before = ops.launch_count
+    y = ff.forward(x)
+    assert ops.launch_count - before <= 2            # gate/up with SwiGLU in one kernel; no pointwise kernel
+    r = lambda t: t.to(torch.bfloat16).double()
+    want = plain.swiglu_mlp(x.double().cpu(), {k.replace("mlp", "m"): v for k, v in w.items()}, "m", r)
+    assert ((y.double().cpu() - want).abs() <= 1e-2 * (1 + want.abs())).all()
 
 
 def test_rotary_part_and_partial_rotation():
