@@ -221,6 +221,9 @@ def main():
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, prefill and e2e")
+    ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prefill only (for profiling it)")
+    ap.add_argument("--policy", default="auto", choices=["auto", "measured", "all", "none"],
+                    help="which products of few rows take the tcgen05 kernel (auto: time both when the engine starts)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -236,9 +239,11 @@ def main():
     from rust_mlx_b200.config import Qwen3Config
     from rust_mlx_b200.engine import Engine
 
+    from rust_mlx_b200.kernels import ops
+    ops.tcgen05_policy = a.policy
     raw = dict(QWEN3_8B, num_hidden_layers=a.layers)
     cfg = Qwen3Config.from_dict(raw)
-    biggest = 1 if a.no_points else max(64, a.batch)
+    biggest = 1 if (a.no_points or a.prefill_only) else max(64, a.batch)
     cache_tokens = max(biggest, a.batch) * (CONTEXT + 2 * PAGE + a.steps + a.warmup + 64)
     engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE,
                     max_requests=max(biggest, a.batch) + 2)
@@ -246,6 +251,13 @@ def main():
         grp.k_pool.normal_(0, 1)
         grp.v_pool.normal_(0, 1)
     pk = peaks()
+    if a.prefill_only:
+        pf_ms = time_prefill(engine, PREFILL_TOKENS)
+        flops = prefill_flops(raw, a.layers, PREFILL_TOKENS)
+        print(json.dumps({"prefill": {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                                      "ms": round(pf_ms, 3), "layers": a.layers,
+                                      "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}}))
+        return 0
 
     clocks = ClockSampler()
     ms, launches, clock_info = time_decode(engine, a.batch, a.steps, a.warmup, clocks)

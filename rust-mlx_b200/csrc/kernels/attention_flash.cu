@@ -381,12 +381,12 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
 }
 
 // ---------------------------------------------------------------------------------------------
-// Decoding with TMA: every tile has at most 16 rows (one or a few tokens by the heads of a group), so
-// the work is reading keys and values.  A fifth warp is the producer: one thread fetches a key tile
-// with a few tensor-map copies (cp.async.bulk.tensor, boxes of up to 64 rows by 64 columns, 128-byte
-// swizzle, completion on an mbarrier) into a ring of DSTAGES stages; the four computing warps each
-// take 16 of the tile's 64 keys, read them with ldmatrix at the swizzled places, and never spend an
-// instruction on addresses.  Built for head sizes 64 and 128 and pages of at least 8 positions.
+// The same attention with keys and values fetched by TMA, for head sizes 64 and 128 and pages of at least 8
+// positions.  A fifth warp is the producer: one thread fetches a key tile with a few tensor-map copies
+// (cp.async.bulk.tensor, boxes of up to 64 rows by 64 columns, 128-byte swizzle, completion on an mbarrier)
+// into a ring of stages; the four computing warps read the tiles with ldmatrix at the swizzled places and
+// never spend an instruction on addresses or wait for one another.  Both arrangements of the warps: rows
+// (prompt portions) and keys (decoding: every tile has at most 16 rows, the work is reading keys and values).
 constexpr int DSTAGES = 3;
 constexpr int DTHREADS = (NWARPS + 1) * 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
@@ -426,25 +426,28 @@ __device__ __forceinline__ const __nv_bfloat16* swz(const __nv_bfloat16* tile, i
     return tile + (col >> 6) * (64 * 64) + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3);
 }
 
-template <int HD>
-__global__ void __launch_bounds__(DTHREADS) attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
-                                                                       const __grid_constant__ CUtensorMap map_v,
-                                                                       const FlashParams p, int box_rows) {
+template <int HD, bool KEYSPLIT>
+__global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                const __grid_constant__ CUtensorMap map_v,
+                                                                const FlashParams p, int box_rows) {
     constexpr int STRIDE = HD + 8, CHUNKS = HD / 8, KSTEPS = HD / 16, DTILES = HD / 8;
+    constexpr int NT = KEYSPLIT ? 2 : BN / 8;              // score tiles of 8 keys per warp and key tile
+    constexpr int QROWS = KEYSPLIT ? 16 : BM;
+    constexpr int STAGES = KEYSPLIT ? DSTAGES : 2;         // decoding is bound by loads in flight, prompts by arithmetic
     constexpr int TILE_ELEMS = 64 * HD;                    // one key tile (or value tile)
     extern __shared__ unsigned char smem_decode_raw[];
     // the stages sit on a 1024-byte boundary, as the 128-byte swizzle asks
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_decode_raw) + 1023) & ~(uintptr_t)1023);
-    __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(base);                        // [DSTAGES][K tile | V tile]
-    __nv_bfloat16* Qs = KV + DSTAGES * 2 * TILE_ELEMS;                                 // [16][STRIDE]
-    __shared__ __align__(8) uint64_t full_bar[DSTAGES], empty_bar[DSTAGES];
-    __shared__ int s_failed;
+    __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(base);                        // [STAGES][K tile | V tile]
+    __nv_bfloat16* Qs = KV + STAGES * 2 * TILE_ELEMS;                                  // [QROWS][STRIDE]
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES];
+    __shared__ int s_failed, s_tile[3];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;   // one tile per sequence
+    const int kvh = blockIdx.y, split = blockIdx.z;
     if (tid == 0) {
         s_failed = 0;
-        for (int st = 0; st < DSTAGES; ++st) {
+        for (int st = 0; st < STAGES; ++st) {
             mbar_init(&full_bar[st], 1);
             mbar_init(&empty_bar[st], NWARPS);
         }
@@ -452,9 +455,53 @@ __global__ void __launch_bounds__(DTHREADS) attention_decode_tma_kernel(const __
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
     }
-    const int tok0 = p.q_start[seq], n_tok = p.q_start[seq + 1] - tok0;
+    int seq, tok0, n_tok;
+    if constexpr (KEYSPLIT) {   // one tile per sequence
+        seq = blockIdx.x;
+        tok0 = p.q_start[seq];
+        n_tok = p.q_start[seq + 1] - tok0;
+    } else {
+        // which sequence and which of its tiles this block has: the threads scan the sequences' tile counts together
+        __shared__ int s_warp_total[NWARPS + 1];
+        if (tid == 0) s_tile[0] = -1;
+        int before_all = 0;
+        for (int chunk = 0; chunk < p.n_seqs; chunk += DTHREADS) {
+            const int sq = chunk + tid;
+            int a = 0, n = 0, tiles = 0;
+            if (sq < p.n_seqs) {
+                a = p.q_start[sq];
+                n = p.q_start[sq + 1] - a;
+                tiles = (n + p.tq - 1) / p.tq;
+            }
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            __syncthreads();
+            if (lane == 31) s_warp_total[warp] = incl;
+            __syncthreads();
+            int before = before_all, total = 0;
+#pragma unroll
+            for (int w = 0; w < NWARPS + 1; ++w) {
+                if (w < warp) before += s_warp_total[w];
+                total += s_warp_total[w];
+            }
+            const int mine = (int)blockIdx.x - (before + incl - tiles);
+            if (tiles > 0 && mine >= 0 && mine < tiles) {
+                s_tile[0] = sq;
+                s_tile[1] = a + mine * p.tq;
+                s_tile[2] = min(p.tq, n - mine * p.tq);
+            }
+            before_all += total;
+        }
+        __syncthreads();
+        seq = s_tile[0]; tok0 = s_tile[1]; n_tok = s_tile[2];
+        if (seq < 0) return;  // the grid is an upper bound
+    }
     const int pos0 = p.positions[tok0];
-    const int rows_valid = n_tok * p.group;                 // at most 16
+    const int rows_valid = n_tok * p.group;
     const int* table = p.block_table + (size_t)seq * p.table_stride;
     const int lo_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int pos_last = pos0 + n_tok - 1;
@@ -466,14 +513,14 @@ __global__ void __launch_bounds__(DTHREADS) attention_decode_tma_kernel(const __
 
     // Q rows (zeros beyond the tile's rows); the stages start as zeros so that a part of a tile that is never
     // fetched (a page the request does not hold) has finite numbers in it
-    for (int idx = tid; idx < 16 * CHUNKS; idx += DTHREADS) {
+    for (int idx = tid; idx < QROWS * CHUNKS; idx += DTHREADS) {
         const int r = idx / CHUNKS, c = idx - r * CHUNKS;
         const bool valid = r < rows_valid;
         const int tok = valid ? r / p.group : 0, g = valid ? r - tok * p.group : 0;
         cp_async16(Qs + r * STRIDE + c * 8, p.q + ((size_t)(tok0 + tok) * p.nq + kvh * p.group + g) * HD + c * 8, valid);
     }
     cp_async_commit();
-    for (int idx = tid; idx < DSTAGES * 2 * TILE_ELEMS / 8; idx += DTHREADS)
+    for (int idx = tid; idx < STAGES * 2 * TILE_ELEMS / 8; idx += DTHREADS)
         reinterpret_cast<uint4*>(KV)[idx] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     cp_async_wait<0>();
@@ -484,7 +531,7 @@ __global__ void __launch_bounds__(DTHREADS) attention_decode_tma_kernel(const __
             // ---- producer: per tile, 64 / box_rows boxes of rows by HD / 64 boxes of columns, for K and for V
             const int boxes = BN / box_rows;
             for (int i = 0; i < n_mine; ++i) {
-                const int st = i % DSTAGES, round = i / DSTAGES, kt = kt_begin + i;
+                const int st = i % STAGES, round = i / STAGES, kt = kt_begin + i;
                 if (round > 0 && !mbar_wait(&empty_bar[st], (round - 1) & 1)) { atomicExch(&s_failed, 1); break; }
                 uint32_t bytes = 0;
                 for (int b = 0; b < boxes; ++b) {
@@ -513,13 +560,17 @@ __global__ void __launch_bounds__(DTHREADS) attention_decode_tma_kernel(const __
         __syncwarp();
     }
 
-    // ---- computing warps: the same 16 rows, 16 keys of every tile each
-    const int key_base = (warp & 3) * 16;
+    // ---- computing warps.  Rows: each warp owns 16 of the tile's rows and all 64 keys.  Keys (KEYSPLIT): the same
+    // 16 rows in every warp, 16 of the 64 keys each.
+    const int cw = warp & 3;
+    const int row_base = KEYSPLIT ? 0 : cw * 16;
+    const int key_base = KEYSPLIT ? cw * 16 : 0;
+    const bool warp_active = warp < NWARPS && row_base < rows_valid;
     int row_pos[2], row_lo[2];
     bool row_ok[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const int r = (lane >> 2) + 8 * i;
+        const int r = row_base + (lane >> 2) + 8 * i;
         row_ok[i] = r < rows_valid;
         row_pos[i] = pos0 + (row_ok[i] ? r / p.group : 0);
         row_lo[i] = p.window > 0 ? max(0, row_pos[i] - p.window + 1) : 0;
@@ -527,94 +578,100 @@ __global__ void __launch_bounds__(DTHREADS) attention_decode_tma_kernel(const __
     uint32_t qf[KSTEPS][4];
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; ++kk)
-        ldmatrix_x4(qf[kk], Qs + (lane & 15) * STRIDE + kk * 16 + (lane >> 4) * 8);
+        ldmatrix_x4(qf[kk], Qs + (row_base + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
     float o[DTILES][4];
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     for (int i = 0; i < n_mine && warp < NWARPS; ++i) {
-        const int kt = kt_begin + i, stage = i % DSTAGES;
-        if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], (i / DSTAGES) & 1))) { atomicExch(&s_failed, 1); break; }
-        const __nv_bfloat16* kbase = KV + stage * 2 * TILE_ELEMS;
-        const __nv_bfloat16* vbase = kbase + TILE_ELEMS;
-        float s[2][4];
+        const int kt = kt_begin + i, stage = i % STAGES;
+        if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], (i / STAGES) & 1))) { atomicExch(&s_failed, 1); break; }
+        if (warp_active) {
+            const __nv_bfloat16* kbase = KV + stage * 2 * TILE_ELEMS;
+            const __nv_bfloat16* vbase = kbase + TILE_ELEMS;
+            float s[NT][4];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk) {
-            uint32_t kf[4];
-            const int key = key_base + (lane & 7) + ((lane >> 4) << 3);
-            const int dcol = kk * 16 + ((lane >> 3) & 1) * 8;
-            ldmatrix_x4(kf, swz<HD>(kbase, key, dcol));
-            mma_bf16(s[0], qf[kk], kf[0], kf[1]);
-            mma_bf16(s[1], qf[kk], kf[2], kf[3]);
-        }
-        float mx[2] = {-INFINITY, -INFINITY};
-        bool any_masked = false;
+            for (int kk = 0; kk < KSTEPS; ++kk) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int r = e >> 1;
-                const int kp = kt * BN + key_base + j * 8 + (lane & 3) * 2 + (e & 1);
-                const bool ok = row_ok[r] && kp <= row_pos[r] && kp >= row_lo[r];
-                any_masked |= kp > pos_last;
-                s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
-                mx[r] = fmaxf(mx[r], s[j][e]);
-            }
-        }
-        float corr[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m[r], mx[r]);
-            corr[r] = m_new == -INFINITY ? 1.f : exp2f(m[r] - m_new);
-            m[r] = m_new;
-            l[r] *= corr[r];
-        }
-        const float mref[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float pv = exp2f(s[j][e] - mref[e >> 1]);
-                s[j][e] = pv;
-                l[e >> 1] += pv;
-            }
-        }
-#pragma unroll
-        for (int d = 0; d < DTILES; ++d) {
-            o[d][0] *= corr[0]; o[d][1] *= corr[0];
-            o[d][2] *= corr[1]; o[d][3] *= corr[1];
-        }
-        uint32_t pf[4];
-        pf[0] = pack_bf16(s[0][0], s[0][1]);
-        pf[1] = pack_bf16(s[0][2], s[0][3]);
-        pf[2] = pack_bf16(s[1][0], s[1][1]);
-        pf[3] = pack_bf16(s[1][2], s[1][3]);
-        // positions past the sequence's end lie in a fetched page but were never written: whatever is there
-        // must not reach the sum, not even multiplied by zero
-        const bool tail = __any_sync(0xffffffffu, any_masked);
-#pragma unroll
-        for (int dp = 0; dp < DTILES / 2; ++dp) {
-            uint32_t vf[4];
-            const int key = key_base + (lane & 7) + ((lane >> 3) & 1) * 8;
-            const int dcol = dp * 16 + (lane >> 4) * 8;
-            ldmatrix_x4_trans(vf, swz<HD>(vbase, key, dcol));
-            if (tail) {
-                // value fragment registers hold keys key_base + 2 * (lane % 4) + {0, 1} (+ 8 for the odd registers)
-                const int k0 = kt * BN + key_base + (lane & 3) * 2;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int ka = k0 + (q & 1) * 8;
-                    if (ka > pos_last) vf[q] &= 0xffff0000u;
-                    if (ka + 1 > pos_last) vf[q] &= 0x0000ffffu;
+                for (int jp = 0; jp < NT / 2; ++jp) {
+                    uint32_t kf[4];
+                    const int key = key_base + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
+                    const int dcol = kk * 16 + ((lane >> 3) & 1) * 8;
+                    ldmatrix_x4(kf, swz<HD>(kbase, key, dcol));
+                    mma_bf16(s[2 * jp], qf[kk], kf[0], kf[1]);
+                    mma_bf16(s[2 * jp + 1], qf[kk], kf[2], kf[3]);
                 }
             }
-            mma_bf16(o[2 * dp], pf, vf[0], vf[1]);
-            mma_bf16(o[2 * dp + 1], pf, vf[2], vf[3]);
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int r = e >> 1;
+                    const int kp = kt * BN + key_base + j * 8 + (lane & 3) * 2 + (e & 1);
+                    const bool ok = row_ok[r] && kp <= row_pos[r] && kp >= row_lo[r];
+                    s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+                    mx[r] = fmaxf(mx[r], s[j][e]);
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m[r], mx[r]);
+                corr[r] = m_new == -INFINITY ? 1.f : exp2f(m[r] - m_new);
+                m[r] = m_new;
+                l[r] *= corr[r];
+            }
+            const float mref[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = exp2f(s[j][e] - mref[e >> 1]);
+                    s[j][e] = pv;
+                    l[e >> 1] += pv;
+                }
+            }
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d) {
+                o[d][0] *= corr[0]; o[d][1] *= corr[0];
+                o[d][2] *= corr[1]; o[d][3] *= corr[1];
+            }
+            // positions past the sequence's end lie in a fetched page but were never written: whatever is there
+            // must not reach the sum, not even multiplied by zero.  Only the tile that holds the end has such keys.
+            const bool tail = kt * BN + BN - 1 > pos_last;
+#pragma unroll
+            for (int kk = 0; kk < NT / 2; ++kk) {
+                uint32_t pf[4];
+                pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pf[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pf[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < DTILES / 2; ++dp) {
+                    uint32_t vf[4];
+                    const int key = key_base + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    const int dcol = dp * 16 + (lane >> 4) * 8;
+                    ldmatrix_x4_trans(vf, swz<HD>(vbase, key, dcol));
+                    if (tail) {
+                        // a value register holds keys k0 + {0, 1}; the odd registers the keys 8 further on
+                        const int k0 = kt * BN + key_base + kk * 16 + (lane & 3) * 2;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int ka = k0 + (q & 1) * 8;
+                            if (ka > pos_last) vf[q] &= 0xffff0000u;
+                            if (ka + 1 > pos_last) vf[q] &= 0x0000ffffu;
+                        }
+                    }
+                    mma_bf16(o[2 * dp], pf, vf[0], vf[1]);
+                    mma_bf16(o[2 * dp + 1], pf, vf[2], vf[3]);
+                }
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[stage]);
@@ -626,7 +683,41 @@ __global__ void __launch_bounds__(DTHREADS) attention_decode_tma_kernel(const __
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     }
     if (tid == 0 && s_failed) atomicExch(p.status, 3);
-    // combine the four warps' partial results in warp order
+
+    if constexpr (!KEYSPLIT) {
+        if (!warp_active) return;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = row_base + (lane >> 2) + 8 * i;
+            if (!row_ok[i]) continue;
+            const int tok = r / p.group, g = r - tok * p.group;
+            const size_t row = (size_t)(tok0 + tok) * p.nq + kvh * p.group + g;
+            if (p.n_splits == 1) {
+                const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+                __nv_bfloat16* dst = p.out + row * HD;
+#pragma unroll
+                for (int d = 0; d < DTILES; ++d) {
+                    const int col = d * 8 + (lane & 3) * 2;
+                    *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(o[d][2 * i] * inv, o[d][2 * i + 1] * inv);
+                }
+            } else {
+                const size_t prow = (size_t)split * p.n_tokens * p.nq + row;
+                float* dst = p.part_o + prow * HD;
+#pragma unroll
+                for (int d = 0; d < DTILES; ++d) {
+                    const int col = d * 8 + (lane & 3) * 2;
+                    *reinterpret_cast<float2*>(dst + col) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+                }
+                if ((lane & 3) == 0) {
+                    p.part_ml[prow * 2] = m[i];
+                    p.part_ml[prow * 2 + 1] = l[i];
+                }
+            }
+        }
+        return;
+    }
+
+    // KEYSPLIT: combine the four warps' partial results in warp order
     float* so = reinterpret_cast<float*>(KV);             // [NWARPS][16][HD]
     float* sml = so + NWARPS * 16 * HD;                   // [NWARPS][16][2]
     __syncthreads();
@@ -792,23 +883,29 @@ int pool_map(CUtensorMap* map, const void* base, long long rows, int hd, int box
     return 0;
 }
 
-template <int HD>
-int launch_decode_tma(const FlashParams& p, long long pool_rows, cudaStream_t s) {
+template <int HD, bool KEYSPLIT>
+int launch_tma_as(const FlashParams& p, int n_tiles, long long pool_rows, cudaStream_t s) {
     const int box_rows = p.page_size < BN ? p.page_size : BN;
     CUtensorMap mk, mv;
     if (pool_map(&mk, p.k_pool, pool_rows, HD, box_rows) != 0) return -1;
     if (pool_map(&mv, p.v_pool, pool_rows, HD, box_rows) != 0) return -1;
-    constexpr size_t smem = 1024 + (size_t)DSTAGES * 2 * 64 * HD * 2 + (size_t)16 * (HD + 8) * 2;
+    constexpr int QROWS = KEYSPLIT ? 16 : BM, STAGES = KEYSPLIT ? DSTAGES : 2;
+    constexpr size_t smem = 1024 + (size_t)STAGES * 2 * 64 * HD * 2 + (size_t)QROWS * (HD + 8) * 2;
     static bool raised = false;
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) RMX_FAIL("attention_decode: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
+        cudaError_t e = cudaFuncSetAttribute(attention_tma_kernel<HD, KEYSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RMX_FAIL("attention_tma: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
-    dim3 grid(p.n_seqs, p.nkv, p.n_splits);
-    attention_decode_tma_kernel<HD><<<grid, DTHREADS, smem, s>>>(mk, mv, p, box_rows);
-    RMX_CHECK_LAUNCH("attention_decode");
+    dim3 grid(n_tiles, p.nkv, p.n_splits);
+    attention_tma_kernel<HD, KEYSPLIT><<<grid, DTHREADS, smem, s>>>(mk, mv, p, box_rows);
+    RMX_CHECK_LAUNCH("attention_tma");
     return 0;
+}
+
+template <int HD>
+int launch_tma(const FlashParams& p, int n_tiles, bool keysplit, long long pool_rows, cudaStream_t s) {
+    return keysplit ? launch_tma_as<HD, true>(p, n_tiles, pool_rows, s) : launch_tma_as<HD, false>(p, n_tiles, pool_rows, s);
 }
 }  // namespace
 
@@ -849,13 +946,13 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     // every tile has at most 16 rows (decoding, or very short portions): spread keys over the warps
     const bool keysplit = max_q_len > 0 && max_q_len * group <= 16;
     int rc;
-    // decoding at the head sizes of real models: keys and values come by TMA (pool_pages tells the pool's extent)
-    if (keysplit && pool_pages > 0 && page_size >= 8 && (hd == 64 || hd == 128) && n_tiles == n_seqs &&
+    // at the head sizes of real models keys and values come by TMA (pool_pages tells the pool's extent)
+    if (pool_pages > 0 && page_size >= 8 && (hd == 64 || hd == 128) && (!keysplit || n_tiles == n_seqs) &&
         ((uintptr_t)k_pool & 127) == 0 && ((uintptr_t)v_pool & 127) == 0) {
         const long long pool_rows = (long long)pool_pages * nkv * page_size;
-        p.counters = counters;   // with counters the kernel combines its splits itself
-        rc = hd == 64 ? launch_decode_tma<64>(p, pool_rows, s) : launch_decode_tma<128>(p, pool_rows, s);
-        if (rc == 0 && counters) return 0;
+        if (keysplit) p.counters = counters;   // with counters the decoding arrangement combines its splits itself
+        rc = hd == 64 ? launch_tma<64>(p, n_tiles, keysplit, pool_rows, s) : launch_tma<128>(p, n_tiles, keysplit, pool_rows, s);
+        if (rc == 0 && keysplit && counters) return 0;
     } else
     switch (hd) {
         case 16: rc = launch_flash<16>(p, n_tiles, keysplit, s); break;
