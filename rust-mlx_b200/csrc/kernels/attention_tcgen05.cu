@@ -1,0 +1,584 @@
+// Attention for prompt portions on the Blackwell tensor cores (tcgen05), head size 128, bfloat16.
+//
+// A block takes one kv head and one tile of 128 query rows of one sequence; a row is a (token, query
+// head of the group) pair, 128 / group tokens by `group` heads, so the heads that share a kv head share
+// every key and value tile.  Keys are visited in tiles of 64 aligned to absolute positions.
+//
+// A block takes two neighbouring tiles, which share every key and value tile it fetches.
+//
+//   warp 0   producer: Q once and then K/V tiles by TMA (tensor-map boxes, 128-byte swizzle) into a ring
+//   warp 1   issues the MMAs: S = Q K^T into tensor memory (two buffers per query tile: the next key tile's
+//            scores are formed while the softmax warps work on this one's), later O += P V
+//   warps 2-5 and 6-9  softmax of the first and the second query tile: every thread owns one row (one lane
+//            of tensor memory): it reads its 64 scores, masks where the tile touches the diagonal or the
+//            window's edge, keeps the running maximum and sum in float, writes its probabilities as bfloat16
+//            into shared memory for the second MMA, and rescales its row of O when the maximum moved
+//
+// S and O live in tensor memory (2 x 64 + 128 columns).  Tiles late in a sequence see more keys: they are
+// handed out first, so that the longest blocks do not run last.  V is used as it lies in the cache, [key][d], through an
+// MN-major operand descriptor.  Every wait on a barrier is bounded: a block that gives up records status 3,
+// frees its tensor memory and ends.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+constexpr int HD = 128, BM = 128, BN = 64;
+constexpr int STAGES = 3;
+constexpr int THREADS = 320;   // producer, MMA issuer, 4 softmax warps for each of the block's two query tiles
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr int Q_BYTES = BM * HD * 2;        // 32 KB: two boxes of [128 rows][64 columns]
+constexpr int KV_BYTES = BN * HD * 2;       // 16 KB per key tile, the same per value tile
+constexpr int P_BYTES = BM * BN * 2;        // 16 KB
+constexpr int TILE_COLS = 256;              // per query tile: S (two buffers) in columns 0..63 and 64..127, O in 128..255
+constexpr int TMEM_COLS = 512;              // two query tiles: all of an SM's tensor memory
+constexpr int O_COL = 128;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_3d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// Operand descriptors for tiles with the 128-byte swizzle.  K-major: rows of 128 bytes (64 elements of the
+// reduction), groups of 8 rows 1024 bytes apart.  MN-major: rows of 128 bytes hold 64 elements of the M/N
+// side, 8 rows (steps of the reduction) per 1024-byte group; `lbo` is the distance between blocks of 64
+// M/N elements, `sbo` between groups of 8 reduction steps.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// bfloat16 x bfloat16 -> float, M = 128; b_mn: the B operand is MN-major.
+__device__ __forceinline__ uint32_t idesc(int n, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t id, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "r"((uint32_t)accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+// 2^x on the special-function unit (x <= 0 here; -inf gives 0).
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct Params {
+    __nv_bfloat16* out;        // [tokens, nq, HD]
+    const int* q_start;        // [seqs + 1]
+    const int* positions;      // [tokens]
+    const int* block_table;    // [seqs, table_stride]
+    int* status;
+    int n_seqs, nq, nkv, group, tq, table_stride, page_size, page_shift, window, box_rows;
+    float scale_log2;
+};
+
+// One block: two neighbouring query tiles (A and B, 128 rows each) of one sequence against one kv head.  Both use
+// every key and value tile the block fetches, and while the softmax warps of one tile work the tensor cores
+// serve the other.
+__global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                   const __grid_constant__ CUtensorMap map_k,
+                                                                   const __grid_constant__ CUtensorMap map_v,
+                                                                   const Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_smem = base;                               // [2 tiles][2 boxes][128 rows][128 B]
+    unsigned char* kv_smem = q_smem + 2 * Q_BYTES;              // [STAGES][K tile | V tile], each [2 boxes][64 rows][128 B]
+    unsigned char* p_smem = kv_smem + STAGES * 2 * KV_BYTES;    // [2 tiles][128 rows][128 B]
+    __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2][2], p_full[2], o_done[2];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int s_failed, s_tile[3], s_warp_total[THREADS / 32];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.y;
+    if (tid == 0) {
+        s_failed = 0;
+        mbar_init(&q_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&s_full[t][0], 1);
+            mbar_init(&s_full[t][1], 1);
+            mbar_init(&p_full[t], 128);
+            mbar_init(&o_done[t], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
+        s_tile[0] = -1;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_smem)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    // which sequence and which pair of its tiles this block has: pairs are counted sequence by sequence, and handed
+    // out from the last to the first (tiles late in a sequence see the most keys)
+    {
+        const int pair_tokens = 2 * p.tq;
+        int before_all = 0;
+        for (int chunk = 0; chunk < p.n_seqs; chunk += THREADS) {
+            const int sq = chunk + tid;
+            int a = 0, n = 0, pairs = 0;
+            if (sq < p.n_seqs) {
+                a = p.q_start[sq];
+                n = p.q_start[sq + 1] - a;
+                pairs = (n + pair_tokens - 1) / pair_tokens;
+            }
+            int incl = pairs;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            __syncthreads();
+            if (lane == 31) s_warp_total[warp] = incl;
+            __syncthreads();
+            int before = before_all, total = 0;
+#pragma unroll
+            for (int w = 0; w < THREADS / 32; ++w) {
+                if (w < warp) before += s_warp_total[w];
+                total += s_warp_total[w];
+            }
+            const int mine = (int)(gridDim.x - 1 - blockIdx.x) - (before + incl - pairs);
+            if (pairs > 0 && mine >= 0 && mine < pairs) {
+                s_tile[0] = sq;
+                s_tile[1] = a + mine * pair_tokens;
+                s_tile[2] = min(pair_tokens, n - mine * pair_tokens);
+            }
+            before_all += total;
+        }
+    }
+    // the key and value stages start as zeros: a part of a tile that is never fetched (beyond the sequence's end, a
+    // page the request does not hold) must hold finite numbers, because a probability of zero still multiplies it
+    for (int idx = tid; idx < STAGES * 2 * KV_BYTES / 16; idx += THREADS)
+        reinterpret_cast<uint4*>(kv_smem)[idx] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = tmem_base_smem;
+    const int seq = s_tile[0], tok0 = s_tile[1], n_tok = s_tile[2];
+    int n_kt = 0, kt_lo = 0, pos0 = 0, pos_last = 0, lo_first = 0;
+    const int* table = nullptr;
+    if (seq >= 0) {
+        pos0 = p.positions[tok0];
+        table = p.block_table + (size_t)seq * p.table_stride;
+        lo_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+        pos_last = pos0 + n_tok - 1;
+        kt_lo = lo_first / BN;
+        n_kt = pos_last / BN - kt_lo + 1;
+    }
+    const bool two = n_tok > p.tq;   // the second tile has rows
+
+    if (warp == 0 && lane == 0 && seq >= 0) {
+        // ---- producer
+        mbar_expect_tx(&q_full, two ? 2 * Q_BYTES : Q_BYTES);
+        for (int t = 0; t < (two ? 2 : 1); ++t) {
+            tma_3d(q_smem + t * Q_BYTES, &map_q, &q_full, 0, kvh * p.group, tok0 + t * p.tq);
+            tma_3d(q_smem + t * Q_BYTES + Q_BYTES / 2, &map_q, &q_full, 64, kvh * p.group, tok0 + t * p.tq);
+        }
+        const int boxes = BN / p.box_rows;
+        for (int i = 0; i < n_kt; ++i) {
+            const int st = i % STAGES, round = i / STAGES, kt = kt_lo + i;
+            if (round > 0 && !mbar_wait(&kv_empty[st], (round - 1) & 1)) { atomicExch(&s_failed, 1); break; }
+            uint32_t bytes = 0;
+            for (int b = 0; b < boxes; ++b) {
+                const int kp = kt * BN + b * p.box_rows;
+                if (kp > pos_last || kp + p.box_rows <= lo_first) continue;
+                if (table[kp >> p.page_shift] >= 0) bytes += 2u * p.box_rows * HD * 2u;
+                else atomicExch(p.status, 2);
+            }
+            mbar_expect_tx(&kv_full[st], bytes);
+            unsigned char* kd = kv_smem + st * 2 * KV_BYTES;
+            unsigned char* vd = kd + KV_BYTES;
+            for (int b = 0; b < boxes; ++b) {
+                const int kp = kt * BN + b * p.box_rows;
+                if (kp > pos_last || kp + p.box_rows <= lo_first) continue;
+                const int page = table[kp >> p.page_shift];
+                if (page < 0) continue;
+                const int row = (page * p.nkv + kvh) * p.page_size + (kp & (p.page_size - 1));
+#pragma unroll
+                for (int cb = 0; cb < 2; ++cb) {
+                    tma_2d(kd + cb * (KV_BYTES / 2) + b * p.box_rows * 128, &map_k, &kv_full[st], cb * 64, row);
+                    tma_2d(vd + cb * (KV_BYTES / 2) + b * p.box_rows * 128, &map_v, &kv_full[st], cb * 64, row);
+                }
+            }
+        }
+    } else if (warp == 1 && lane == 0 && seq >= 0) {
+        // ---- MMA issuer
+        const uint32_t id_s = idesc(BN, false), id_o = idesc(HD, true);
+        const int n_t = two ? 2 : 1;
+        // S = Q K^T of key tile i for query tile t into its score buffer i & 1: the reduction runs over d, 8 steps of
+        // 16; d 0..63 lie in the first box of a tile, 64..127 in the second
+        auto scores = [&](int t, int i) {
+            const uint32_t q_addr = smem_u32(q_smem + t * Q_BYTES);
+            const uint32_t k_addr = smem_u32(kv_smem + (i % STAGES) * 2 * KV_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                const uint32_t qa = q_addr + (kk >> 2) * (Q_BYTES / 2) + (kk & 3) * 32;
+                const uint32_t ka = k_addr + (kk >> 2) * (KV_BYTES / 2) + (kk & 3) * 32;
+                umma(tmem + t * TILE_COLS + (i & 1) * BN, desc_kmajor(qa), desc_kmajor(ka), id_s, kk > 0);
+            }
+            umma_commit(&s_full[t][i & 1]);
+        };
+        bool ok = mbar_wait(&q_full, 0);
+        if (ok && n_kt > 0) {
+            ok = mbar_wait(&kv_full[0], 0);
+            if (ok) {
+                fence_after();
+                for (int t = 0; t < n_t; ++t) scores(t, 0);
+            }
+        }
+        for (int i = 0; i < n_kt && ok; ++i) {
+            const int st = i % STAGES;
+            const bool more = i + 1 < n_kt;
+            if (more) {
+                if (!mbar_wait(&kv_full[(i + 1) % STAGES], ((i + 1) / STAGES) & 1)) { ok = false; break; }
+                fence_after();
+            }
+            const uint32_t v_addr = smem_u32(kv_smem + st * 2 * KV_BYTES) + KV_BYTES;
+            for (int t = 0; t < n_t && ok; ++t) {
+                // the next key tile's scores for this query tile are formed while its softmax warps work on this one's
+                // (that buffer is free: the probabilities of tile i - 1 were made from it before the last O += P V)
+                if (more) scores(t, i + 1);
+                if (!mbar_wait(&p_full[t], i & 1)) { ok = false; break; }
+                fence_after();
+                // O += P V: the reduction runs over the tile's 64 keys, 4 steps of 16; V is [key][d], MN-major:
+                // blocks of 64 d are 8 KB apart, groups of 8 keys 1 KB
+                const uint32_t p_addr = smem_u32(p_smem + t * P_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk)
+                    umma(tmem + t * TILE_COLS + O_COL, desc_kmajor(p_addr + kk * 32),
+                         desc_mnmajor(v_addr + kk * 2048, KV_BYTES / 2, 1024), id_o, i > 0 || kk > 0);
+                umma_commit(&o_done[t]);
+            }
+            umma_commit(&kv_empty[st]);   // both query tiles are done with this stage once these MMAs have finished
+        }
+        if (!ok) atomicExch(&s_failed, 1);
+    } else if (warp >= 2 && seq >= 0 && (warp < 6 || two)) {
+        // ---- softmax of query tile t: thread owns row r of the tile = lane r of tensor memory
+        const int t = warp < 6 ? 0 : 1;
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16) + t * TILE_COLS;
+        const int tile_tok0 = tok0 + t * p.tq;
+        const int tile_tokens = min(p.tq, n_tok - t * p.tq);
+        const int rows_valid = tile_tokens * p.group;
+        const bool row_ok = r < rows_valid;
+        const int tok = row_ok ? r / p.group : 0;
+        const int row_pos = pos0 + t * p.tq + tok;
+        const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
+        unsigned char* p_tile = p_smem + t * P_BYTES;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_kt; ++i) {
+            const int kt = kt_lo + i;
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t][i & 1], (i >> 1) & 1));
+            if (!ok) break;
+            fence_after();
+            float s[BN];
+#pragma unroll
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(lane_addr + (i & 1) * BN + c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) s[c + j] = __uint_as_float(v[j]);
+            }
+            // a tile that every row of this warp sees whole (below the diagonal, inside the window) needs no mask:
+            // the maximum is taken over the raw scores and the scale goes into the exponent's multiply-add
+            const bool whole = __all_sync(0xffffffffu, row_ok && kt * BN + BN - 1 <= row_pos && kt * BN >= row_lo);
+            float mx = -INFINITY;
+            if (whole) {
+#pragma unroll
+                for (int j = 0; j < BN; ++j) mx = fmaxf(mx, s[j]);
+                mx *= p.scale_log2;
+            } else {
+#pragma unroll
+                for (int j = 0; j < BN; ++j) {
+                    const int kp = kt * BN + j;
+                    const bool seen = row_ok && kp <= row_pos && kp >= row_lo;
+                    s[j] = seen ? s[j] : -INFINITY;
+                    mx = fmaxf(mx, s[j]);
+                }
+                mx = mx == -INFINITY ? mx : mx * p.scale_log2;
+            }
+            const float m_new = fmaxf(m, mx);
+            const float corr = m_new == -INFINITY ? 1.f : ex2(m - m_new);
+            const float neg_ref = m_new == -INFINITY ? 0.f : -m_new;
+            m = m_new;
+            float sum = 0.f;
+            uint32_t pk[BN / 2];
+#pragma unroll
+            for (int j = 0; j < BN; j += 2) {
+                const float a = ex2(fmaf(s[j], p.scale_log2, neg_ref)), b = ex2(fmaf(s[j + 1], p.scale_log2, neg_ref));
+                sum += a + b;
+                pk[j / 2] = pack_bf16(a, b);
+            }
+            l = l * corr + sum;
+            if (i > 0) {
+                // the MMA that used the last probabilities and added into O has finished
+                ok = __all_sync(0xffffffffu, mbar_wait(&o_done[t], (i - 1) & 1));
+                if (!ok) break;
+                fence_after();
+                if (__any_sync(0xffffffffu, corr != 1.f)) {   // the maximum of some row of this warp moved: rescale O
+#pragma unroll
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(lane_addr + O_COL + c, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+                        tmem_st32(lane_addr + O_COL + c, v);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // probabilities of this row: 64 bfloat16 = one 128-byte row with its 16-byte chunks swizzled
+            unsigned char* prow = p_tile + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            // positions past the sequence's end lie in a fetched page but were never written: their values must
+            // not reach the sum, not even multiplied by zero.  Only the tile that holds the end has such keys; the
+            // first query tile's warps clear them (both tiles' MMAs wait for these warps' arrival or come after it).
+            if (t == 0 && kt * BN + BN - 1 > pos_last) {
+                unsigned char* vd = kv_smem + (i % STAGES) * 2 * KV_BYTES + KV_BYTES;
+                const int first_bad = pos_last + 1 - kt * BN;
+                for (int idx = quad * 32 + lane; idx < (BN - first_bad) * 16; idx += 128) {
+                    const int row = first_bad + idx / 16, c = idx % 16;   // 16 chunks of 16 bytes per row: two boxes of 8
+                    *reinterpret_cast<uint4*>(vd + (c >> 3) * (KV_BYTES / 2) + row * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            fence_before();
+            mbar_arrive(&p_full[t]);
+        }
+        if (ok && n_kt > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&o_done[t], (n_kt - 1) & 1));
+            if (ok) {
+                fence_after();
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                const int g = r - tok * p.group;
+                __nv_bfloat16* dst = p.out + ((size_t)(tile_tok0 + tok) * p.nq + kvh * p.group + g) * HD;
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_addr + O_COL + c, v);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 o4;
+                            o4.x = pack_bf16(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv);
+                            o4.y = pack_bf16(__uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv);
+                            o4.z = pack_bf16(__uint_as_float(v[j + 4]) * inv, __uint_as_float(v[j + 5]) * inv);
+                            o4.w = pack_bf16(__uint_as_float(v[j + 6]) * inv, __uint_as_float(v[j + 7]) * inv);
+                            *reinterpret_cast<uint4*>(dst + c + j) = o4;
+                        }
+                    }
+                }
+            }
+        }
+        if (!ok) atomicExch(&s_failed, 1);
+    }
+    __syncwarp();
+    fence_before();
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
+    if (tid == 0 && s_failed) atomicExch(p.status, 3);
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)ptr;
+    }
+    return fn;
+}
+
+struct MapKey {
+    const void* base;
+    long long a, b;
+    int c, d;
+    bool operator==(const MapKey& o) const { return base == o.base && a == o.a && b == o.b && c == o.c && d == o.d; }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.base) ^ (std::hash<long long>()(k.a) * 31) ^ (std::hash<long long>()(k.b) * 131) ^
+               (size_t)(k.c * 7 + k.d);
+    }
+};
+std::mutex g_lock;
+std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;
+
+// A pool of one layer as [rows, 128] bfloat16; boxes of [box_rows, 64].
+int pool_map(CUtensorMap* map, const void* base, long long rows, int box_rows) {
+    std::lock_guard<std::mutex> guard(g_lock);
+    const MapKey key{base, rows, 0, box_rows, 2};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *map = it->second; return 0; }
+    EncodeTiled fn = encoder();
+    if (!fn) RMX_FAIL("attention_tcgen05: the driver has no cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) RMX_FAIL("attention_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, *map);
+    return 0;
+}
+
+// The queries [tokens, nq, 128]; boxes of [tq tokens, group heads, 64]: a tile's rows come out token by token, the
+// group's heads side by side.
+int q_map(CUtensorMap* map, const void* base, long long tokens, int nq, int group, int tq) {
+    std::lock_guard<std::mutex> guard(g_lock);
+    const MapKey key{base, tokens, nq, group, 3};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *map = it->second; return 0; }
+    EncodeTiled fn = encoder();
+    if (!fn) RMX_FAIL("attention_tcgen05: the driver has no cuTensorMapEncodeTiled");
+    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nq, (cuuint64_t)tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)nq * HD * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)group, (cuuint32_t)tq};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) RMX_FAIL("attention_tcgen05: cuTensorMapEncodeTiled (queries) failed with code %d", (int)r);
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, *map);
+    return 0;
+}
+}  // namespace
+
+// Head size 128, a group that divides 128, pages of at least 8 positions (a power of two).
+RMX_API int rmx_attention_tcgen05_supports(int hd, int group, int page_size) {
+    return hd == 128 && group >= 1 && group <= 16 && (group & (group - 1)) == 0 && page_size >= 8 &&
+           (page_size & (page_size - 1)) == 0;
+}
+
+RMX_API int rmx_attention_tcgen05_tile_tokens(int group) { return BM / group; }
+
+// n_tiles: the number of blocks: sum over sequences of ceil(tokens / (2 * 128 / group)) (a block takes two tiles).  pool_pages: pages in k_pool / v_pool.
+RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* q_start,
+                                  const int* positions, const int* block_table, int table_stride, int page_size,
+                                  void* out, int n_seqs, int n_tokens, int n_tiles, int nq, int nkv, int hd, int window,
+                                  float scale, int pool_pages, int* status, void* stream) {
+    if (n_tokens == 0) return 0;
+    RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tcgen05: %d query heads over %d kv heads", nq, nkv);
+    const int group = nq / nkv;
+    RMX_REQUIRE(rmx_attention_tcgen05_supports(hd, group, page_size),
+                "attention_tcgen05: head_dim %d, group %d, page size %d is not built", hd, group, page_size);
+    RMX_REQUIRE(table_stride > 0 && window >= 0 && n_tiles > 0 && n_seqs > 0 && pool_pages > 0 && nkv <= 65535,
+                "attention_tcgen05: bad geometry");
+    RMX_REQUIRE(scale > 0.f, "attention_tcgen05: the scale must be positive (the maximum is taken before scaling)");
+    RMX_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pool & 127) == 0 && ((uintptr_t)v_pool & 127) == 0,
+                "attention_tcgen05: operands must be aligned");
+    Params p;
+    p.out = (__nv_bfloat16*)out; p.q_start = q_start; p.positions = positions; p.block_table = block_table; p.status = status;
+    p.n_seqs = n_seqs; p.nq = nq; p.nkv = nkv; p.group = group; p.tq = BM / group; p.table_stride = table_stride;
+    p.page_size = page_size; p.window = window; p.box_rows = page_size < BN ? page_size : BN;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.scale_log2 = scale * LOG2E;
+    CUtensorMap mq, mk, mv;
+    const long long pool_rows = (long long)pool_pages * nkv * page_size;
+    if (q_map(&mq, q, n_tokens, nq, group, p.tq) != 0) return -1;
+    if (pool_map(&mk, k_pool, pool_rows, p.box_rows) != 0) return -1;
+    if (pool_map(&mv, v_pool, pool_rows, p.box_rows) != 0) return -1;
+    constexpr size_t smem = 1024 + 2 * Q_BYTES + (size_t)STAGES * 2 * KV_BYTES + 2 * P_BYTES;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RMX_FAIL("attention_tcgen05: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
+        raised = true;
+    }
+    attention_tcgen05_kernel<<<dim3(n_tiles, nkv), THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    RMX_CHECK_LAUNCH("attention_tcgen05");
+    return 0;
+}

@@ -275,6 +275,11 @@ def linear_bf16(x, w, out, workspace=None, status=None):
 
 
 def attention(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=None):
+    group = nq // nkv
+    if (q.dtype == torch.bfloat16 and use_tcgen05_attention and getattr(batch, "max_q_len", 0) * group > 16
+            and tcgen05_attention_supported(hd, group, page_size)):
+        attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale)
+        return
     if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, nq // nkv):
         attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace)
         return
@@ -411,3 +416,26 @@ def prefers_fused_swiglu(m: int, n: int, k: int) -> bool:
     if not fused_swiglu or tcgen05_policy == "none" or not tcgen05_supported(m, n, k) or n % 128:
         return False
     return _tuned.get((n, k, _mpad(m), "swiglu"), True)
+
+
+use_tcgen05_attention = True   # prompt portions at head size 128 run on the tcgen05 tensor cores
+
+
+def tcgen05_attention_supported(hd: int, group: int, page_size: int) -> bool:
+    return bool(kernels_library().rmx_attention_tcgen05_supports(c_int(hd), c_int(group), c_int(page_size)))
+
+
+def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale):
+    """Prompt portions: S = Q K^T and O += P V as tcgen05 MMAs with accumulators in tensor memory."""
+    lib = kernels_library()
+    pair = 2 * (128 // (nq // nkv))     # a block takes two neighbouring tiles of 128 rows
+    starts = batch.q_start_host
+    n_tiles = sum(-(-(starts[i + 1] - starts[i]) // pair) for i in range(batch.n_seqs))
+    check(lib.rmx_attention_tcgen05(
+        _ptr(q, torch.bfloat16, "q"), _ptr(k_pool, torch.bfloat16, "k_pool"), _ptr(v_pool, torch.bfloat16, "v_pool"),
+        _ptr(batch.q_start, torch.int32, "q_start"), _ptr(batch.positions, torch.int32, "positions"),
+        _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
+        _ptr(out, torch.bfloat16, "out"), c_int(batch.n_seqs), c_int(q.shape[0]), c_int(n_tiles), c_int(nq), c_int(nkv),
+        c_int(hd), c_int(window), c_float(scale), c_int(k_pool.shape[0]), _ptr(batch.status, torch.int32, "status"),
+        _stream()))
+    _launched()

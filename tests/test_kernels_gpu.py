@@ -567,3 +567,52 @@ def test_gemm_tcgen05_refuses_what_it_cannot_do():
     with pytest.raises(KernelError, match="K % 8"):
         ops().gemm_tcgen05(a, w, torch.empty(4, 128, dtype=torch.bfloat16, device=DEV))
     assert not ops().prefers_tcgen05(4, 128, 60)
+
+
+@pytest.mark.parametrize("nq, nkv, page, window", [(32, 8, 64, 0), (8, 8, 16, 0), (16, 1, 8, 0), (4, 2, 32, 50), (8, 2, 128, 0),
+                                                   (32, 8, 64, 300)])
+def test_attention_tcgen05_over_pages(nq, nkv, page, window):
+    """Prompt portions on the tcgen05 tensor cores (head size 128): several sequences whose portions span
+    more than one tile of 128 rows and several key tiles, beside short ones; NaN in every slot of the pool
+    that must not be read."""
+    hd = 128
+    torch.manual_seed(nq * 100 + page)
+    lengths = [300, 40, 33, 130, 700, 64, 1]
+    new = [170, 40, 5, 130, 260, 64, 1]
+    k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, torch.bfloat16, seed=page + nq)
+    qs = [torch.randn(c, nq, hd).to(torch.bfloat16) for c in new]
+    q = torch.cat(qs).to(DEV).reshape(-1, nq * hd)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    batch = _Batch(lengths, new, status)
+    out = torch.full_like(q, float("nan"))
+    scale = hd ** -0.5
+    ops().attention_tcgen05(q, k_pool, v_pool, batch, table, page, out, nq, nkv, hd, window, scale)
+    assert status.item() == 0
+    at = 0
+    for s, (n, c) in enumerate(zip(lengths, new)):
+        want = plain_attention(qs[s], ks[s], vs[s], torch.arange(n - c, n), window, scale)
+        got = out[at:at + c].double().cpu().reshape(c, nq, hd)
+        assert not torch.isnan(got).any(), (s, n, c)
+        assert ((got - want).abs() <= 1e-2 * (1 + want.abs())).all(), (s, n, c, (got - want).abs().max().item())
+        at += c
+
+
+def test_attention_tcgen05_finds_a_far_key_and_respects_the_window_edge():
+    nq, nkv, hd, page, n = 8, 2, 128, 16, 900
+    k_pool, v_pool, table, ks, vs = paged_setup([n], nkv, hd, page, torch.bfloat16, seed=8)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    batch = _Batch([n], [40], status)
+    for window, target, seen in ((0, 0, True), (0, 63, True), (0, 64, True), (0, 511, True), (0, n - 1, True),
+                                 (100, n - 101, False), (100, n - 100, True)):
+        q = torch.zeros(40, nq, hd)
+        q[:, :, 5] = 24.0
+        kp = k_pool.clone()
+        kp[table[0, target // page].item(), :, target % page, :] = 0
+        kp[table[0, target // page].item(), :, target % page, 5] = 24.0
+        out = torch.empty(40, nq * hd, dtype=torch.bfloat16, device=DEV)
+        ops().attention_tcgen05(q.reshape(40, -1).to(torch.bfloat16).to(DEV), kp, v_pool, batch, table, page, out, nq, nkv, hd,
+                                window, hd ** -0.5)
+        want = vs[0][target].float().repeat_interleave(nq // nkv, 0).reshape(-1)
+        hit = (out[-1].float().cpu() - want).abs().max().item() < 2e-2     # the last token, at position n - 1
+        assert hit == seen, (window, target)
+    assert status.item() == 0
