@@ -206,9 +206,13 @@ def time_e2e(engine, batch, new_tokens):
                                  max_batch_tokens=batch * CONTEXT)
     decoded = r.generated_tokens - batch
     # bytes per decode step: ids, positions, sequence indices, starts, lengths, slots, rows, block tables up; tokens + status down
-    entries = MAX_CONTEXT // PAGE   # a captured decode step carries block tables of the context limit
-    h2d = 4 * (3 * batch + (batch + 1) + 5 * batch + batch * entries)
-    d2h = 4 * (batch + 1)
+    # a captured decode step uploads one buffer of fixed layout: ids, positions, sequence indices, starts, lengths,
+    # slots, rows, temperatures, uniforms and block tables of the context limit
+    from rust_mlx_b200.engine.batch import BatchLayout
+    from rust_mlx_b200.engine.graphs import bucket
+    b = bucket(batch)
+    h2d = 4 * BatchLayout(b, b, b, [engine.max_context // PAGE for _ in engine.pools.paged_groups]).total
+    d2h = 4 * (b + 1)
     return decoded / r.decode_seconds, h2d, d2h
 
 
@@ -289,7 +293,7 @@ def main():
         flops = prefill_flops(raw, a.layers, PREFILL_TOKENS)
         line["prefill"] = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
                            "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"]}
-        e2e, h2d, d2h = time_e2e(engine, a.batch, max(16, a.steps // 2))
+        e2e, h2d, d2h = time_e2e(engine, a.batch, max(16, a.steps))
         line["e2e"] = {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
     print(json.dumps(line))
     return 0

@@ -77,6 +77,8 @@ class BatchLayout:
     def fill(self, buf: np.ndarray, seqs: list, pools, vocab_size: int, temperatures=None, uniforms=None) -> dict:
         """Write the arrays of ``seqs`` into ``buf`` (int32, ``total`` long); returns host-side facts."""
         counts = [len(s.tokens) for s in seqs]
+        if self.n_tokens == self.n_seqs == self.n_rows and max(counts) == 1:
+            return self._fill_decode(buf, seqs, pools, vocab_size, temperatures, uniforms)
         q_start, rows = [0], []
         for s, c in zip(seqs, counts):
             for w in s.want:
@@ -115,6 +117,38 @@ class BatchLayout:
                 table.table_into(s.req, grp.table_index, tab[i].ctypes.data, e)
         return dict(q_start_host=q_start, seq_lens_host=seq_lens, start_host=[s.start for s in seqs],
                     slots_host=slots, max_q_len=max(counts), max_seq_len=max(seq_lens))
+
+    def _fill_decode(self, buf, seqs, pools, vocab_size, temperatures, uniforms) -> dict:
+        """The same for a decode step (every sequence brings one token and wants its logits): whole arrays at once."""
+        n = self.n_seqs
+        ids = np.fromiter((s.tokens[0] for s in seqs), dtype=np.int64, count=n)
+        if ids.min() < 0 or ids.max() >= vocab_size:
+            raise ValueError("token outside vocabulary")
+        starts = np.fromiter((s.start for s in seqs), dtype=np.int32, count=n)
+        ramp = np.arange(n + 1, dtype=np.int32)
+        self.part(buf, 0)[:] = ids
+        self.part(buf, 1)[:] = starts
+        self.part(buf, 2)[:] = ramp[:n]
+        self.part(buf, 3)[:] = ramp
+        self.part(buf, 4)[:] = starts + 1
+        table = pools.table
+        slots = [table.slot(s.req) for s in seqs]
+        self.part(buf, 5)[:] = slots
+        self.part(buf, 6)[:] = ramp[:n]
+        fl = self.part(buf, 7).view(np.float32)
+        fl[:] = 0.0 if temperatures is None else temperatures
+        fl = self.part(buf, 8).view(np.float32)
+        fl[:] = 0.0 if uniforms is None else uniforms
+        for g, grp in enumerate(pools.paged_groups):
+            e = self.entries[g]
+            tab = self.part(buf, 9 + g)
+            tab[:] = -1
+            ptr = tab.ctypes.data
+            for i, s in enumerate(seqs):
+                table.table_into(s.req, grp.table_index, ptr + i * e * 4, e)
+        seq_lens = (starts + 1).tolist()
+        return dict(q_start_host=ramp.tolist(), seq_lens_host=seq_lens, start_host=starts.tolist(), slots_host=slots,
+                    max_q_len=1, max_seq_len=max(seq_lens))
 
     def views(self, dev: torch.Tensor, status: torch.Tensor, host_facts: dict) -> StepBatch:
         p = lambda i, n=None: self.part(dev, i, n)  # noqa: E731
