@@ -52,7 +52,7 @@ def engine_for(folder, dtype, page, tokens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("way", ["whole", "tail_one_by_one", "portions", "mixed"])
 def test_every_way_of_cutting_matches_the_plain_implementation(workdir, name, dtype, way):
     raw, page, folder, reqs, ref = cached_setup(workdir, name, dtype)
@@ -68,7 +68,7 @@ def test_every_way_of_cutting_matches_the_plain_implementation(workdir, name, dt
     _cache[(name, dtype, way)] = got
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_float32_ways_agree_bit_for_bit(workdir, name):
     raw, page, folder, reqs, ref = cached_setup(workdir, name, "float32")
     results = []

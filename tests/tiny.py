@@ -23,7 +23,23 @@ TINY_B = dict(
     use_sliding_window=True, sliding_window=20, max_window_layers=1)
 PAGE_B = 8
 
-CONFIGS = {"A": (TINY_A, PAGE_A), "B": (TINY_B, PAGE_B)}
+# C and D have the head sizes of real checkpoints, so that the engine's bfloat16 replay goes through the kernels
+# that serve them (TMA-fed attention at 64 and 128, tcgen05 prompt attention at 128, the tcgen05 products):
+# C: head 64, group 3, a window; D: head 128, group 4, widths that are multiples of 64 (fused gate/up blocks).
+TINY_C = dict(
+    model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=136,
+    num_attention_heads=6, num_key_value_heads=2, head_dim=64, intermediate_size=200, vocab_size=333,
+    rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096,
+    use_sliding_window=True, sliding_window=70, max_window_layers=1)
+PAGE_C = 32
+
+TINY_D = dict(
+    model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=256,
+    num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=384, vocab_size=520,
+    rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
+PAGE_D = 64
+
+CONFIGS = {"A": (TINY_A, PAGE_A), "B": (TINY_B, PAGE_B), "C": (TINY_C, PAGE_C), "D": (TINY_D, PAGE_D)}
 
 
 def make_folder(tmp_path, raw: dict, seed: int = 0, store: str = "float32") -> str:
