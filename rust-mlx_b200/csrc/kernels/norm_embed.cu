@@ -187,15 +187,47 @@ __global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ ou
     store4(out + t * inter + j, make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w)));
 }
 
+// bfloat16, eight outputs per thread (16-byte loads and stores); inter and block are multiples of 8
+__global__ void swiglu_kernel8(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter,
+                               int block, size_t total8) {
+    allow_dependents();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total8) return;
+    const int per_row = inter >> 3;
+    const size_t t = idx / per_row;
+    const int j = (int)(idx - t * per_row) * 8;
+    int gi, ui;
+    gate_up_at(j, inter, block, gi, ui);
+    const uint4 g = *reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + gi);
+    const uint4 u = *reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + ui);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[i]));
+        __nv_bfloat162 r = __floats2bfloat162_rn(silu_mul(a.x, b.x), silu_mul(a.y, b.y));
+        ow[i] = *reinterpret_cast<uint32_t*>(&r);
+    }
+    *reinterpret_cast<uint4*>(out + t * inter + j) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
 RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int block, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && inter > 0, "swiglu: bad sizes");
     RMX_REQUIRE(block == 0 || (block > 0 && inter % block == 0), "swiglu: blocks of %d do not divide %d", block, inter);
     const bool vec = (inter & 3) == 0 && (block & 3) == 0;
-    const size_t total = (size_t)n_tokens * inter / (vec ? 4 : 1);
     const int threads = 256;
-    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_BF16 && (inter & 7) == 0 && (block & 7) == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        const size_t total8 = (size_t)n_tokens * inter / 8;
+        swiglu_kernel8<<<(unsigned)((total8 + threads - 1) / threads), threads, 0, s>>>(
+            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total8);
+        RMX_CHECK_LAUNCH("swiglu");
+        return 0;
+    }
+    const size_t total = (size_t)n_tokens * inter / (vec ? 4 : 1);
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dtype == RMX_F32) {
         if (vec) swiglu_kernel4<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, block, total);
         else swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, block, total);

@@ -11,6 +11,10 @@
 // numbers from rotary_dim on pass through.  Norm weights are float; either may be null
 // (no norm).  With write_kv == 0 only q is produced (a layer that reads another layer's
 // cache).  Everything is computed in float and rounded once to T.
+//
+// The cosines and sines of a step's positions are the same for every head and every layer:
+// rope_table_kernel forms them once per step ([token][cos of j | sin of j], float, with the same
+// float product and the same sincosf), and the kernels here read them when the table is given.
 #include "common.cuh"
 
 namespace {
@@ -23,7 +27,7 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_kernel(
     const float* __restrict__ inv_freq, int rotary_dim, const int* __restrict__ positions,
     const int* __restrict__ seq_index, const int* __restrict__ block_table, int table_stride, int page_size,
     T* __restrict__ k_pool, T* __restrict__ v_pool, T* __restrict__ q_out, int n_tokens, int nq, int nkv, int hd,
-    int row_stride, int write_kv, int* __restrict__ status) {
+    int row_stride, int write_kv, int* __restrict__ status, const float* __restrict__ cos_sin) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
@@ -71,9 +75,13 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_kernel(
     const int half = rotary_dim >> 1;
     if (rotate && half > 0) {
         for (int j = lane; j < half; j += 32) {
-            const float angle = (float)pos * inv_freq[j];
             float sn, cs;
-            sincosf(angle, &sn, &cs);
+            if (cos_sin) {
+                cs = cos_sin[(size_t)t * rotary_dim + j];
+                sn = cos_sin[(size_t)t * rotary_dim + half + j];
+            } else {
+                sincosf((float)pos * inv_freq[j], &sn, &cs);
+            }
             const float a = buf[j], b = buf[j + half];
             dst[j] = from_float<T>(a * cs - b * sn);
             dst[j + half] = from_float<T>(b * cs + a * sn);
@@ -83,34 +91,136 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_kernel(
         for (int d = lane; d < hd; d += 32) dst[d] = from_float<T>(buf[d]);
     }
 }
+
+// cos_sin[t][j] = cos(pos_t * inv_freq[j]), cos_sin[t][half + j] = sin(...): once per step.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float* __restrict__ cos_sin, int n_tokens, int half) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_tokens * half) return;
+    const int t = idx / half, j = idx - t * half;
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
+    cos_sin[(size_t)t * 2 * half + j] = cs;
+    cos_sin[(size_t)t * 2 * half + half + j] = sn;
+}
+
+// bfloat16, head size 128, all 128 numbers rotated, table given: a lane holds four neighbouring numbers of the
+// head; the partner of number j is j + 64, sixteen lanes away.
+__global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_128_kernel(
+    const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+    const float* __restrict__ cos_sin, const int* __restrict__ positions, const int* __restrict__ seq_index,
+    const int* __restrict__ block_table, int table_stride, int page_size, __nv_bfloat16* __restrict__ k_pool,
+    __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ q_out, int n_tokens, int nq, int nkv, int row_stride,
+    int write_kv, int* __restrict__ status) {
+    constexpr int hd = 128;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = nq + (write_kv ? 2 * nkv : 0);
+    const long long item = (long long)blockIdx.x * WARPS + warp;
+    if (item >= (long long)n_tokens * heads_total) return;
+    const int t = (int)(item / heads_total);
+    const int head = (int)(item % heads_total);
+    const __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)head * hd + lane * 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    __nv_bfloat16* dst;
+    const float* norm_w;
+    bool rotate = true;
+    if (head < nq) {
+        dst = q_out + ((size_t)t * nq + head) * hd;
+        norm_w = q_norm;
+    } else {
+        const int pos = positions[t];
+        const int kvh = (head - nq) % nkv;
+        const bool is_v = head >= nq + nkv;
+        const int page = block_table[(size_t)seq_index[t] * table_stride + pos / page_size];
+        if (page < 0) {
+            if (lane == 0) atomicExch(status, 1);
+            return;
+        }
+        dst = (is_v ? v_pool : k_pool) + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * hd;
+        norm_w = is_v ? nullptr : k_norm;
+        rotate = !is_v;
+    }
+    if (!rotate) {  // values pass through
+        *reinterpret_cast<uint2*>(dst + lane * 4) = raw;
+        return;
+    }
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    float v[4] = {lo.x, lo.y, hi.x, hi.y};
+    if (norm_w) {
+        float ss = v[0] * v[0];
+        ss += v[1] * v[1];
+        ss += v[2] * v[2];
+        ss += v[3] * v[3];
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)hd + eps);
+        const float4 w = *reinterpret_cast<const float4*>(norm_w + lane * 4);
+        v[0] = v[0] * inv * w.x; v[1] = v[1] * inv * w.y; v[2] = v[2] * inv * w.z; v[3] = v[3] * inv * w.w;
+    }
+    const int j = (lane & 15) * 4;   // index of the pair (j, j + 64) this lane's numbers belong to
+    const float4 cs = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * hd + j);
+    const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * hd + 64 + j);
+    const float c[4] = {cs.x, cs.y, cs.z, cs.w}, s_[4] = {sn.x, sn.y, sn.z, sn.w};
+    float out[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+        // lanes 0..15 hold x[j] (partner x[j + 64] comes from lane + 16): out = a cos - b sin
+        // lanes 16..31 hold x[j + 64] (partner x[j]):                      out = b cos + a sin
+        out[i] = lane < 16 ? v[i] * c[i] - other * s_[i] : v[i] * c[i] + other * s_[i];
+    }
+    __nv_bfloat162 o01 = __floats2bfloat162_rn(out[0], out[1]), o23 = __floats2bfloat162_rn(out[2], out[3]);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&o01);
+    packed.y = *reinterpret_cast<uint32_t*>(&o23);
+    *reinterpret_cast<uint2*>(dst + lane * 4) = packed;
+}
 }  // namespace
+
+RMX_API int rmx_rope_table(const int* positions, const float* inv_freq, float* cos_sin, int n_tokens, int rotary_dim,
+                           void* stream) {
+    if (n_tokens == 0 || rotary_dim == 0) return 0;
+    RMX_REQUIRE(n_tokens > 0 && rotary_dim > 0 && rotary_dim % 2 == 0, "rope_table: bad sizes");
+    const int half = rotary_dim / 2, total = n_tokens * half;
+    rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, cos_sin, n_tokens, half);
+    RMX_CHECK_LAUNCH("rope_table");
+    return 0;
+}
 
 RMX_API int rmx_qk_rope_cache(const void* qkv, const float* q_norm, const float* k_norm, float eps,
                               const float* inv_freq, int rotary_dim, const int* positions, const int* seq_index,
                               const int* block_table, int table_stride, int page_size, void* k_pool, void* v_pool,
                               void* q_out, int n_tokens, int nq, int nkv, int hd, int row_stride, int write_kv,
-                              int* status, int dtype, void* stream) {
+                              int* status, const float* cos_sin, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(nq > 0 && nkv > 0 && hd > 0 && hd <= MAX_HD, "qk_rope_cache: head_dim %d must be in 1..%d", hd, MAX_HD);
     RMX_REQUIRE(rotary_dim >= 0 && rotary_dim <= hd && rotary_dim % 2 == 0,
                 "qk_rope_cache: rotary_dim %d must be even and at most head_dim %d", rotary_dim, hd);
     RMX_REQUIRE(page_size > 0 && table_stride > 0, "qk_rope_cache: bad page geometry");
     RMX_REQUIRE(row_stride >= (nq + (write_kv ? 2 * nkv : 0)) * hd, "qk_rope_cache: row stride %d too small", row_stride);
-    RMX_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "qk_rope_cache: rotation without a table");
+    RMX_REQUIRE(rotary_dim == 0 || inv_freq != nullptr || cos_sin != nullptr, "qk_rope_cache: rotation without a table");
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     const long long items = (long long)n_tokens * heads_total;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_BF16 && hd == 128 && rotary_dim == 128 && cos_sin != nullptr && row_stride % 4 == 0 &&
+        ((uintptr_t)qkv & 7) == 0) {
+        qk_rope_cache_128_kernel<<<blocks, WARPS * 32, 0, s>>>(
+            (const __nv_bfloat16*)qkv, q_norm, k_norm, eps, cos_sin, positions, seq_index, block_table, table_stride, page_size,
+            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, n_tokens, nq, nkv, row_stride, write_kv, status);
+        RMX_CHECK_LAUNCH("qk_rope_cache_128");
+        return 0;
+    }
     if (dtype == RMX_F32)
         qk_rope_cache_kernel<float><<<blocks, WARPS * 32, smem, s>>>(
             (const float*)qkv, q_norm, k_norm, eps, inv_freq, rotary_dim, positions, seq_index, block_table,
-            table_stride, page_size, (float*)k_pool, (float*)v_pool, (float*)q_out, n_tokens, nq, nkv, hd, row_stride, write_kv, status);
+            table_stride, page_size, (float*)k_pool, (float*)v_pool, (float*)q_out, n_tokens, nq, nkv, hd, row_stride, write_kv, status, cos_sin);
     else if (dtype == RMX_BF16)
         qk_rope_cache_kernel<__nv_bfloat16><<<blocks, WARPS * 32, smem, s>>>(
             (const __nv_bfloat16*)qkv, q_norm, k_norm, eps, inv_freq, rotary_dim, positions, seq_index, block_table,
             table_stride, page_size, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, n_tokens,
-            nq, nkv, hd, row_stride, write_kv, status);
+            nq, nkv, hd, row_stride, write_kv, status, cos_sin);
     else
         RMX_FAIL("qk_rope_cache: unknown dtype %d", dtype);
     RMX_CHECK_LAUNCH("qk_rope_cache");

@@ -50,6 +50,9 @@ class StepBatch:
     slots_host: list
     max_q_len: int
     max_seq_len: int
+    # what parts form once per step and share between layers (the rotation's cosines and sines); emptied by the
+    # engine at the start of every forward pass
+    per_step: dict = field(default_factory=dict)
 
     @property
     def all_decode(self) -> bool:

@@ -186,6 +186,7 @@ class Engine:
         """The model over one batch whose pages are reserved: embedding, the schedule's
         layer runs, then final norm and head on the wanted rows."""
         spec = self.spec
+        batch.per_step.clear()
         h = spec.embedding.forward(batch.token_ids)
         pending = None
         for call, read_only in self._calls:

@@ -108,8 +108,17 @@ def gemm_plain(a, w, out):
     _launched()
 
 
+def rope_table(positions, inv_freq, rotary_dim, out):
+    """out[t] = [cos(pos_t * inv_freq[j]) for j | sin(...) for j]: the angles of a step's positions, formed once."""
+    lib = kernels_library()
+    n = positions.shape[0]
+    check(lib.rmx_rope_table(_ptr(positions, torch.int32, "positions"), _ptr(inv_freq, torch.float32, "inv_freq"),
+                             _ptr(out, torch.float32, "out"), c_int(n), c_int(rotary_dim), _stream()))
+    _launched()
+
+
 def qk_rope_cache(qkv, q_norm, k_norm, eps, inv_freq, rotary_dim, positions, seq_index, block_table, page_size,
-                  k_pool, v_pool, q_out, nq, nkv, hd, write_kv, status):
+                  k_pool, v_pool, q_out, nq, nkv, hd, write_kv, status, cos_sin=None):
     lib = kernels_library()
     n = qkv.shape[0]
     check(lib.rmx_qk_rope_cache(
@@ -119,7 +128,7 @@ def qk_rope_cache(qkv, q_norm, k_norm, eps, inv_freq, rotary_dim, positions, seq
         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
         _ptr(k_pool, qkv.dtype, "k_pool"), _ptr(v_pool, qkv.dtype, "v_pool"), _ptr(q_out, qkv.dtype, "q_out"),
         c_int(n), c_int(nq), c_int(nkv), c_int(hd), c_int(qkv.shape[1]), c_int(1 if write_kv else 0),
-        _ptr(status, torch.int32, "status"), c_int(dtype_code(qkv)), _stream()))
+        _ptr(status, torch.int32, "status"), _ptr(cos_sin, torch.float32, "cos_sin"), c_int(dtype_code(qkv)), _stream()))
     _launched()
 
 

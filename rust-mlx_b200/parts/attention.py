@@ -69,7 +69,7 @@ class AttentionMixer(Mixer):
         ops.qk_rope_cache(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.position.inv_freq,
                           self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
                           cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, hd, not cache.read_only,
-                          batch.status)
+                          batch.status, self.position.angles(batch))
         o = ws.get("attn_out", (n, nq * hd), dt)
         ops.attention(q, cache.k_pool, cache.v_pool, batch, cache.block_table, cache.page_size, o, nq, nkv, hd,
                       cache.window, self.scale, ws)

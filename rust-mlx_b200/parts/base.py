@@ -130,6 +130,11 @@ class PositionEncoding(Part):
     rotary_dim: int = 0
     inv_freq: Optional[torch.Tensor] = None
 
+    def angles(self, batch):
+        """Optional: [tokens, rotary_dim] float32, cosines then sines of the step's positions, formed once per
+        step (kept in ``batch.per_step``).  None: the kernel forms them from ``inv_freq``."""
+        return None
+
 
 class Mixer(Part):
     """``forward(x, batch, cache) -> y`` over the flat token batch ``x`` [tokens, width].

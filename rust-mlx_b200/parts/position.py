@@ -31,9 +31,25 @@ class RotaryEmbedding(PositionEncoding):
         super().bind(tensors, ctx)
         self.inv_freq = self._table.to(ctx.device).contiguous()
 
+    def angles(self, batch):
+        """[tokens, rotary_dim] float32: cosines then sines of the step's positions.  The same for every
+        head and layer, so they are formed once per step and kept with the batch."""
+        if self.rotary_dim == 0:
+            return None
+        cache = batch.per_step
+        key = ("rope", id(self))
+        if key not in cache:
+            out = self.ctx.workspace.get(f"rope_table_{id(self)}", (batch.n_tokens, self.rotary_dim), torch.float32)
+            self.ctx.ops.rope_table(batch.positions, self.inv_freq, self.rotary_dim, out)
+            cache[key] = out
+        return cache[key]
+
 
 class NoPositionEncoding(PositionEncoding):
     graph_safe = True
+
+    def angles(self, batch):
+        return None
 
     rotary_dim = 0
     inv_freq = None

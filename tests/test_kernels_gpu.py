@@ -275,8 +275,9 @@ def test_qk_norm_rotation_and_cache_write(dtype, nq, nkv, hd, rot, page, norm):
     q_out = torch.empty(n_tok, nq * hd, dtype=dt, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     positions = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    table_dev = table.to(DEV)
     ops().qk_rope_cache(qkv, qn, kn, eps, inv_freq, rot, positions, torch.tensor(sidx, dtype=torch.int32, device=DEV),
-                        table.to(DEV), page, k_pool, v_pool, q_out, nq, nkv, hd, True, status)
+                        table_dev, page, k_pool, v_pool, q_out, nq, nkv, hd, True, status)
     assert status.item() == 0
     x = qkv.double().cpu()
     q = x[:, :nq * hd].reshape(n_tok, nq, hd)
@@ -302,6 +303,18 @@ def test_qk_norm_rotation_and_cache_write(dtype, nq, nkv, hd, rot, page, norm):
     tol = 1e-5 if dtype == "float32" else 3e-2
     want_q = rotate(normed(q, qn))
     assert (q_out.double().cpu().reshape(n_tok, nq, hd) - want_q).abs().max().item() < tol
+    if rot:
+        # the same with the step's cosines and sines formed once (for head 128 in bfloat16 a kernel of its own)
+        angles = torch.empty(n_tok, rot, device=DEV)
+        ops().rope_table(positions, inv_freq, rot, angles)
+        ang = positions.cpu().float()[:, None] * inv_freq.cpu()[None, :]
+        assert torch.allclose(angles.cpu(), torch.cat([ang.cos(), ang.sin()], 1), atol=1e-6)
+        q2, k2, v2 = torch.empty_like(q_out), torch.zeros_like(k_pool), torch.zeros_like(v_pool)
+        ops().qk_rope_cache(qkv, qn, kn, eps, inv_freq, rot, positions, torch.tensor(sidx, dtype=torch.int32, device=DEV),
+                            table_dev, page, k2, v2, q2, nq, nkv, hd, True, status, cos_sin=angles)
+        assert (q2.double() - q_out.double()).abs().max().item() <= (0 if not (dtype == "bfloat16" and hd == 128) else 3e-2)
+        assert (k2.double() - k_pool.double()).abs().max().item() <= (0 if not (dtype == "bfloat16" and hd == 128) else 3e-2)
+        assert torch.equal(v2, v_pool) and status.item() == 0
     want_k = rotate(normed(k, kn))
     for t in range(n_tok):
         pg, slot = table[sidx[t], pos[t] // page].item(), pos[t] % page
