@@ -13,7 +13,9 @@ import torch
 
 import plain_qwen3 as plain
 
-FIXTURE = "/root/reference/tests/fixtures/dense"
+# the reference's checkout, beside this repository unless REFERENCE_DIR says otherwise
+REFERENCE = os.environ.get("REFERENCE_DIR", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "..", "reference"))
+FIXTURE = os.path.join(REFERENCE, "tests", "fixtures", "dense")
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "dense_fixture_plain.json")
 
 
