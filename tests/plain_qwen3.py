@@ -73,7 +73,7 @@ def layer_windows(config):
 
 def embedding(table, ids):
     """h = embed_tokens.weight[ids] (src/weights.rs:203-204, src/dense.rs:378-379)."""
-    return table[torch.as_tensor(ids, dtype=torch.long)]
+    return table[torch.as_tensor(ids, dtype=torch.long, device=table.device)]
 
 
 def rms_norm(v, weight, eps):
@@ -99,9 +99,9 @@ def rope(x, positions, theta, rotary_dim):
     src/rope.rs:21-27; sine, cosine and the rotation are then exact here.
     x: [T, heads, head_dim]; positions: [T]."""
     half = rotary_dim // 2
-    j = torch.arange(half, dtype=F)
+    j = torch.arange(half, dtype=F, device=x.device)
     inv_freq = (theta ** (-2.0 * j / rotary_dim)).to(torch.float32)
-    angle = (positions.to(torch.float32)[:, None] * inv_freq[None, :]).to(F)   # [T, half]
+    angle = (positions.to(device=x.device, dtype=torch.float32)[:, None] * inv_freq[None, :]).to(F)   # [T, half]
     cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
     a, b = x[..., :half], x[..., half:rotary_dim]
     out = x.clone()
@@ -119,7 +119,7 @@ def attention_scores(q, k, v, positions, window):
     nkv = k.shape[1]
     group = nq // nkv
     scale = hd ** -0.5
-    pos = positions.to(torch.long)
+    pos = positions.to(device=q.device, dtype=torch.long)
     allowed = pos[None, :] <= pos[:, None]
     if window > 0:
         allowed &= pos[None, :] > pos[:, None] - window
