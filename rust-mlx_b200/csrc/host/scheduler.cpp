@@ -119,9 +119,16 @@ const std::vector<Entry>& Scheduler::next() {
         schedule(running_.back(), want, budget);
     }
 
-    // 4. nothing could run although requests hold pages: the one admitted last steps back
+    // 4. a request has tokens to feed, nothing could run, and others hold pages: the one admitted last steps back.
+    // (Requests that merely wait for their next token to be chosen hold pages too, but they are not stuck.)
     if (batch_.empty() && !running_.empty()) {
-        if (running_.size() > 1 || !waiting_.empty()) {
+        bool starving = !waiting_.empty() && (int)running_.size() < max_seqs_ && cache_->free_slots() > 0;
+        bool anyone_idle = false;
+        for (const Req& r : running_) {
+            if (r.total > r.computed) starving = true;
+            else anyone_idle = true;
+        }
+        if (starving && !anyone_idle && (running_.size() > 1 || !waiting_.empty())) {
             preempt_last(-1);
             return next();
         }

@@ -29,11 +29,15 @@ static inline int block_threads(int width) {
 
 // h[t, :] = table[ids[t], :] as float.  An id outside the table writes zeros (the host
 // rejects such ids before the step; the kernel never reads outside the table).
+// from_last (or null): where from_last[t] != 0 the token's id is not ids[t] but the one the last step's sampling
+// left for the token's sequence, last_tokens[slots[seq_index[t]]] (the host launched this step before it read it).
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ h, int width, int vocab) {
+                                 float* __restrict__ h, int width, int vocab, const int* __restrict__ from_last,
+                                 const int* __restrict__ seq_index, const int* __restrict__ slots,
+                                 const int* __restrict__ last_tokens) {
     const int t = blockIdx.x;
-    const int id = ids[t];
+    const int id = (from_last && from_last[t]) ? last_tokens[slots[seq_index[t]]] : ids[t];
     const bool ok = id >= 0 && id < vocab;
     const T* row = table + (size_t)(ok ? id : 0) * width;
     float* out = h + (size_t)t * width;
@@ -49,15 +53,18 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 }
 
 RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tokens, int width, int vocab,
+                          const int* from_last, const int* seq_index, const int* slots, const int* last_tokens,
                           int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embedding: bad sizes");
+    RMX_REQUIRE(from_last == nullptr || (seq_index && slots && last_tokens), "embedding: from_last needs seq_index, slots and last_tokens");
     const int threads = block_threads(width);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_F32)
-        embedding_kernel<float><<<n_tokens, threads, 0, s>>>(ids, (const float*)table, h, width, vocab);
+        embedding_kernel<float><<<n_tokens, threads, 0, s>>>(ids, (const float*)table, h, width, vocab, from_last, seq_index, slots, last_tokens);
     else if (dtype == RMX_BF16)
-        embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, h, width, vocab);
+        embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, h, width, vocab, from_last, seq_index,
+                                                                  slots, last_tokens);
     else
         RMX_FAIL("embedding: unknown dtype %d", dtype);
     RMX_CHECK_LAUNCH("embedding");

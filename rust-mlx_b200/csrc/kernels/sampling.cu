@@ -13,7 +13,8 @@ constexpr int THREADS = 1024;
 __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict__ logits, int ld,
                                                          const float* __restrict__ temperature,
                                                          const float* __restrict__ uniform, int* __restrict__ out,
-                                                         int vocab) {
+                                                         int vocab, const int* __restrict__ slots,
+                                                         int* __restrict__ last_tokens) {
     __shared__ float s_val[THREADS];
     __shared__ int s_idx[THREADS];
     __shared__ int s_choice;
@@ -42,7 +43,10 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     const int arg = s_idx[0] == 0x7fffffff ? 0 : s_idx[0];
     const float temp = temperature ? temperature[r] : 0.f;
     if (!(temp > 0.f)) {
-        if (tid == 0) out[r] = arg;
+        if (tid == 0) {
+            out[r] = arg;
+            if (last_tokens) last_tokens[slots[r]] = arg;
+        }
         return;
     }
     __syncthreads();
@@ -74,16 +78,23 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
         s_choice = pick;
     }
     __syncthreads();
-    if (tid == 0) out[r] = s_choice >= 0 ? s_choice : arg;  // target == total by rounding: the likeliest token
+    if (tid == 0) {
+        const int choice = s_choice >= 0 ? s_choice : arg;  // target == total by rounding: the likeliest token
+        out[r] = choice;
+        if (last_tokens) last_tokens[slots[r]] = choice;
+    }
 }
 }  // namespace
 
+// slots / last_tokens (both or neither): the choice of row r is also left at last_tokens[slots[r]], where the next
+// step's embedding can find it without a trip through the host.
 RMX_API int rmx_sample(const float* logits, int ld, const float* temperature, const float* uniform, int* out,
-                       int n_rows, int vocab, void* stream) {
+                       int n_rows, int vocab, const int* slots, int* last_tokens, void* stream) {
     if (n_rows == 0) return 0;
     RMX_REQUIRE(n_rows > 0 && vocab > 0 && ld >= vocab, "sample: bad sizes");
     RMX_REQUIRE(temperature == nullptr || uniform != nullptr, "sample: temperatures without uniform numbers");
-    sample_kernel<<<n_rows, THREADS, 0, (cudaStream_t)stream>>>(logits, ld, temperature, uniform, out, vocab);
+    RMX_REQUIRE((slots == nullptr) == (last_tokens == nullptr), "sample: slots and last_tokens go together");
+    sample_kernel<<<n_rows, THREADS, 0, (cudaStream_t)stream>>>(logits, ld, temperature, uniform, out, vocab, slots, last_tokens);
     RMX_CHECK_LAUNCH("sample");
     return 0;
 }

@@ -26,6 +26,7 @@ class SequenceInput:
     start: int
     tokens: list
     want: list = field(default_factory=list)  # indices into ``tokens`` whose logits are wanted
+    from_last: bool = False  # the (single) token's id is what the last step's sampling left on the device
 
 
 @dataclass
@@ -44,6 +45,9 @@ class StepBatch:
     status: torch.Tensor
     temperatures: torch.Tensor
     uniforms: torch.Tensor
+    from_last: torch.Tensor     # int32 [tokens]: 1 where the id comes from the last step's sampling, on the device
+    row_slots: torch.Tensor     # int32 [rows]: the state slot of the sequence of every wanted row
+    any_from_last: bool
     q_start_host: list
     seq_lens_host: list
     start_host: list
@@ -53,6 +57,8 @@ class StepBatch:
     # what parts form once per step and share between layers (the rotation's cosines and sines); emptied by the
     # engine at the start of every forward pass
     per_step: dict = field(default_factory=dict)
+    # int32 [state slots] on the device: the token the last sampling chose for the request in each slot (the engine's)
+    last_tokens: torch.Tensor = None
 
     @property
     def all_decode(self) -> bool:
@@ -65,8 +71,9 @@ class BatchLayout:
     def __init__(self, n_tokens: int, n_seqs: int, n_rows: int, entries: list):
         self.n_tokens, self.n_seqs, self.n_rows, self.entries = n_tokens, n_seqs, n_rows, list(entries)
         rows = max(n_rows, 1)
-        self.sizes = [n_tokens, n_tokens, n_tokens, n_seqs + 1, n_seqs, n_seqs, rows, rows, rows] + \
+        self.sizes = [n_tokens, n_tokens, n_tokens, n_seqs + 1, n_seqs, n_seqs, rows, rows, rows, n_tokens, rows] + \
                      [n_seqs * e for e in entries]
+        self.first_table = 11
         # every array starts on a 16-byte boundary
         self.offsets, at = [], 0
         for n in self.sizes:
@@ -112,21 +119,33 @@ class BatchLayout:
         fl[:] = 0.0
         if uniforms is not None:
             fl[:len(uniforms)] = uniforms
+        fromlast = self.part(buf, 9)
+        fromlast[:] = 0
+        row_slots = []
+        for i, (s, c) in enumerate(zip(seqs, counts)):
+            if s.from_last:
+                if c != 1:
+                    raise ValueError("only a single decoded token can take its id from the last step")
+                fromlast[q_start[i]] = 1
+            row_slots += [slots[i]] * len(s.want)
+        self.part(buf, 10)[:len(row_slots)] = row_slots
         for g, grp in enumerate(pools.paged_groups):
             e = self.entries[g]
-            tab = self.part(buf, 9 + g).reshape(self.n_seqs, e)
+            tab = self.part(buf, self.first_table + g).reshape(self.n_seqs, e)
             tab[:] = -1
             for i, s in enumerate(seqs):
                 table.table_into(s.req, grp.table_index, tab[i].ctypes.data, e)
         return dict(q_start_host=q_start, seq_lens_host=seq_lens, start_host=[s.start for s in seqs],
-                    slots_host=slots, max_q_len=max(counts), max_seq_len=max(seq_lens))
+                    slots_host=slots, max_q_len=max(counts), max_seq_len=max(seq_lens),
+                    any_from_last=any(s.from_last for s in seqs))
 
     def _fill_decode(self, buf, seqs, pools, vocab_size, temperatures, uniforms) -> dict:
         """The same for a decode step (every sequence brings one token and wants its logits): whole arrays at once."""
         n = self.n_seqs
-        ids = np.fromiter((s.tokens[0] for s in seqs), dtype=np.int64, count=n)
+        ids = np.fromiter((0 if s.from_last else s.tokens[0] for s in seqs), dtype=np.int64, count=n)
         if ids.min() < 0 or ids.max() >= vocab_size:
             raise ValueError("token outside vocabulary")
+        self.part(buf, 9)[:] = np.fromiter((1 if s.from_last else 0 for s in seqs), dtype=np.int32, count=n)
         starts = np.fromiter((s.start for s in seqs), dtype=np.int32, count=n)
         ramp = np.arange(n + 1, dtype=np.int32)
         self.part(buf, 0)[:] = ids
@@ -138,20 +157,21 @@ class BatchLayout:
         slots = [table.slot(s.req) for s in seqs]
         self.part(buf, 5)[:] = slots
         self.part(buf, 6)[:] = ramp[:n]
+        self.part(buf, 10)[:] = slots
         fl = self.part(buf, 7).view(np.float32)
         fl[:] = 0.0 if temperatures is None else temperatures
         fl = self.part(buf, 8).view(np.float32)
         fl[:] = 0.0 if uniforms is None else uniforms
         for g, grp in enumerate(pools.paged_groups):
             e = self.entries[g]
-            tab = self.part(buf, 9 + g)
+            tab = self.part(buf, self.first_table + g)
             tab[:] = -1
             ptr = tab.ctypes.data
             for i, s in enumerate(seqs):
                 table.table_into(s.req, grp.table_index, ptr + i * e * 4, e)
         seq_lens = (starts + 1).tolist()
         return dict(q_start_host=ramp.tolist(), seq_lens_host=seq_lens, start_host=starts.tolist(), slots_host=slots,
-                    max_q_len=1, max_seq_len=max(seq_lens))
+                    max_q_len=1, max_seq_len=max(seq_lens), any_from_last=any(s.from_last for s in seqs))
 
     def views(self, dev: torch.Tensor, status: torch.Tensor, host_facts: dict) -> StepBatch:
         p = lambda i, n=None: self.part(dev, i, n)  # noqa: E731
@@ -159,7 +179,8 @@ class BatchLayout:
             n_tokens=self.n_tokens, n_seqs=self.n_seqs, n_rows=self.n_rows, token_ids=p(0), positions=p(1),
             seq_index=p(2), q_start=p(3), seq_lens=p(4), slots=p(5), logit_rows=p(6, self.n_rows),
             temperatures=p(7, self.n_rows).view(torch.float32), uniforms=p(8, self.n_rows).view(torch.float32),
-            block_tables=[p(9 + g).view(self.n_seqs, self.entries[g]) for g in range(len(self.entries))],
+            from_last=p(9), row_slots=p(10, self.n_rows),
+            block_tables=[p(self.first_table + g).view(self.n_seqs, self.entries[g]) for g in range(len(self.entries))],
             status=status, **host_facts)
 
 

@@ -96,6 +96,9 @@ class Engine:
             self._calls.append((call, call.cache in seen))
             seen.add(call.cache)
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # the token the last sampling chose for the request in each state slot: a decode step launched before the
+        # host has read the step before takes its ids from here
+        self.last_tokens = torch.zeros(max_requests, dtype=torch.int32, device=self.device)
         # the longest sequence a request may reach: the cache's size, the model's stated limit, or the caller's
         limit = self.pools.num_pages * page_size
         stated = getattr(self.config, "max_position_embeddings", 0) or 0
@@ -187,7 +190,8 @@ class Engine:
         layer runs, then final norm and head on the wanted rows."""
         spec = self.spec
         batch.per_step.clear()
-        h = spec.embedding.forward(batch.token_ids)
+        batch.last_tokens = self.last_tokens
+        h = spec.embedding.forward(batch.token_ids, batch)
         pending = None
         for call, read_only in self._calls:
             cache = self.pools.view(call.cache, batch, read_only) if call.cache in self.pools._where else None

@@ -33,14 +33,31 @@ class GenerationResult:
     preemptions: int = 0
 
 
+class _Launched:
+    """A step that is on its way: which requests want a token from it, and where the tokens will arrive."""
+
+    __slots__ = ("wanting", "host", "event", "t0")
+
+    def __init__(self, wanting, host, event, t0):
+        self.wanting, self.host, self.event, self.t0 = wanting, host, event, t0
+
+
 def generate(engine, prompts: list, *, max_tokens: int = 256, temperature: float = 0.0, seed: int = 0,
              ignore_eos: bool = False, prefill_chunk: int = 128, max_batch_tokens: int | None = None,
-             max_seqs: int | None = None, max_context: int = 0, eos_token_ids=None) -> GenerationResult:
+             max_seqs: int | None = None, max_context: int = 0, eos_token_ids=None,
+             run_ahead: bool = True) -> GenerationResult:
     """Generate up to ``max_tokens`` tokens after each prompt (lists of token ids).
 
     An end-of-sequence token ends a request and is not part of its output, as in the
     reference (src/bin/infer.rs:172-176).  ``temperature`` may be one number or one per
-    prompt; 0 is greedy."""
+    prompt; 0 is greedy.
+
+    ``run_ahead``: the next step is launched before the host has read the tokens of the step
+    before: a decoding request's next id is taken on the device from where the sampling left
+    it, so the host's work for a step (scheduling, tables, launch) hides behind the GPU's work
+    on the step before.  A request that turns out to have ended (end-of-sequence) has then
+    been given one step too many; that step's token is dropped and its cache position is
+    never read."""
     if max_tokens <= 0 or prefill_chunk <= 0:
         raise ValueError("max_tokens and prefill_chunk must be positive")
     n = len(prompts)
@@ -59,69 +76,124 @@ def generate(engine, prompts: list, *, max_tokens: int = 256, temperature: float
                       max_context=max_context)
     rids = [engine._rid(("generate", id(sched), i)) for i in range(n)]
     index = {rid: i for i, rid in enumerate(rids)}
-    known = [list(p) for p in prompts]
+    known = [list(p) for p in prompts]      # token ids the host knows
     out = [[] for _ in range(n)]
     reasons = ["length"] * n
+    done = [False] * n
+    owed = [0] * n                          # tokens sampled on the device that the host has not read yet (0 or 1)
+    res = GenerationResult(out, reasons, prompt_tokens=sum(len(p) for p in prompts))
+    result_buf = torch.zeros(max_seqs + 1, dtype=torch.int32, device=engine.device)
+    stream = torch.cuda.current_stream()
+    first_done = 0
+    t_first = None
+
+    def launch(entries) -> _Launched:
+        """Build the batch of ``entries`` and put it on the stream; the tokens travel to pinned memory behind it."""
+        t0 = time.perf_counter()
+        seqs, wanting = [], []
+        for e in entries:
+            i = index[e.req]
+            from_last = owed[i] > 0 and e.start + e.count > len(known[i])
+            toks = [0] if from_last else known[i][e.start:e.start + e.count]
+            seqs.append(SequenceInput(e.req, e.start, toks, [e.count - 1] if e.wants_logits else [], from_last))
+            if e.wants_logits:
+                wanting.append(i)
+        t_list = [temps[i] for i in wanting]
+        u_list = [uniform(seed, i, len(out[i]) + owed[i]) if temps[i] > 0 else 0.0 for i in wanting]
+        if engine.graphs is not None and len(wanting) == len(entries) and all(e.count == 1 for e in entries):
+            result = engine.graphs.run(seqs, t_list, u_list)              # a decode step: one captured graph
+        else:
+            batch = build_batch(seqs, engine.pools, engine.device, engine._status, engine.vocab_size, t_list, u_list)
+            logits = engine.forward(batch)
+            if wanting:
+                engine.ops.sample(logits, batch.temperatures, batch.uniforms, result_buf[1:1 + len(wanting)],
+                                  batch.row_slots, engine.last_tokens)
+            result_buf[0:1].copy_(engine._status)
+            result = result_buf
+        host = torch.empty(1 + len(wanting), dtype=torch.int32, pin_memory=True)
+        host.copy_(result[:1 + len(wanting)], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record(stream)
+        return _Launched(wanting, host, event, t0)
+
+    def harvest(step: _Launched) -> None:
+        """Wait for a step's tokens and hand them to their requests."""
+        nonlocal first_done, t_first
+        step.event.synchronize()                                          # the step's one synchronisation
+        host = step.host.tolist()
+        if host[0] != 0:
+            engine.check_status()
+        for i, tok in zip(step.wanting, host[1:]):
+            ahead = owed[i] > 0
+            owed[i] = 0
+            if done[i]:
+                continue                                                  # a step too many for a request that had ended
+            if tok in eos:
+                reasons[i] = "stop"
+                done[i] = True
+                sched.finish(rids[i])
+                continue
+            if not out[i]:
+                first_done += 1
+            out[i].append(tok)
+            known[i].append(tok)
+            if len(out[i]) >= max_tokens:
+                done[i] = True
+                sched.finish(rids[i])
+            elif not ahead:
+                sched.append_token(rids[i])
+        res.steps += 1
+        now = time.perf_counter()
+        res.step_seconds.append(now - step.t0)
+        if t_first is None and all(out[i] or done[i] for i in range(n)):
+            t_first = now
+
     try:
         for i, p in enumerate(prompts):
             sched.add(rids[i], len(p), max_tokens)
-        res = GenerationResult(out, reasons, prompt_tokens=sum(len(p) for p in prompts))
-        result_buf = torch.zeros(max_seqs + 1, dtype=torch.int32, device=engine.device)
-        first_done = 0
         t_start = time.perf_counter()
-        t_first = None
-        while not sched.idle():
-            t0 = time.perf_counter()
-            entries = sched.next()
-            res.preemptions += len(sched.take_preempted())
-            if not entries:
-                raise RuntimeError("the scheduler has requests but could build no step")
-            seqs, wanting = [], []
-            for e in entries:
-                i = index[e.req]
-                seqs.append(SequenceInput(e.req, e.start, known[i][e.start:e.start + e.count],
-                                          [e.count - 1] if e.wants_logits else []))
-                if e.wants_logits:
-                    wanting.append(i)
-            t_list = [temps[i] for i in wanting]
-            u_list = [uniform(seed, i, len(out[i])) if temps[i] > 0 else 0.0 for i in wanting]
-            if engine.graphs is not None and len(wanting) == len(entries) and all(e.count == 1 for e in entries):
-                result = engine.graphs.run(seqs, t_list, u_list)          # a decode step: one captured graph
-                host = result.tolist()                                    # the step's one synchronisation
-            else:
-                batch = build_batch(seqs, engine.pools, engine.device, engine._status, engine.vocab_size, t_list, u_list)
-                logits = engine.forward(batch)
-                if wanting:
-                    engine.ops.sample(logits, batch.temperatures, batch.uniforms, result_buf[1:1 + len(wanting)])
-                result_buf[0:1].copy_(engine._status)
-                host = result_buf[:1 + len(wanting)].tolist()             # the step's one synchronisation
-            if host[0] != 0:
-                engine.check_status()
-            sched.step_done()
-            for i, tok in zip(wanting, host[1:]):
-                if tok in eos:
-                    reasons[i] = "stop"
-                    sched.finish(rids[i])
-                    continue
-                if not out[i]:
-                    first_done += 1
-                out[i].append(tok)
-                known[i].append(tok)
-                if len(out[i]) >= max_tokens:
-                    sched.finish(rids[i])
-                else:
+        pending = None
+        while pending is not None or not sched.idle():
+            if pending is None:
+                entries = sched.next()
+                res.preemptions += len(sched.take_preempted())
+                if not entries:
+                    raise RuntimeError("the scheduler has requests but could build no step")
+                pending = launch(entries)
+                sched.step_done()
+            # the step after `pending`, launched before its tokens are read where that is possible: requests that
+            # will get a token from `pending` and need more are counted as having it
+            following = None
+            if run_ahead:
+                hopeful = [i for i in pending.wanting if not done[i] and len(out[i]) + 1 < max_tokens]
+                for i in hopeful:
                     sched.append_token(rids[i])
-            res.steps += 1
-            now = time.perf_counter()
-            res.step_seconds.append(now - t0)
-            if t_first is None and (first_done == n or sched.idle() or all(out[i] or reasons[i] == "stop" for i in range(n))):
-                t_first = now
+                    owed[i] = 1
+                entries = sched.next() if hopeful or not sched.idle() else []
+                preempted = sched.take_preempted()
+                res.preemptions += len(preempted)
+                if entries and not preempted:
+                    following = launch(entries)
+                    sched.step_done()
+                    harvest(pending)
+                else:
+                    # a request that was put back needs its tokens on the host to be computed again: read them first
+                    harvest(pending)
+                    if entries:
+                        alive = [e for e in entries if not done[index[e.req]]]
+                        if alive:
+                            following = launch(alive)
+                        sched.step_done()
+            else:
+                harvest(pending)
+            pending = following
         t_end = time.perf_counter()
         res.prefill_seconds = (t_first or t_end) - t_start
         res.decode_seconds = t_end - (t_first or t_end)
         res.generated_tokens = sum(len(o) for o in out)
         return res
     finally:
+        torch.cuda.synchronize()
         for rid in rids:
             if engine.pools.table.has(rid):
                 engine.pools.table.close(rid)

@@ -100,8 +100,11 @@ class DecodeGraphs:
         cap.batch = cap.layout.views(cap.dev, e._status, facts)
         cap.batch.forced_splits = key[1]
         # once eagerly: buffers reach their size, kernels' attributes are set, libraries warm up.
-        # It writes this step's keys and values, which the replay below writes again, the same.
+        # It writes this step's keys and values, which the replay below writes again, the same; the tokens it
+        # chooses are put back, because a step that runs ahead takes its ids from there.
+        saved = e.last_tokens.clone()
         self._step(cap)
+        e.last_tokens.copy_(saved)
         torch.cuda.synchronize()
         cap.generation = e.workspace.generation
         e.workspace.frozen = True
@@ -121,5 +124,5 @@ class DecodeGraphs:
     def _step(self, cap) -> None:
         e = self.engine
         logits = e.forward(cap.batch)
-        e.ops.sample(logits, cap.batch.temperatures, cap.batch.uniforms, cap.result[1:])
+        e.ops.sample(logits, cap.batch.temperatures, cap.batch.uniforms, cap.result[1:], cap.batch.row_slots, e.last_tokens)
         cap.result[0:1].copy_(e._status)

@@ -53,12 +53,15 @@ def count_launches(n: int) -> None:
     _launched(n)
 
 
-def embedding(ids, table, h_out):
-    """h_out[t] = table[ids[t]] as float32 (the residual stream)."""
+def embedding(ids, table, h_out, from_last=None, seq_index=None, slots=None, last_tokens=None):
+    """h_out[t] = table[ids[t]] as float32 (the residual stream).  Where from_last[t] is set the id is the one the
+    last step's sampling left for the token's sequence: last_tokens[slots[seq_index[t]]]."""
     lib = kernels_library()
     n, width = h_out.shape
     check(lib.rmx_embedding(_ptr(ids, torch.int32, "ids"), _ptr(table, name="table"), _ptr(h_out, torch.float32, "h"),
-                            c_int(n), c_int(width), c_int(table.shape[0]), c_int(dtype_code(table)), _stream()))
+                            c_int(n), c_int(width), c_int(table.shape[0]), _ptr(from_last, torch.int32, "from_last"),
+                            _ptr(seq_index, torch.int32, "seq_index"), _ptr(slots, torch.int32, "slots"),
+                            _ptr(last_tokens, torch.int32, "last_tokens"), c_int(dtype_code(table)), _stream()))
     _launched()
 
 
@@ -145,8 +148,9 @@ def attention_plain(q, k_pool, v_pool, positions, seq_index, block_table, page_s
     _launched()
 
 
-def sample(logits, temperature, uniform, out):
-    """out[r] = greedy choice (temperature None or 0) or a draw from softmax(logits / temperature)."""
+def sample(logits, temperature, uniform, out, slots=None, last_tokens=None):
+    """out[r] = greedy choice (temperature None or 0) or a draw from softmax(logits / temperature); with ``slots``
+    and ``last_tokens`` the choice is also left at last_tokens[slots[r]] for the next step's embedding."""
     lib = kernels_library()
     r, v = logits.shape
     if logits.stride(1) != 1:
@@ -155,7 +159,7 @@ def sample(logits, temperature, uniform, out):
         raise KernelError("sample: logits must be float32 on a CUDA device")
     check(lib.rmx_sample(c_void_p(logits.data_ptr()), c_int(logits.stride(0)), _ptr(temperature, torch.float32, "temperature"),
                          _ptr(uniform, torch.float32, "uniform"), _ptr(out, torch.int32, "out"), c_int(r), c_int(v),
-                         _stream()))
+                         _ptr(slots, torch.int32, "slots"), _ptr(last_tokens, torch.int32, "last_tokens"), _stream()))
     _launched()
 
 

@@ -25,9 +25,14 @@ class TokenEmbedding(Part):
         super().bind(tensors, ctx)
         self.weight = tensors[self.name].contiguous()
 
-    def forward(self, ids):
+    def forward(self, ids, batch=None):
+        """Rows of the table for ``ids``; where the batch says so (``from_last``) a token's id is the one the last
+        step's sampling left on the device for its sequence."""
         h = self.ctx.workspace.get("residual", (ids.shape[0], self.width), torch.float32)
-        self.ctx.ops.embedding(ids, self.weight, h)
+        if batch is not None and batch.last_tokens is not None:
+            self.ctx.ops.embedding(ids, self.weight, h, batch.from_last, batch.seq_index, batch.slots, batch.last_tokens)
+        else:
+            self.ctx.ops.embedding(ids, self.weight, h)
         return h
 
 

@@ -84,6 +84,33 @@ def test_long_greedy_generation_with_a_window(workdir):
     assert eng.generate([p], max_tokens=60, prefill_chunk=16)[0] == want
 
 
+def test_running_ahead_changes_nothing_but_the_time(workdir):
+    """With run_ahead the next step is launched before the host reads the last step's tokens (ids are taken on the
+    device); the tokens must be the same, also when requests end at different times, stop at an end-of-sequence
+    token, sample with a temperature, or are put back for lack of pages."""
+    raw, page = tiny.CONFIGS["D"]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=13))
+    ps = tiny.prompts(raw["vocab_size"], [30, 7, 65, 18], seed=4)
+    for dtype in ("float32", "bfloat16"):
+        eng = engine(folder, dtype, page, tokens=1024)
+        for opts in (dict(max_tokens=12), dict(max_tokens=9, temperature=0.8, seed=5), dict(max_tokens=20, prefill_chunk=16)):
+            a = eng.generate_detailed(ps, run_ahead=True, **opts)
+            b = eng.generate_detailed(ps, run_ahead=False, **opts)
+            assert a.tokens == b.tokens and a.finish_reasons == b.finish_reasons
+        base = eng.generate(ps, max_tokens=12, run_ahead=False)
+        stop = base[2][5]
+        a = eng.generate_detailed(ps, max_tokens=12, eos_token_ids=[stop], run_ahead=True)
+        b = eng.generate_detailed(ps, max_tokens=12, eos_token_ids=[stop], run_ahead=False)
+        assert a.tokens == b.tokens and a.finish_reasons == b.finish_reasons and "stop" in a.finish_reasons
+        assert eng.pools.table.live() == 0
+    small = engine(folder, "float32", page, tokens=256)        # four pages of 64: requests are put back
+    ps2 = tiny.prompts(raw["vocab_size"], [60, 58, 50], seed=6)
+    a = small.generate_detailed(ps2, max_tokens=40, prefill_chunk=32, run_ahead=True)
+    b = small.generate_detailed(ps2, max_tokens=40, prefill_chunk=32, run_ahead=False)
+    assert a.tokens == b.tokens and a.preemptions > 0 and b.preemptions > 0
+    assert small.pools.table.live() == 0 and small.pools.table.free_pages(0) == 4
+
+
 def test_eos_stops_and_is_not_part_of_the_output(workdir):
     raw, page = tiny.CONFIGS["A"]
     folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=11))

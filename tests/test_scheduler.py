@@ -149,3 +149,24 @@ def test_random_workloads_finish_with_every_page_back(seed):
     made = run(table, s, lengths, gen)
     assert made == gen
     assert table.free_pages(0) == pages and table.live() == 0
+
+
+def test_requests_that_await_their_token_are_not_disturbed():
+    """A step may be asked for while the last step's tokens are not read yet (the caller runs ahead): requests
+    whose next token is not known have nothing to feed; that is no reason to take their pages away."""
+    table, s = make(pages=8, page=4, max_seqs=3, budget=32, chunk=32)
+    s.add(0, 5, 4)
+    s.add(1, 6, 4)
+    assert [e.req for e in s.next()] == [0, 1]
+    s.step_done()
+    assert s.next() == [] and s.take_preempted() == []          # both await their first token
+    s.append_token(0)                                            # request 0's token is on its way: it may run ahead
+    entries = s.next()
+    assert [(e.req, e.start, e.count) for e in entries] == [(0, 5, 1)] and s.take_preempted() == []
+    s.step_done()
+    s.finish(1)                                                  # request 1's token turned out to end it
+    s.append_token(0)
+    assert [(e.req, e.start) for e in s.next()] == [(0, 6)]
+    s.step_done()
+    s.finish(0)
+    assert s.idle() and table.free_pages(0) == 8
