@@ -293,7 +293,7 @@ def main():
         flops = prefill_flops(raw, a.layers, PREFILL_TOKENS)
         line["prefill"] = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
                            "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"]}
-        e2e, h2d, d2h = time_e2e(engine, a.batch, max(16, a.steps))
+        e2e, h2d, d2h = time_e2e(engine, a.batch, max(128, a.steps))
         line["e2e"] = {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
     print(json.dumps(line))
     return 0

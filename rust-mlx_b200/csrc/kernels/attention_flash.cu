@@ -455,6 +455,8 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
     }
+    // everything above needs nothing from the kernels before this one; queries, keys and tables do
+    wait_for_prior_kernels();
     int seq, tok0, n_tok;
     if constexpr (KEYSPLIT) {   // one tile per sequence
         seq = blockIdx.x;
@@ -898,8 +900,8 @@ int launch_tma_as(const FlashParams& p, int n_tiles, long long pool_rows, cudaSt
         raised = true;
     }
     dim3 grid(n_tiles, p.nkv, p.n_splits);
-    attention_tma_kernel<HD, KEYSPLIT><<<grid, DTHREADS, smem, s>>>(mk, mv, p, box_rows);
-    RMX_CHECK_LAUNCH("attention_tma");
+    RMX_CHECK_LAUNCHED(launch_dependent(attention_tma_kernel<HD, KEYSPLIT>, grid, dim3(DTHREADS), smem, s, mk, mv, p, box_rows),
+                       "attention_tma");
     return 0;
 }
 

@@ -63,3 +63,33 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // (and do what does not need that kernel's results, such as fetching weights) once every block of that
 // kernel has called this or has ended.  It has no effect when the next kernel is launched the usual way.
 __device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+// The other half: a kernel launched as a programmatic dependent waits here until the kernels before it on the
+// stream have completed and their writes are visible.  Launched the usual way, it returns at once.
+__device__ __forceinline__ void wait_for_prior_kernels() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+// Whether kernels are launched as programmatic dependents (their blocks may take their places on the SMs while the
+// kernel before them drains; each waits for it with wait_for_prior_kernels() before touching memory).
+bool rmx_dependent_launch_enabled();
+
+#include <utility>
+// Launch `kernel` as a programmatic dependent of the work before it on the stream (or the usual way when that is
+// switched off).  The kernel must call wait_for_prior_kernels() before it reads or writes global memory.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = rmx_dependent_launch_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+#define RMX_CHECK_LAUNCHED(err, name)                                                     \
+    do {                                                                                  \
+        cudaError_t e__ = (err);                                                          \
+        if (e__ != cudaSuccess) RMX_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+    } while (0)

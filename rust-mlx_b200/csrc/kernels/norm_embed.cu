@@ -36,6 +36,8 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
                                  float* __restrict__ h, int width, int vocab, const int* __restrict__ from_last,
                                  const int* __restrict__ seq_index, const int* __restrict__ slots,
                                  const int* __restrict__ last_tokens) {
+    wait_for_prior_kernels();
+    allow_dependents();
     const int t = blockIdx.x;
     const int id = (from_last && from_last[t]) ? last_tokens[slots[seq_index[t]]] : ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -61,10 +63,11 @@ RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tok
     const int threads = block_threads(width);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_F32)
-        embedding_kernel<float><<<n_tokens, threads, 0, s>>>(ids, (const float*)table, h, width, vocab, from_last, seq_index, slots, last_tokens);
+        RMX_CHECK_LAUNCHED(launch_dependent(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, ids, (const float*)table, h, width,
+                                            vocab, from_last, seq_index, slots, last_tokens), "embedding");
     else if (dtype == RMX_BF16)
-        embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, h, width, vocab, from_last, seq_index,
-                                                                  slots, last_tokens);
+        RMX_CHECK_LAUNCHED(launch_dependent(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, ids,
+                                            (const __nv_bfloat16*)table, h, width, vocab, from_last, seq_index, slots, last_tokens), "embedding");
     else
         RMX_FAIL("embedding: unknown dtype %d", dtype);
     RMX_CHECK_LAUNCH("embedding");
@@ -82,6 +85,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
                                    T* __restrict__ x, int width, int write_h) {
     __shared__ float scratch[32];
     extern __shared__ __align__(16) float vals[];
+    wait_for_prior_kernels();
     allow_dependents();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -135,12 +139,13 @@ RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const int* rows, const 
     if (dtype == RMX_F32) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<float><<<n_rows, threads, smem, s>>>(h, (const float*)delta, rows, w, eps, (float*)x, width, write_h);
+        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), smem, s, h, (const float*)delta, rows, w,
+                                            eps, (float*)x, width, write_h), "add_rmsnorm");
     } else if (dtype == RMX_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, s>>>(h, (const __nv_bfloat16*)delta, rows, w, eps,
-                                                                      (__nv_bfloat16*)x, width, write_h);
+        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, s, h,
+                                            (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)x, width, write_h), "add_rmsnorm");
     } else {
         RMX_FAIL("add_rmsnorm: unknown dtype %d", dtype);
     }
@@ -180,6 +185,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 // four outputs per thread; inter is a multiple of 4
 template <typename T>
 __global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total4) {
+    wait_for_prior_kernels();
     allow_dependents();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total4) return;
@@ -197,6 +203,7 @@ __global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ ou
 // bfloat16, eight outputs per thread (16-byte loads and stores); inter and block are multiples of 8
 __global__ void swiglu_kernel8(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter,
                                int block, size_t total8) {
+    wait_for_prior_kernels();
     allow_dependents();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total8) return;
@@ -228,18 +235,17 @@ RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, 
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_BF16 && (inter & 7) == 0 && (block & 7) == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         const size_t total8 = (size_t)n_tokens * inter / 8;
-        swiglu_kernel8<<<(unsigned)((total8 + threads - 1) / threads), threads, 0, s>>>(
-            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total8);
-        RMX_CHECK_LAUNCH("swiglu");
+        RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel8, dim3((unsigned)((total8 + threads - 1) / threads)), dim3(threads), 0, s,
+                                            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total8), "swiglu");
         return 0;
     }
     const size_t total = (size_t)n_tokens * inter / (vec ? 4 : 1);
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dtype == RMX_F32) {
-        if (vec) swiglu_kernel4<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, block, total);
+        if (vec) RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel4<float>, dim3(blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, inter, block, total), "swiglu");
         else swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, block, total);
     } else if (dtype == RMX_BF16) {
-        if (vec) swiglu_kernel4<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total);
+        if (vec) RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel4<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total), "swiglu");
         else swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total);
     } else {
         RMX_FAIL("swiglu: unknown dtype %d", dtype);

@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_kernel(
     T* __restrict__ k_pool, T* __restrict__ v_pool, T* __restrict__ q_out, int n_tokens, int nq, int nkv, int hd,
     int row_stride, int write_kv, int* __restrict__ status, const float* __restrict__ cos_sin) {
     extern __shared__ float smem[];
+    wait_for_prior_kernels();
+    allow_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -95,6 +97,8 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_kernel(
 // cos_sin[t][j] = cos(pos_t * inv_freq[j]), cos_sin[t][half + j] = sin(...): once per step.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float* __restrict__ cos_sin, int n_tokens, int half) {
+    wait_for_prior_kernels();
+    allow_dependents();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_tokens * half) return;
     const int t = idx / half, j = idx - t * half;
@@ -113,6 +117,8 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_128_kernel(
     __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ q_out, int n_tokens, int nq, int nkv, int row_stride,
     int write_kv, int* __restrict__ status) {
     constexpr int hd = 128;
+    wait_for_prior_kernels();
+    allow_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -182,8 +188,8 @@ RMX_API int rmx_rope_table(const int* positions, const float* inv_freq, float* c
     if (n_tokens == 0 || rotary_dim == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && rotary_dim > 0 && rotary_dim % 2 == 0, "rope_table: bad sizes");
     const int half = rotary_dim / 2, total = n_tokens * half;
-    rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, cos_sin, n_tokens, half);
-    RMX_CHECK_LAUNCH("rope_table");
+    RMX_CHECK_LAUNCHED(launch_dependent(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, (cudaStream_t)stream, positions,
+                                        inv_freq, cos_sin, n_tokens, half), "rope_table");
     return 0;
 }
 
@@ -206,21 +212,21 @@ RMX_API int rmx_qk_rope_cache(const void* qkv, const float* q_norm, const float*
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_BF16 && hd == 128 && rotary_dim == 128 && cos_sin != nullptr && row_stride % 4 == 0 &&
         ((uintptr_t)qkv & 7) == 0) {
-        qk_rope_cache_128_kernel<<<blocks, WARPS * 32, 0, s>>>(
+        RMX_CHECK_LAUNCHED(launch_dependent(qk_rope_cache_128_kernel, dim3(blocks), dim3(WARPS * 32), 0, s,
             (const __nv_bfloat16*)qkv, q_norm, k_norm, eps, cos_sin, positions, seq_index, block_table, table_stride, page_size,
-            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, n_tokens, nq, nkv, row_stride, write_kv, status);
-        RMX_CHECK_LAUNCH("qk_rope_cache_128");
+            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, n_tokens, nq, nkv, row_stride, write_kv, status),
+            "qk_rope_cache_128");
         return 0;
     }
     if (dtype == RMX_F32)
-        qk_rope_cache_kernel<float><<<blocks, WARPS * 32, smem, s>>>(
+        RMX_CHECK_LAUNCHED(launch_dependent(qk_rope_cache_kernel<float>, dim3(blocks), dim3(WARPS * 32), smem, s,
             (const float*)qkv, q_norm, k_norm, eps, inv_freq, rotary_dim, positions, seq_index, block_table,
-            table_stride, page_size, (float*)k_pool, (float*)v_pool, (float*)q_out, n_tokens, nq, nkv, hd, row_stride, write_kv, status, cos_sin);
+            table_stride, page_size, (float*)k_pool, (float*)v_pool, (float*)q_out, n_tokens, nq, nkv, hd, row_stride, write_kv, status, cos_sin), "qk_rope_cache");
     else if (dtype == RMX_BF16)
-        qk_rope_cache_kernel<__nv_bfloat16><<<blocks, WARPS * 32, smem, s>>>(
+        RMX_CHECK_LAUNCHED(launch_dependent(qk_rope_cache_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), smem, s,
             (const __nv_bfloat16*)qkv, q_norm, k_norm, eps, inv_freq, rotary_dim, positions, seq_index, block_table,
             table_stride, page_size, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, n_tokens,
-            nq, nkv, hd, row_stride, write_kv, status, cos_sin);
+            nq, nkv, hd, row_stride, write_kv, status, cos_sin), "qk_rope_cache");
     else
         RMX_FAIL("qk_rope_cache: unknown dtype %d", dtype);
     RMX_CHECK_LAUNCH("qk_rope_cache");

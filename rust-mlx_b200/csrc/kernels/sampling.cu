@@ -18,6 +18,8 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     __shared__ float s_val[THREADS];
     __shared__ int s_idx[THREADS];
     __shared__ int s_choice;
+    wait_for_prior_kernels();
+    allow_dependents();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * ld;
 
@@ -94,7 +96,7 @@ RMX_API int rmx_sample(const float* logits, int ld, const float* temperature, co
     RMX_REQUIRE(n_rows > 0 && vocab > 0 && ld >= vocab, "sample: bad sizes");
     RMX_REQUIRE(temperature == nullptr || uniform != nullptr, "sample: temperatures without uniform numbers");
     RMX_REQUIRE((slots == nullptr) == (last_tokens == nullptr), "sample: slots and last_tokens go together");
-    sample_kernel<<<n_rows, THREADS, 0, (cudaStream_t)stream>>>(logits, ld, temperature, uniform, out, vocab, slots, last_tokens);
-    RMX_CHECK_LAUNCH("sample");
+    RMX_CHECK_LAUNCHED(launch_dependent(sample_kernel, dim3(n_rows), dim3(THREADS), 0, (cudaStream_t)stream, logits, ld, temperature,
+                                        uniform, out, vocab, slots, last_tokens), "sample");
     return 0;
 }

@@ -452,3 +452,11 @@ def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq,
         c_int(hd), c_int(window), c_float(scale), c_int(k_pool.shape[0]), _ptr(batch.status, torch.int32, "status"),
         _stream()))
     _launched()
+
+
+def set_dependent_launch(on: bool) -> None:
+    """Programmatic dependent launch of this package's kernels (on by default): a kernel's blocks may take their
+    places while the kernel before it drains, and the tcgen05 product fetches weights meanwhile."""
+    global dependent_launch
+    dependent_launch = bool(on)
+    kernels_library().rmx_set_dependent_launch(c_int(1 if on else 0))
