@@ -375,7 +375,10 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
                 }
                 mx = mx == -INFINITY ? mx : mx * p.scale_log2;
             }
-            const float m_new = fmaxf(m, mx);
+            // m is the reference the exponentials are taken against, not the true maximum: it moves only when a
+            // score exceeds it by more than 8 (probabilities then stay below 2^8, far from overflow), so that O, which
+            // sits in tensor memory, has to be rescaled only rarely
+            const float m_new = (m == -INFINITY || mx > m + 8.f) ? fmaxf(m, mx) : m;
             const float corr = m_new == -INFINITY ? 1.f : ex2(m - m_new);
             const float neg_ref = m_new == -INFINITY ? 0.f : -m_new;
             m = m_new;

@@ -109,7 +109,10 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
 }
 
 // bfloat16, head size 128, all 128 numbers rotated, table given: a lane holds four neighbouring numbers of the
-// head; the partner of number j is j + 64, sixteen lanes away.
+// head; the partner of number j is j + 64, sixteen lanes away.  A warp takes PER_WARP (token, head) items and
+// issues all their loads before it works on the first, so that their latencies overlap.
+constexpr int PER_WARP = 4;
+
 __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_128_kernel(
     const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
     const float* __restrict__ cos_sin, const int* __restrict__ positions, const int* __restrict__ seq_index,
@@ -121,65 +124,78 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_128_kernel(
     allow_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
-    const long long item = (long long)blockIdx.x * WARPS + warp;
-    if (item >= (long long)n_tokens * heads_total) return;
-    const int t = (int)(item / heads_total);
-    const int head = (int)(item % heads_total);
-    const __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)head * hd + lane * 4;
-    const uint2 raw = *reinterpret_cast<const uint2*>(src);
-    __nv_bfloat16* dst;
-    const float* norm_w;
-    bool rotate = true;
-    if (head < nq) {
-        dst = q_out + ((size_t)t * nq + head) * hd;
-        norm_w = q_norm;
-    } else {
-        const int pos = positions[t];
-        const int kvh = (head - nq) % nkv;
-        const bool is_v = head >= nq + nkv;
-        const int page = block_table[(size_t)seq_index[t] * table_stride + pos / page_size];
-        if (page < 0) {
-            if (lane == 0) atomicExch(status, 1);
-            return;
-        }
-        dst = (is_v ? v_pool : k_pool) + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * hd;
-        norm_w = is_v ? nullptr : k_norm;
-        rotate = !is_v;
-    }
-    if (!rotate) {  // values pass through
-        *reinterpret_cast<uint2*>(dst + lane * 4) = raw;
-        return;
-    }
-    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    float v[4] = {lo.x, lo.y, hi.x, hi.y};
-    if (norm_w) {
-        float ss = v[0] * v[0];
-        ss += v[1] * v[1];
-        ss += v[2] * v[2];
-        ss += v[3] * v[3];
-        ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)hd + eps);
-        const float4 w = *reinterpret_cast<const float4*>(norm_w + lane * 4);
-        v[0] = v[0] * inv * w.x; v[1] = v[1] * inv * w.y; v[2] = v[2] * inv * w.z; v[3] = v[3] * inv * w.w;
-    }
-    const int j = (lane & 15) * 4;   // index of the pair (j, j + 64) this lane's numbers belong to
-    const float4 cs = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * hd + j);
-    const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * hd + 64 + j);
-    const float c[4] = {cs.x, cs.y, cs.z, cs.w}, s_[4] = {sn.x, sn.y, sn.z, sn.w};
-    float out[4];
+    const int total = n_tokens * heads_total;   // the launcher keeps this below 2^31
+    const int first = (blockIdx.x * WARPS + warp) * PER_WARP;
+    if (first >= total) return;
+    uint2 raw[PER_WARP];
+    __nv_bfloat16* dst[PER_WARP];
+    const float* norm_w[PER_WARP];
+    int tok[PER_WARP];
+    bool rotate[PER_WARP], live[PER_WARP];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-        // lanes 0..15 hold x[j] (partner x[j + 64] comes from lane + 16): out = a cos - b sin
-        // lanes 16..31 hold x[j + 64] (partner x[j]):                      out = b cos + a sin
-        out[i] = lane < 16 ? v[i] * c[i] - other * s_[i] : v[i] * c[i] + other * s_[i];
+    for (int u = 0; u < PER_WARP; ++u) {
+        const int item = first + u;
+        live[u] = item < total;
+        const int t = live[u] ? item / heads_total : 0;
+        const int head = live[u] ? item - t * heads_total : 0;
+        tok[u] = t;
+        raw[u] = *reinterpret_cast<const uint2*>(qkv + (size_t)t * row_stride + (size_t)head * hd + lane * 4);
+        rotate[u] = true;
+        if (head < nq) {
+            dst[u] = q_out + ((size_t)t * nq + head) * hd;
+            norm_w[u] = q_norm;
+        } else {
+            const int pos = positions[t];
+            const int kvh = (head - nq) % nkv;
+            const bool is_v = head >= nq + nkv;
+            const int page = block_table[(size_t)seq_index[t] * table_stride + pos / page_size];
+            if (page < 0) {  // the host reserves pages before the step; never write through a hole
+                if (lane == 0 && live[u]) atomicExch(status, 1);
+                live[u] = false;
+            }
+            dst[u] = (is_v ? v_pool : k_pool) + (((size_t)(page < 0 ? 0 : page) * nkv + kvh) * page_size + pos % page_size) * hd;
+            norm_w[u] = is_v ? nullptr : k_norm;
+            rotate[u] = !is_v;
+        }
     }
-    __nv_bfloat162 o01 = __floats2bfloat162_rn(out[0], out[1]), o23 = __floats2bfloat162_rn(out[2], out[3]);
-    uint2 packed;
-    packed.x = *reinterpret_cast<uint32_t*>(&o01);
-    packed.y = *reinterpret_cast<uint32_t*>(&o23);
-    *reinterpret_cast<uint2*>(dst + lane * 4) = packed;
+#pragma unroll
+    for (int u = 0; u < PER_WARP; ++u) {
+        if (!live[u]) continue;
+        if (!rotate[u]) {  // values pass through
+            *reinterpret_cast<uint2*>(dst[u] + lane * 4) = raw[u];
+            continue;
+        }
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u].x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u].y));
+        float v[4] = {lo.x, lo.y, hi.x, hi.y};
+        if (norm_w[u]) {
+            float ss = v[0] * v[0];
+            ss += v[1] * v[1];
+            ss += v[2] * v[2];
+            ss += v[3] * v[3];
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)hd + eps);
+            const float4 w = *reinterpret_cast<const float4*>(norm_w[u] + lane * 4);
+            v[0] = v[0] * inv * w.x; v[1] = v[1] * inv * w.y; v[2] = v[2] * inv * w.z; v[3] = v[3] * inv * w.w;
+        }
+        const int j = (lane & 15) * 4;   // index of the pair (j, j + 64) this lane's numbers belong to
+        const float4 cs = *reinterpret_cast<const float4*>(cos_sin + (size_t)tok[u] * hd + j);
+        const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)tok[u] * hd + 64 + j);
+        const float c[4] = {cs.x, cs.y, cs.z, cs.w}, s_[4] = {sn.x, sn.y, sn.z, sn.w};
+        float out[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+            // lanes 0..15 hold x[j] (partner x[j + 64] comes from lane + 16): out = a cos - b sin
+            // lanes 16..31 hold x[j + 64] (partner x[j]):                      out = b cos + a sin
+            out[i] = lane < 16 ? v[i] * c[i] - other * s_[i] : v[i] * c[i] + other * s_[i];
+        }
+        __nv_bfloat162 o01 = __floats2bfloat162_rn(out[0], out[1]), o23 = __floats2bfloat162_rn(out[2], out[3]);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&o01);
+        packed.y = *reinterpret_cast<uint32_t*>(&o23);
+        *reinterpret_cast<uint2*>(dst[u] + lane * 4) = packed;
+    }
 }
 }  // namespace
 
@@ -211,8 +227,9 @@ RMX_API int rmx_qk_rope_cache(const void* qkv, const float* q_norm, const float*
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_BF16 && hd == 128 && rotary_dim == 128 && cos_sin != nullptr && row_stride % 4 == 0 &&
-        ((uintptr_t)qkv & 7) == 0) {
-        RMX_CHECK_LAUNCHED(launch_dependent(qk_rope_cache_128_kernel, dim3(blocks), dim3(WARPS * 32), 0, s,
+        ((uintptr_t)qkv & 7) == 0 && items < (1LL << 30)) {
+        const unsigned blocks128 = (unsigned)((items + (long long)WARPS * PER_WARP - 1) / (WARPS * PER_WARP));
+        RMX_CHECK_LAUNCHED(launch_dependent(qk_rope_cache_128_kernel, dim3(blocks128), dim3(WARPS * 32), 0, s,
             (const __nv_bfloat16*)qkv, q_norm, k_norm, eps, cos_sin, positions, seq_index, block_table, table_stride, page_size,
             (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, n_tokens, nq, nkv, row_stride, write_kv, status),
             "qk_rope_cache_128");
