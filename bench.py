@@ -28,6 +28,12 @@ QWEN3_8B = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidd
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
                 max_position_embeddings=4096)
+# the other layer sizes BASELINE.json names (configs[3] and configs[4]); the default run is configs[2]
+SHAPES = {
+    "qwen3-8b": QWEN3_8B,
+    "qwen3-4b": dict(QWEN3_8B, hidden_size=2560, intermediate_size=9728, tie_word_embeddings=True),
+    "qwen3-32b": dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600),
+}
 CONTEXT = 2048          # tokens each request holds when decoding starts
 MAX_CONTEXT = 4096
 PREFILL_TOKENS = 2048
@@ -216,7 +222,39 @@ def time_e2e(engine, batch, new_tokens):
     return decoded / r.decode_seconds, h2d, d2h
 
 
+def continuous(cfg, raw, a):
+    """64 requests, prompts of 128..3072 uniform-random ids, 256 generated tokens each, through the scheduler:
+    portions of prompts (at most 512 tokens a step) run beside the decoded tokens of the requests already past theirs."""
+    import random
+
+    import torch
+    from rust_mlx_b200.engine import Engine
+    rng = random.Random(0)
+    lengths = [rng.randrange(128, 3073) for _ in range(64)]
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, raw["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+    new_tokens = 256
+    cache_tokens = sum(-(-(n + new_tokens) // PAGE) * PAGE for n in lengths)
+    engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE, max_requests=64)
+    opts = dict(max_tokens=new_tokens, ignore_eos=True, prefill_chunk=512, max_batch_tokens=512 + 64, max_seqs=64)
+    engine.generate(prompts[:8], **dict(opts, max_tokens=8))            # warm-up: kernels, graphs of the first sizes
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    r = engine.generate_detailed(prompts, **opts)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    line = {"metric": "continuous batching: generated tok/s over the whole run", "value": round(r.generated_tokens / wall, 1),
+            "unit": "tok/s", "impl": "ours", "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": a.shape + " shape, random weights", "layers": a.layers, "requests": 64, "prompt_tokens": r.prompt_tokens,
+                       "generated_tokens": r.generated_tokens, "prefill_chunk": 512, "max_batch_tokens": 576, "page_size": PAGE},
+            "seconds": round(wall, 3), "steps": r.steps, "preemptions": r.preemptions,
+            "total_tok_per_s": round((r.generated_tokens + r.prompt_tokens) / wall, 1)}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
+    global CONTEXT, MAX_CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -226,6 +264,11 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, prefill and e2e")
     ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prefill only (for profiling it)")
+    ap.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES), help="layer sizes (default: the Qwen3-8B shape)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when decoding starts")
+    ap.add_argument("--continuous", action="store_true",
+                    help="instead: 64 requests with prompts of 128..3072 random ids, 256 tokens each, through the "
+                         "scheduler with chunked prefill of 512 (continuous batching); prints its own JSON line")
     ap.add_argument("--policy", default="auto", choices=["auto", "measured", "all", "none"],
                     help="which products of few rows take the tcgen05 kernel (auto: time both when the engine starts)")
     a = ap.parse_args()
@@ -245,8 +288,15 @@ def main():
 
     from rust_mlx_b200.kernels import ops
     ops.tcgen05_policy = a.policy
-    raw = dict(QWEN3_8B, num_hidden_layers=a.layers)
+    CONTEXT = a.context
+    base = SHAPES[a.shape]
+    if a.shape != "qwen3-8b" and a.layers == QWEN3_8B["num_hidden_layers"]:
+        a.layers = base["num_hidden_layers"]
+    MAX_CONTEXT = max(MAX_CONTEXT, 2 * CONTEXT)
+    raw = dict(base, num_hidden_layers=a.layers, max_position_embeddings=MAX_CONTEXT)
     cfg = Qwen3Config.from_dict(raw)
+    if a.continuous:
+        return continuous(cfg, raw, a)
     biggest = 1 if (a.no_points or a.prefill_only) else max(64, a.batch)
     cache_tokens = max(biggest, a.batch) * (CONTEXT + 2 * PAGE + a.steps + a.warmup + 64)
     engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE,
@@ -270,12 +320,13 @@ def main():
     step_bytes = weight_bytes + a.batch * (CONTEXT + a.warmup + a.steps / 2) * kv_bytes_per_token(raw, a.layers)
     achieved = step_bytes / (ms * 1e-3) / 1e9
     line = {
-        "metric": "decode tok/s at batch 8, context 2048 (Qwen3-8B shape, bf16)", "value": round(value, 2), "unit": "tok/s",
+        "metric": f"decode tok/s at batch {a.batch}, context {CONTEXT} ({a.shape} shape, bf16)", "value": round(value, 2), "unit": "tok/s",
         "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "Qwen3-8B shape, random weights", "layers": a.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
-                   "hidden": 4096, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288,
-                   "vocab": 151936, "global_batch": a.batch, "seq_len": CONTEXT, "max_context": MAX_CONTEXT,
+        "config": {"model": a.shape + " shape, random weights", "layers": a.layers, "layers_full": base["num_hidden_layers"],
+                   "hidden": raw["hidden_size"], "q_heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+                   "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"],
+                   "vocab": raw["vocab_size"], "global_batch": a.batch, "seq_len": CONTEXT, "max_context": MAX_CONTEXT,
                    "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (15 GB of weights per step), no flush",
                    "peaks": pk["source"]},
