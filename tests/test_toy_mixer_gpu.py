@@ -119,3 +119,107 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
             ids.append(t)
     finally:
         unregister_architecture("ToyStateForCausalLM")
+
+
+def test_toy_routed_feed_forward_and_unrotated_layers(tmp_path):
+    """Two more toy parts defined here and built by the engine without a change to its files: a feed-forward
+    that routes every token to its best expert of three (router logits and the choice in float32, so the
+    choice does not depend on the batch), and attention layers without any position encoding.  Stepped in
+    portions and mixed batches, compared with the plain restatement below."""
+    import replay
+    from rust_mlx_b200.config import Qwen3Config
+    from rust_mlx_b200.engine import Engine
+    from rust_mlx_b200.models.qwen3 import build_qwen3
+    from rust_mlx_b200.parts import FeedForward, ParamSpec
+    from rust_mlx_b200.parts.position import NoPositionEncoding
+    from rust_mlx_b200.registry import register_architecture, unregister_architecture
+    from rust_mlx_b200.weights import write_random_model
+
+    class RoutedFeedForward(FeedForward):
+        def __init__(self, prefix, width, inner, experts):
+            self.prefix, self.width, self.inner, self.experts = prefix, width, inner, experts
+
+        def param_specs(self):
+            p = self.prefix
+            specs = [ParamSpec(f"{p}.router.weight", (self.experts, self.width), "linear", "float32")]
+            for e in range(self.experts):
+                specs += [ParamSpec(f"{p}.experts.{e}.up.weight", (self.inner, self.width)),
+                          ParamSpec(f"{p}.experts.{e}.down.weight", (self.width, self.inner))]
+            return specs
+
+        def bind(self, tensors, ctx):
+            super().bind(tensors, ctx)
+            p = self.prefix
+            self.router = tensors[f"{p}.router.weight"]
+            self.up = [tensors[f"{p}.experts.{e}.up.weight"] for e in range(self.experts)]
+            self.down = [tensors[f"{p}.experts.{e}.down.weight"] for e in range(self.experts)]
+
+        def forward(self, x, batch=None):
+            logits = x.float() @ self.router.t()
+            choice = logits.argmax(-1)
+            weight = torch.softmax(logits, -1).gather(1, choice[:, None])
+            y = torch.zeros_like(x)
+            for e in range(self.experts):
+                rows = (choice == e).nonzero()[:, 0]
+                if rows.numel():
+                    h = torch.relu(x[rows].float() @ self.up[e].float().t())
+                    y[rows] = ((h @ self.down[e].float().t()) * weight[rows]).to(x.dtype)
+            return y
+
+    def build(config):
+        spec = build_qwen3(config)
+        for i, block in enumerate(spec.blocks):
+            block.ffn = RoutedFeedForward(f"model.layers.{i}.moe", config.hidden_size, config.intermediate_size, 3)
+            if i % 2 == 1:
+                block.mixer.position = NoPositionEncoding()
+        return spec
+
+    def plain_logits(folder, ids):
+        config, tensors = plain.read_folder(folder)
+        w = plain.prepare_weights(config, tensors, None)
+        eps, T = config["rms_norm_eps"], len(ids)
+        nq, nkv, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+        pos = torch.arange(T)
+        h = plain.embedding(w["model.embed_tokens.weight"], ids)
+        for i in range(config["num_hidden_layers"]):
+            p = f"model.layers.{i}"
+            x = plain.rms_norm(h, w[p + ".input_layernorm.weight"], eps)
+            a = p + ".self_attn"
+            q = plain.rms_norm(plain.linear(x, w[a + ".q_proj.weight"]).reshape(T, nq, hd), w[a + ".q_norm.weight"], eps)
+            k = plain.rms_norm(plain.linear(x, w[a + ".k_proj.weight"]).reshape(T, nkv, hd), w[a + ".k_norm.weight"], eps)
+            v = plain.linear(x, w[a + ".v_proj.weight"]).reshape(T, nkv, hd)
+            if i % 2 == 0:
+                q, k = plain.rope(q, pos, config["rope_theta"], hd), plain.rope(k, pos, config["rope_theta"], hd)
+            o = plain.attention_scores(q, k, v, pos, 0)
+            h = h + plain.linear(o.reshape(T, nq * hd), w[a + ".o_proj.weight"])
+            x = plain.rms_norm(h, w[p + ".post_attention_layernorm.weight"], eps)
+            logits = x.float().double() @ w[p + ".moe.router.weight"].t()
+            choice = logits.float().argmax(-1)
+            weight = torch.softmax(logits, -1).gather(1, choice[:, None])
+            y = torch.zeros_like(x)
+            for e in range(3):
+                rows = (choice == e).nonzero()[:, 0]
+                if rows.numel():
+                    hid = torch.relu(x[rows] @ w[f"{p}.moe.experts.{e}.up.weight"].t())
+                    y[rows] = (hid @ w[f"{p}.moe.experts.{e}.down.weight"].t()) * weight[rows]
+            h = h + y
+        return plain.linear(plain.rms_norm(h, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+
+    register_architecture("ToyRoutedForCausalLM", Qwen3Config, build)
+    try:
+        raw = dict(tiny.TINY_A, architectures=["ToyRoutedForCausalLM"])
+        folder = str(tmp_path / "routed")
+        write_random_model(Qwen3Config.from_dict(raw), folder, seed=31, store_dtype="float32")
+        names = set(plain.read_folder(folder)[1])
+        assert "model.layers.0.moe.router.weight" in names and "model.layers.0.mlp.gate_proj.weight" not in names
+        reqs = {f"r{i}": p for i, p in enumerate(tiny.prompts(256, [19, 6, 33, 12], seed=2))}
+        ref = {rid: plain_logits(folder, ids).float() for rid, ids in reqs.items()}
+        for way in ("whole", "portions", "mixed"):
+            steps = getattr(replay, way)(reqs, **({"live": 3} if way == "mixed" else {}))
+            eng = Engine(folder, dtype="float32", max_tokens=replay.tokens_needed(steps, 16), page_size=16, max_requests=3)
+            assert eng.graphs is None      # the toy part does not declare itself safe to capture
+            got = replay.run_engine(eng, steps)
+            for rid in reqs:
+                assert tiny.max_abs(got[rid], ref[rid]) < 5e-5, (way, rid)
+    finally:
+        unregister_architecture("ToyRoutedForCausalLM")
