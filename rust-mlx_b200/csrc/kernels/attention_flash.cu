@@ -68,6 +68,7 @@ struct FlashParams {
     int* status;
     int n_seqs, n_tokens, nq, nkv, group, tq, table_stride, page_size, page_shift, window, n_splits;
     float scale_log2;
+    int cluster;                   // the splits of a (sequence, kv head) are one thread-block cluster (decoding by TMA)
 };
 
 template <int HD, bool KEYSPLIT>
@@ -419,6 +420,15 @@ __device__ __forceinline__ void tma_box(void* smem, const CUtensorMap* map, uint
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
         ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// The address, in the cluster's shared window, of what `local` is in the block of the given rank.
+__device__ __forceinline__ uint32_t in_block(const void* local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    return remote;
+}
 // Element (row, col) of a key or value tile held as HD/64 blocks of [64 rows][64 columns], rows of 128
 // bytes whose 16-byte chunks are exchanged by the row's low three bits (the 128-byte swizzle of TMA).
 template <int HD>
@@ -440,8 +450,13 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_decode_raw) + 1023) & ~(uintptr_t)1023);
     __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(base);                        // [STAGES][K tile | V tile]
     __nv_bfloat16* Qs = KV + STAGES * 2 * TILE_ELEMS;                                  // [QROWS][STRIDE]
+    // decoding with its splits as a cluster: where the other splits leave their shares of this block's output columns
+    float4* recv = reinterpret_cast<float4*>(Qs + QROWS * STRIDE);                     // [splits][ceil(16 * HD / 4 / splits)]
+    float2* recv_ml = reinterpret_cast<float2*>(recv + 16 * HD / 4 + 8);               // [8 splits][16 rows] (max, sum)
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES];
     __shared__ int s_failed, s_tile[3];
+    constexpr int TABLE_KEPT = 512;
+    __shared__ int s_table[KEYSPLIT ? TABLE_KEPT : 1];   // decoding: the head of the sequence's block table
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.y, split = blockIdx.z;
@@ -455,13 +470,31 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
     }
+    // the stages start as zeros so that a part of a tile that is never fetched (a page the request does not
+    // hold) has finite numbers in it
+    for (int idx = tid; idx < STAGES * 2 * TILE_ELEMS / 8; idx += DTHREADS)
+        reinterpret_cast<uint4*>(KV)[idx] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    __syncthreads();
+    // (the matching wait stands before the first store into another block's shared memory: every block of the
+    // cluster has started by then)
+    if (KEYSPLIT && p.cluster) asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     // everything above needs nothing from the kernels before this one; queries, keys and tables do
+    allow_dependents();
     wait_for_prior_kernels();
-    int seq, tok0, n_tok;
+    int seq, tok0, n_tok, pos0;
     if constexpr (KEYSPLIT) {   // one tile per sequence
         seq = blockIdx.x;
-        tok0 = p.q_start[seq];
-        n_tok = p.q_start[seq + 1] - tok0;
+        // loads that do not wait for one another: the table's head, the sequence's tokens, and the position of
+        // token number `seq`, which is the sequence's first token whenever every sequence brings one token
+        if (warp == NWARPS) {
+            const int* row = p.block_table + (size_t)seq * p.table_stride;
+            for (int j = lane; j < min(p.table_stride, TABLE_KEPT); j += 32) s_table[j] = row[j];
+        }
+        const int a = p.q_start[seq], b = p.q_start[seq + 1], guess = p.positions[seq];
+        tok0 = a;
+        n_tok = b - a;
+        pos0 = tok0 == seq ? guess : p.positions[tok0];
     } else {
         // which sequence and which of its tiles this block has: the threads scan the sequences' tile counts together
         __shared__ int s_warp_total[NWARPS + 1];
@@ -501,8 +534,8 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
         __syncthreads();
         seq = s_tile[0]; tok0 = s_tile[1]; n_tok = s_tile[2];
         if (seq < 0) return;  // the grid is an upper bound
+        pos0 = p.positions[tok0];
     }
-    const int pos0 = p.positions[tok0];
     const int rows_valid = n_tok * p.group;
     const int* table = p.block_table + (size_t)seq * p.table_stride;
     const int lo_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
@@ -513,25 +546,23 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
     const int kt_end = min(kt_hi + 1, kt_begin + per_split);
     const int n_mine = kt_begin < kt_end ? kt_end - kt_begin : 0;
 
-    // Q rows (zeros beyond the tile's rows); the stages start as zeros so that a part of a tile that is never
-    // fetched (a page the request does not hold) has finite numbers in it
-    for (int idx = tid; idx < QROWS * CHUNKS; idx += DTHREADS) {
-        const int r = idx / CHUNKS, c = idx - r * CHUNKS;
-        const bool valid = r < rows_valid;
-        const int tok = valid ? r / p.group : 0, g = valid ? r - tok * p.group : 0;
-        cp_async16(Qs + r * STRIDE + c * 8, p.q + ((size_t)(tok0 + tok) * p.nq + kvh * p.group + g) * HD + c * 8, valid);
+    // Q rows (zeros beyond the tile's rows), fetched by the computing warps; the producer does not wait for them
+    if (warp < NWARPS) {
+        for (int idx = tid; idx < QROWS * CHUNKS; idx += NWARPS * 32) {
+            const int r = idx / CHUNKS, c = idx - r * CHUNKS;
+            const bool valid = r < rows_valid;
+            const int tok = valid ? r / p.group : 0, g = valid ? r - tok * p.group : 0;
+            cp_async16(Qs + r * STRIDE + c * 8, p.q + ((size_t)(tok0 + tok) * p.nq + kvh * p.group + g) * HD + c * 8, valid);
+        }
+        cp_async_commit();
     }
-    cp_async_commit();
-    for (int idx = tid; idx < STAGES * 2 * TILE_ELEMS / 8; idx += DTHREADS)
-        reinterpret_cast<uint4*>(KV)[idx] = make_uint4(0u, 0u, 0u, 0u);
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    cp_async_wait<0>();
-    __syncthreads();
 
     if (warp == NWARPS) {
+        __syncwarp();   // the table's head is in shared memory
         if (lane == 0) {
             // ---- producer: per tile, 64 / box_rows boxes of rows by HD / 64 boxes of columns, for K and for V
             const int boxes = BN / box_rows;
+            auto entry = [&](int j) { return KEYSPLIT && j < TABLE_KEPT ? s_table[j] : table[j]; };
             for (int i = 0; i < n_mine; ++i) {
                 const int st = i % STAGES, round = i / STAGES, kt = kt_begin + i;
                 if (round > 0 && !mbar_wait(&empty_bar[st], (round - 1) & 1)) { atomicExch(&s_failed, 1); break; }
@@ -539,7 +570,7 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
                 for (int b = 0; b < boxes; ++b) {
                     const int kp = kt * BN + b * box_rows;
                     if (kp > pos_last || kp + box_rows <= lo_first) continue;
-                    if (table[kp >> p.page_shift] >= 0) bytes += 2u * box_rows * HD * 2u;
+                    if (entry(kp >> p.page_shift) >= 0) bytes += 2u * box_rows * HD * 2u;
                     else atomicExch(p.status, 2);
                 }
                 mbar_expect_tx(&full_bar[st], bytes);
@@ -548,7 +579,7 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
                 for (int b = 0; b < boxes; ++b) {
                     const int kp = kt * BN + b * box_rows;
                     if (kp > pos_last || kp + box_rows <= lo_first) continue;
-                    const int page = table[kp >> p.page_shift];
+                    const int page = entry(kp >> p.page_shift);
                     if (page < 0) continue;
                     const int row = (page * p.nkv + kvh) * p.page_size + (kp & (p.page_size - 1));
 #pragma unroll
@@ -560,6 +591,9 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
             }
         }
         __syncwarp();
+    } else {
+        cp_async_wait<0>();
+        asm volatile("bar.sync 1, %0;\n" ::"n"(NWARPS * 32) : "memory");   // the computing warps among themselves
     }
 
     // ---- computing warps.  Rows: each warp owns 16 of the tile's rows and all 64 keys.  Keys (KEYSPLIT): the same
@@ -678,7 +712,6 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[stage]);
     }
-    allow_dependents();
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
@@ -726,6 +759,7 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
 #pragma unroll
     for (int i = 0; i < 2 && warp < NWARPS; ++i) {
         const int r = (lane >> 2) + 8 * i;
+        if (r >= rows_valid) continue;
 #pragma unroll
         for (int d = 0; d < DTILES; ++d) {
             const int col = d * 8 + (lane & 3) * 2;
@@ -737,6 +771,67 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
         }
     }
     __syncthreads();
+    if (p.cluster) {
+        // The splits of this (sequence, kv head) are one cluster, and the output's groups of four columns are dealt
+        // out among its blocks: group number i falls to block i % n.  Every block adds its four warps' results and
+        // stores each group's sum, with its row's (max, sum), into the shared memory of the block the group falls
+        // to; after one cluster barrier each block holds all splits' shares of its groups and adds them in split
+        // order.  Nothing is read from another block's memory, so no block waits for a second barrier.
+        const int n = p.n_splits, per_block = (16 * (HD / 4) + n - 1) / n;
+        uint32_t rank;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+        asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");   // all blocks of the cluster run
+        for (int it = tid; it < rows_valid * (HD / 4); it += DTHREADS) {
+            const int r = it / (HD / 4), d = (it - r * (HD / 4)) * 4;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, sml[(w * 16 + r) * 2]);
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < NWARPS; ++w) {
+                const float mw = sml[(w * 16 + r) * 2];
+                const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+                const float4 v = *reinterpret_cast<const float4*>(so + (w * 16 + r) * HD + d);
+                L += f * sml[(w * 16 + r) * 2 + 1];
+                acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+            }
+            const uint32_t to = (uint32_t)(it % n);
+            const uint32_t dst = in_block(recv + rank * per_block + it / n, to);
+            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
+            if (d == 0) {
+                for (int z = 0; z < n; ++z) {
+                    const uint32_t dml = in_block(recv_ml + rank * 16 + r, (uint32_t)z);
+                    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};\n" ::"r"(dml), "f"(M), "f"(L) : "memory");
+                }
+            }
+        }
+        cluster_sync_all();
+        for (int j = tid; j < per_block; j += DTHREADS) {
+            const int it = j * n + (int)rank;
+            if (it >= rows_valid * (HD / 4)) break;
+            const int r = it / (HD / 4), d = (it - r * (HD / 4)) * 4;
+            float M = -INFINITY;
+            for (int z = 0; z < n; ++z) M = fmaxf(M, recv_ml[z * 16 + r].x);
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int z = 0; z < n; ++z) {      // in split order
+                const float2 ml = recv_ml[z * 16 + r];
+                const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
+                const float4 v = recv[z * per_block + j];
+                L += f * ml.y;
+                acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+            }
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            const int tok = r / p.group, g = r - tok * p.group;
+            const size_t row = (size_t)(tok0 + tok) * p.nq + kvh * p.group + g;
+            uint2 packed;
+            packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+            packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2*>(p.out + row * HD + d) = packed;
+        }
+        return;
+    }
     for (int idx = tid; idx < rows_valid * HD; idx += DTHREADS) {
         const int r = idx / HD, d = idx - r * HD;
         float M = -INFINITY;
@@ -772,22 +867,48 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // Two rounds of loads, each of loads that do not wait for one another: first every split's (m, l) of every
+    // row, from which each row's factors 2^(m_z - M) / L follow; then the partial outputs, four floats at a time.
     const size_t rows_all = (size_t)p.n_tokens * p.nq;
-    for (int idx = tid; idx < rows_valid * HD; idx += DTHREADS) {
-        const int r = idx / HD, d = idx - r * HD;
+    float* factor = reinterpret_cast<float*>(KV);          // [n_splits][16]; the partial sums in KV are spent
+    for (int idx = tid; idx < p.n_splits * rows_valid; idx += DTHREADS) {
+        const int z = idx / rows_valid, r = idx - z * rows_valid;
         const int tok = r / p.group, g = r - tok * p.group;
         const size_t row = (size_t)(tok0 + tok) * p.nq + kvh * p.group + g;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (z * rows_all + row) * 2));
+        factor[z * 16 + r] = ml.x;
+        factor[(p.n_splits + z) * 16 + r] = ml.y;
+    }
+    __syncthreads();
+    if (tid < rows_valid) {
         float M = -INFINITY;
-        for (int z = 0; z < p.n_splits; ++z) M = fmaxf(M, __ldcg(p.part_ml + (z * rows_all + row) * 2));
-        float L = 0.f, acc = 0.f;
-        for (int z = 0; z < p.n_splits; ++z) {
-            const float mz = __ldcg(p.part_ml + (z * rows_all + row) * 2);
-            if (mz == -INFINITY) continue;
-            const float f = exp2f(mz - M);
-            L += f * __ldcg(p.part_ml + (z * rows_all + row) * 2 + 1);
-            acc += f * __ldcg(p.part_o + (z * rows_all + row) * HD + d);
+        for (int z = 0; z < p.n_splits; ++z) M = fmaxf(M, factor[z * 16 + tid]);
+        float L = 0.f;
+        for (int z = 0; z < p.n_splits; ++z) {      // in split order
+            const float mz = factor[z * 16 + tid];
+            const float f = mz == -INFINITY ? 0.f : exp2f(mz - M);
+            L += f * factor[(p.n_splits + z) * 16 + tid];
+            factor[z * 16 + tid] = f;
         }
-        p.out[row * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        for (int z = 0; z < p.n_splits; ++z) factor[z * 16 + tid] *= inv;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows_valid * (HD / 4); idx += DTHREADS) {
+        const int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
+        const int tok = r / p.group, g = r - tok * p.group;
+        const size_t row = (size_t)(tok0 + tok) * p.nq + kvh * p.group + g;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int z = 0; z < p.n_splits; ++z) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_o + (z * rows_all + row) * HD + d));
+            const float f = factor[z * 16 + r];
+            acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+        }
+        uint2 packed;
+        packed.x = pack_bf16(acc.x, acc.y);
+        packed.y = pack_bf16(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(p.out + row * HD + d) = packed;
     }
     if (tid == 0) p.counters[seq * p.nkv + kvh] = 0;   // zero again for the next launch
 }
@@ -892,7 +1013,9 @@ int launch_tma_as(const FlashParams& p, int n_tiles, long long pool_rows, cudaSt
     if (pool_map(&mk, p.k_pool, pool_rows, HD, box_rows) != 0) return -1;
     if (pool_map(&mv, p.v_pool, pool_rows, HD, box_rows) != 0) return -1;
     constexpr int QROWS = KEYSPLIT ? 16 : BM, STAGES = KEYSPLIT ? DSTAGES : 2;
-    constexpr size_t smem = 1024 + (size_t)STAGES * 2 * 64 * HD * 2 + (size_t)QROWS * (HD + 8) * 2;
+    // stages, Q rows and, for decoding, the cluster's receive buffers (16 rows of HD floats and 8 x 16 pairs)
+    constexpr size_t smem = 1024 + (size_t)STAGES * 2 * 64 * HD * 2 + (size_t)QROWS * (HD + 8) * 2 +
+                            (KEYSPLIT ? (size_t)16 * HD * 4 + 8 * 16 + 8 * 16 * 8 : 0);
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(attention_tma_kernel<HD, KEYSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -900,6 +1023,25 @@ int launch_tma_as(const FlashParams& p, int n_tiles, long long pool_rows, cudaSt
         raised = true;
     }
     dim3 grid(n_tiles, p.nkv, p.n_splits);
+    if (p.cluster) {
+        // the splits of one (sequence, kv head) as a cluster, and still a programmatic dependent of the kernel before
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(DTHREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = p.n_splits;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = rmx_dependent_launch_enabled() ? 2 : 1;
+        RMX_CHECK_LAUNCHED(cudaLaunchKernelEx(&cfg, attention_tma_kernel<HD, KEYSPLIT>, mk, mv, p, box_rows), "attention_tma (cluster)");
+        return 0;
+    }
     RMX_CHECK_LAUNCHED(launch_dependent(attention_tma_kernel<HD, KEYSPLIT>, grid, dim3(DTHREADS), smem, s, mk, mv, p, box_rows),
                        "attention_tma");
     return 0;
@@ -938,7 +1080,7 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     FlashParams p;
     p.q = (const __nv_bfloat16*)q; p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
     p.q_start = q_start; p.positions = positions; p.block_table = block_table; p.out = (__nv_bfloat16*)out;
-    p.part_o = part_o; p.part_ml = part_ml; p.status = status; p.counters = nullptr;
+    p.part_o = part_o; p.part_ml = part_ml; p.status = status; p.counters = nullptr; p.cluster = 0;
     p.n_seqs = n_seqs; p.n_tokens = n_tokens; p.nq = nq; p.nkv = nkv; p.group = group; p.tq = BM / group;
     p.table_stride = table_stride; p.page_size = page_size; p.window = window; p.n_splits = n_splits;
     p.page_shift = 0;
@@ -952,9 +1094,14 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     if (pool_pages > 0 && page_size >= 8 && (hd == 64 || hd == 128) && (!keysplit || n_tiles == n_seqs) &&
         ((uintptr_t)k_pool & 127) == 0 && ((uintptr_t)v_pool & 127) == 0) {
         const long long pool_rows = (long long)pool_pages * nkv * page_size;
-        if (keysplit) p.counters = counters;   // with counters the decoding arrangement combines its splits itself
+        // The decoding arrangement combines its splits itself: up to 8 as a thread-block cluster, through
+        // distributed shared memory; more (up to 128) through the partial buffers, the last block to finish adding
+        // them, if the caller gave counters.
+        if (keysplit && n_splits >= 2 && n_splits <= 8) p.cluster = 1;
+        else if (keysplit && n_splits <= 128) p.counters = counters;
         rc = hd == 64 ? launch_tma<64>(p, n_tiles, keysplit, pool_rows, s) : launch_tma<128>(p, n_tiles, keysplit, pool_rows, s);
-        if (rc == 0 && keysplit && counters) return 0;
+        if (rc == 0 && (p.cluster || p.counters)) return 0;
+        p.cluster = 0;
     } else
     switch (hd) {
         case 16: rc = launch_flash<16>(p, n_tiles, keysplit, s); break;

@@ -316,11 +316,17 @@ def _sm_count() -> int:
 
 def flash_splits(n_tiles: int, nkv: int, max_seq_len: int) -> int:
     """Few rows and long contexts (decoding): share a tile's keys among blocks so that every
-    SM has work.  Two blocks fit an SM: fill them once, not one and a bit."""
+    SM has work.  Two blocks fit an SM: fill them once, not one and a bit.  Up to 8 splits form a
+    thread-block cluster and add their results through shared memory, which costs far less than the
+    round through global memory that more splits take: more than 8 only where each would still
+    have 16 tiles of 64 keys."""
     blocks = n_tiles * nkv
     kv_tiles = -(-max_seq_len // 64)
     if blocks < 2 * _sm_count() and kv_tiles >= 4:
-        return max(1, min(2 * _sm_count() // blocks, kv_tiles // 2, 64))
+        splits = max(1, min(2 * _sm_count() // blocks, kv_tiles // 2, 64))
+        if splits > 8 and kv_tiles // splits < 16:
+            splits = 8
+        return splits
     return 1
 
 
