@@ -63,13 +63,21 @@ class AttentionMixer(Mixer):
         ops, ws, dt = self.ctx.ops, self.ctx.workspace, self.ctx.dtype
         n = x.shape[0]
         nq, nkv, hd = self.heads, self.kv_heads, self.head_dim
-        qkv = ws.get("qkv", (n, (nq + 2 * nkv) * hd), dt)
-        ops.linear(x, self.w_qkv, qkv, ws, batch.status)
         q = ws.get("q_rot", (n, nq * hd), dt)
-        ops.qk_rope_cache(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.position.inv_freq,
-                          self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
-                          cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, hd, not cache.read_only,
-                          batch.status, self.position.angles(batch))
+        angles = self.position.angles(batch)
+        if ops.qkv_heads_supported(n, hd, self.position.rotary_dim, dt, angles):
+            # few rows: the product norms, rotates and stores its heads itself
+            ops.gemm_qkv_heads(x, self.w_qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, angles,
+                               self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
+                               cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, not cache.read_only, ws,
+                               batch.status, dependent=ops.dependent_launch)
+        else:
+            qkv = ws.get("qkv", (n, (nq + 2 * nkv) * hd), dt)
+            ops.linear(x, self.w_qkv, qkv, ws, batch.status)
+            ops.qk_rope_cache(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.position.inv_freq,
+                              self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
+                              cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, hd, not cache.read_only,
+                              batch.status, angles)
         o = ws.get("attn_out", (n, nq * hd), dt)
         ops.attention(q, cache.k_pool, cache.v_pool, batch, cache.block_table, cache.page_size, o, nq, nkv, hd,
                       cache.window, self.scale, ws)

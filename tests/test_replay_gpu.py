@@ -68,6 +68,23 @@ def test_every_way_of_cutting_matches_the_plain_implementation(workdir, name, dt
     _cache[(name, dtype, way)] = got
 
 
+@pytest.mark.parametrize("way", ["tail_one_by_one", "mixed"])
+def test_heads_finished_in_the_products_epilogue(workdir, way, monkeypatch):
+    """Configuration C (heads of 128) in bfloat16 with the q/k/v product norming, rotating and storing its heads
+    itself wherever a step brings at most 16 tokens (off by default): the same bound as the separate kernels."""
+    from rust_mlx_b200.kernels import ops
+    monkeypatch.setattr(ops, "fused_qkv_heads", True)
+    monkeypatch.setattr(ops, "tcgen05_policy", "all")
+    raw, page, folder, reqs, ref = cached_setup(workdir, "C", "bfloat16")
+    steps = getattr(replay, way)(reqs)
+    eng = engine_for(folder, "bfloat16", page, replay.tokens_needed(steps, page))
+    before = ops.launch_count
+    got = replay.run_engine(eng, steps)
+    assert ops.launch_count > before
+    for rid in reqs:
+        assert tiny.max_abs(got[rid], ref[rid]) < TOL["bfloat16"], (way, rid)
+
+
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_float32_ways_agree_bit_for_bit(workdir, name):
     raw, page, folder, reqs, ref = cached_setup(workdir, name, "float32")
