@@ -287,7 +287,59 @@ def linear_bf16(x, w, out, workspace=None, status=None):
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
 
 
+class _Sequences:
+    """A run of neighbouring sequences of a batch, with what the attention kernels read of a batch.  Token
+    numbers in ``q_start`` stay those of the whole batch, so q, out and positions are passed whole."""
+
+    def __init__(self, batch, first: int, last: int):
+        self.q_start = batch.q_start[first:last + 1]
+        self.q_start_host = batch.q_start_host[first:last + 1]
+        self.n_seqs = last - first
+        lens = batch.seq_lens_host[first:last]
+        counts = [self.q_start_host[i + 1] - self.q_start_host[i] for i in range(self.n_seqs)]
+        self.max_seq_len, self.max_q_len = max(lens), max(counts)
+        self.positions, self.status = batch.positions, batch.status
+        self.first, self.last = first, last
+
+
+def _short_and_long(batch, group: int):
+    """A mixed step: decoded tokens (rows * group <= 16: the key-split kernel's case) beside prompt portions.  If
+    the short sequences are the batch's head or its tail, returns the two runs (short, long), else None."""
+    if getattr(batch, "seq_lens_host", None) is None or batch.n_seqs < 2:
+        return None
+    key = ("short_and_long", group)
+    memo = getattr(batch, "per_step", None)
+    if memo is not None and key in memo:
+        return memo[key]
+    starts = batch.q_start_host
+    short = [(starts[i + 1] - starts[i]) * group <= 16 for i in range(batch.n_seqs)]
+    n_short = sum(short)
+    found = None
+    if 0 < n_short < batch.n_seqs:
+        if all(short[:n_short]):
+            found = (_Sequences(batch, 0, n_short), _Sequences(batch, n_short, batch.n_seqs))
+        elif all(short[batch.n_seqs - n_short:]):
+            found = (_Sequences(batch, batch.n_seqs - n_short, batch.n_seqs), _Sequences(batch, 0, batch.n_seqs - n_short))
+    if memo is not None:
+        memo[key] = found
+    return found
+
+
 def attention(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=None):
+    """Picks the attention kernel for the dtype, head size and shape of the step.  A step that mixes decoded
+    tokens with prompt portions runs as two launches, each kind with the kernel made for it."""
+    group = nq // nkv
+    if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, group):
+        runs = _short_and_long(batch, group)
+        if runs is not None:
+            for run in runs:
+                _attention_bf16(q, k_pool, v_pool, run, block_table[run.first:run.last], page_size, out, nq, nkv, hd,
+                                window, scale, workspace)
+            return
+    _attention_bf16(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace)
+
+
+def _attention_bf16(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace):
     group = nq // nkv
     if (q.dtype == torch.bfloat16 and use_tcgen05_attention and getattr(batch, "max_q_len", 0) * group > 16
             and tcgen05_attention_supported(hd, group, page_size)):
