@@ -139,6 +139,7 @@ struct Params {
     const int* block_table;    // [seqs, table_stride]
     int* status;
     int n_seqs, nq, nkv, group, tq, table_stride, page_size, page_shift, window, box_rows;
+    int per_block;   // query tiles a block takes: 2 (they share each key tile) or, for small steps, 1 (more blocks)
     float scale_log2;
 };
 
@@ -186,7 +187,7 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
     // which sequence and which pair of its tiles this block has: pairs are counted sequence by sequence, and handed
     // out from the last to the first (tiles late in a sequence see the most keys)
     {
-        const int pair_tokens = 2 * p.tq;
+        const int pair_tokens = p.per_block * p.tq;
         int before_all = 0;
         for (int chunk = 0; chunk < p.n_seqs; chunk += THREADS) {
             const int sq = chunk + tid;
@@ -547,12 +548,16 @@ RMX_API int rmx_attention_tcgen05_supports(int hd, int group, int page_size) {
 
 RMX_API int rmx_attention_tcgen05_tile_tokens(int group) { return BM / group; }
 
-// n_tiles: the number of blocks: sum over sequences of ceil(tokens / (2 * 128 / group)) (a block takes two tiles).  pool_pages: pages in k_pool / v_pool.
+// tiles_per_block: 2 (a block takes two neighbouring query tiles of 128 rows, which share every key tile it fetches)
+// or 1 (twice the blocks: for steps so small that two tiles a block would leave SMs without work).
+// n_tiles: the number of blocks: sum over sequences of ceil(tokens / (tiles_per_block * 128 / group)).
+// pool_pages: pages in k_pool / v_pool.
 RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* q_start,
                                   const int* positions, const int* block_table, int table_stride, int page_size,
-                                  void* out, int n_seqs, int n_tokens, int n_tiles, int nq, int nkv, int hd, int window,
-                                  float scale, int pool_pages, int* status, void* stream) {
+                                  void* out, int n_seqs, int n_tokens, int n_tiles, int tiles_per_block, int nq, int nkv,
+                                  int hd, int window, float scale, int pool_pages, int* status, void* stream) {
     if (n_tokens == 0) return 0;
+    RMX_REQUIRE(tiles_per_block == 1 || tiles_per_block == 2, "attention_tcgen05: a block takes 1 or 2 tiles, not %d", tiles_per_block);
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tcgen05: %d query heads over %d kv heads", nq, nkv);
     const int group = nq / nkv;
     RMX_REQUIRE(rmx_attention_tcgen05_supports(hd, group, page_size),
@@ -566,6 +571,7 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
     p.out = (__nv_bfloat16*)out; p.q_start = q_start; p.positions = positions; p.block_table = block_table; p.status = status;
     p.n_seqs = n_seqs; p.nq = nq; p.nkv = nkv; p.group = group; p.tq = BM / group; p.table_stride = table_stride;
     p.page_size = page_size; p.window = window; p.box_rows = page_size < BN ? page_size : BN;
+    p.per_block = tiles_per_block;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2 = scale * LOG2E;

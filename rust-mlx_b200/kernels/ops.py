@@ -547,19 +547,24 @@ def tcgen05_attention_supported(hd: int, group: int, page_size: int) -> bool:
     return bool(kernels_library().rmx_attention_tcgen05_supports(c_int(hd), c_int(group), c_int(page_size)))
 
 
-def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale):
-    """Prompt portions: S = Q K^T and O += P V as tcgen05 MMAs with accumulators in tensor memory."""
+def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, per_block=None):
+    """Prompt portions: S = Q K^T and O += P V as tcgen05 MMAs with accumulators in tensor memory.  A block takes
+    two neighbouring tiles of 128 rows, which share the key tiles it fetches, unless that leaves SMs without work
+    (a portion of a few hundred tokens): then one tile a block."""
     lib = kernels_library()
-    pair = 2 * (128 // (nq // nkv))     # a block takes two neighbouring tiles of 128 rows
+    tile = 128 // (nq // nkv)
     starts = batch.q_start_host
-    n_tiles = sum(-(-(starts[i + 1] - starts[i]) // pair) for i in range(batch.n_seqs))
+    if per_block is None:
+        pairs = sum(-(-(starts[i + 1] - starts[i]) // (2 * tile)) for i in range(batch.n_seqs))
+        per_block = 2 if pairs * nkv >= _sm_count() else 1
+    n_tiles = sum(-(-(starts[i + 1] - starts[i]) // (per_block * tile)) for i in range(batch.n_seqs))
     check(lib.rmx_attention_tcgen05(
         _ptr(q, torch.bfloat16, "q"), _ptr(k_pool, torch.bfloat16, "k_pool"), _ptr(v_pool, torch.bfloat16, "v_pool"),
         _ptr(batch.q_start, torch.int32, "q_start"), _ptr(batch.positions, torch.int32, "positions"),
         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
-        _ptr(out, torch.bfloat16, "out"), c_int(batch.n_seqs), c_int(q.shape[0]), c_int(n_tiles), c_int(nq), c_int(nkv),
-        c_int(hd), c_int(window), c_float(scale), c_int(k_pool.shape[0]), _ptr(batch.status, torch.int32, "status"),
-        _stream()))
+        _ptr(out, torch.bfloat16, "out"), c_int(batch.n_seqs), c_int(q.shape[0]), c_int(n_tiles), c_int(per_block),
+        c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(k_pool.shape[0]),
+        _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched()
 
 
