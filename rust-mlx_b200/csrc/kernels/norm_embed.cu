@@ -127,28 +127,94 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
     }
 }
 
+// The same for rows of up to CHUNKS * 4 * blockDim numbers (a multiple of 4): every thread keeps its CHUNKS groups
+// of four in registers, all their loads under way at once, and the blocks are small enough for several to share an
+// SM.  The reduction order depends on the width and the block size only, as above.
+template <typename T, int CHUNKS>
+__global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restrict__ delta,
+                                        const int* __restrict__ rows, const float* __restrict__ w, float eps,
+                                        T* __restrict__ x, int width, int write_h) {
+    __shared__ float scratch[32];
+    wait_for_prior_kernels();
+    allow_dependents();
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* hrow = h + (size_t)src * width;
+    const T* drow = delta ? delta + (size_t)src * width : nullptr;
+    T* xrow = x + (size_t)r * width;
+    float4 v[CHUNKS], d[CHUNKS];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        v[c] = d[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < width) {
+            v[c] = *reinterpret_cast<const float4*>(hrow + i);
+            if (drow) load4(drow + i, d[c]);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        v[c].x += d[c].x; v[c].y += d[c].y; v[c].z += d[c].z; v[c].w += d[c].w;
+        if (write_h && i < width) *reinterpret_cast<float4*>(hrow + i) = v[c];
+        ss += v[c].x * v[c].x;
+        ss += v[c].y * v[c].y;
+        ss += v[c].z * v[c].z;
+        ss += v[c].w * v[c].w;
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        if (i < width) {
+            const float4 g = *reinterpret_cast<const float4*>(w + i);
+            store4(xrow + i, make_float4(v[c].x * inv * g.x, v[c].y * inv * g.y, v[c].z * inv * g.z, v[c].w * inv * g.w));
+        }
+    }
+}
+
+template <typename T>
+int launch_add_rmsnorm(float* h, const T* delta, const int* rows, const float* w, float eps, T* x, int n_rows, int width,
+                       int write_h, cudaStream_t s) {
+    const int groups = width / 4;
+    if ((width & 3) == 0 && groups <= 1024 && n_rows <= 256) {
+        // few rows (decoding): as many threads as the row has groups of four, so that a row's latency is one load
+        const int threads = (groups + 31) / 32 * 32;
+        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, s, h, delta, rows, w, eps,
+                                            x, width, write_h), "add_rmsnorm");
+        return 0;
+    }
+    constexpr int CHUNKS = 4;
+    if ((width & 3) == 0 && groups <= CHUNKS * 1024) {
+        // many rows: as few threads as hold the row in CHUNKS groups each (at least a warp), several blocks an SM
+        int threads = ((groups + CHUNKS - 1) / CHUNKS + 31) / 32 * 32;
+        threads = threads < 32 ? 32 : threads;
+        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, CHUNKS>, dim3(n_rows), dim3(threads), 0, s, h, delta, rows, w, eps,
+                                            x, width, write_h), "add_rmsnorm");
+        return 0;
+    }
+    const int threads = block_threads(width);
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, s, h, delta, rows, w, eps, x, width,
+                                        write_h), "add_rmsnorm");
+    return 0;
+}
+
 RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const int* rows, const float* w, float eps, void* x,
                             int n_rows, int width, int write_h, int dtype, void* stream) {
     if (n_rows == 0) return 0;
     RMX_REQUIRE(n_rows > 0 && width > 0, "add_rmsnorm: bad sizes");
     RMX_REQUIRE((size_t)width * 4 <= 160 * 1024, "add_rmsnorm: width %d is beyond 40960", width);
     RMX_REQUIRE(!(rows && write_h), "add_rmsnorm: rows and write_h do not go together");
-    const int threads = block_threads(width);
-    const size_t smem = (size_t)width * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == RMX_F32) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), smem, s, h, (const float*)delta, rows, w,
-                                            eps, (float*)x, width, write_h), "add_rmsnorm");
-    } else if (dtype == RMX_BF16) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, s, h,
-                                            (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)x, width, write_h), "add_rmsnorm");
-    } else {
-        RMX_FAIL("add_rmsnorm: unknown dtype %d", dtype);
-    }
+    int rc;
+    if (dtype == RMX_F32) rc = launch_add_rmsnorm<float>(h, (const float*)delta, rows, w, eps, (float*)x, n_rows, width, write_h, s);
+    else if (dtype == RMX_BF16)
+        rc = launch_add_rmsnorm<__nv_bfloat16>(h, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)x, n_rows, width, write_h, s);
+    else RMX_FAIL("add_rmsnorm: unknown dtype %d", dtype);
+    if (rc != 0) return rc;
     RMX_CHECK_LAUNCH("add_rmsnorm");
     return 0;
 }
@@ -200,30 +266,45 @@ __global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ ou
     store4(out + t * inter + j, make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w)));
 }
 
-// bfloat16, eight outputs per thread (16-byte loads and stores); inter and block are multiples of 8
+// bfloat16, sixteen outputs per thread as two groups of eight (16-byte loads and stores); inter and block are
+// multiples of 8.  blockIdx.x is the token, blockIdx.y the part of its row.  The exponential and the division are
+// the fast ones (about two units in the last place of a float): the result is rounded to bfloat16, eight bits.
+__device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+
 __global__ void swiglu_kernel8(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter,
-                               int block, size_t total8) {
+                               int block) {
     wait_for_prior_kernels();
     allow_dependents();
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total8) return;
     const int per_row = inter >> 3;
-    const size_t t = idx / per_row;
-    const int j = (int)(idx - t * per_row) * 8;
-    int gi, ui;
-    gate_up_at(j, inter, block, gi, ui);
-    const uint4 g = *reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + gi);
-    const uint4 u = *reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + ui);
-    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
-    uint32_t ow[4];
+    const __nv_bfloat16* src = gate_up + (size_t)blockIdx.x * 2 * inter;
+    __nv_bfloat16* dst = out + (size_t)blockIdx.x * inter;
+    uint4 g[2], u[2];
+    int j[2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[i]));
-        __nv_bfloat162 r = __floats2bfloat162_rn(silu_mul(a.x, b.x), silu_mul(a.y, b.y));
-        ow[i] = *reinterpret_cast<uint32_t*>(&r);
+    for (int c = 0; c < 2; ++c) {
+        const int item = (blockIdx.y * 2 + c) * blockDim.x + threadIdx.x;
+        j[c] = item < per_row ? item * 8 : -1;
+        if (j[c] >= 0) {
+            int gi, ui;
+            gate_up_at(j[c], inter, block, gi, ui);
+            g[c] = *reinterpret_cast<const uint4*>(src + gi);
+            u[c] = *reinterpret_cast<const uint4*>(src + ui);
+        }
     }
-    *reinterpret_cast<uint4*>(out + t * inter + j) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        if (j[c] < 0) continue;
+        const uint32_t gw[4] = {g[c].x, g[c].y, g[c].z, g[c].w}, uw[4] = {u[c].x, u[c].y, u[c].z, u[c].w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+            const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[i]));
+            __nv_bfloat162 r = __floats2bfloat162_rn(silu_mul_fast(a.x, b.x), silu_mul_fast(a.y, b.y));
+            ow[i] = *reinterpret_cast<uint32_t*>(&r);
+        }
+        *reinterpret_cast<uint4*>(dst + j[c]) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
 }
 
 RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int block, int dtype, void* stream) {
@@ -234,9 +315,10 @@ RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, 
     const int threads = 256;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_BF16 && (inter & 7) == 0 && (block & 7) == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
-        const size_t total8 = (size_t)n_tokens * inter / 8;
-        RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel8, dim3((unsigned)((total8 + threads - 1) / threads)), dim3(threads), 0, s,
-                                            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total8), "swiglu");
+        const int per_row = inter / 8;
+        const int t8 = per_row >= 512 ? 256 : 128;
+        RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel8, dim3(n_tokens, (per_row + 2 * t8 - 1) / (2 * t8)), dim3(t8), 0, s,
+                                            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block), "swiglu");
         return 0;
     }
     const size_t total = (size_t)n_tokens * inter / (vec ? 4 : 1);

@@ -197,6 +197,113 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_128_kernel(
         *reinterpret_cast<uint2*>(dst[u] + lane * 4) = packed;
     }
 }
+// The same for many tokens (prompt portions): a warp takes one token and HEADS_PER_WARP neighbouring heads of it,
+// two heads a pass (sixteen lanes a head, eight neighbouring numbers a lane, 16-byte loads and stores; the partner
+// of number j is j + 64, eight lanes away).  The token's position, page and its cosines and sines are read once a
+// warp, and all loads of the warp's heads are under way before the first is worked on.
+constexpr int HEADS_PER_WARP = 8;
+
+__global__ void __launch_bounds__(WARPS * 32, 8) qk_rope_cache_128_wide_kernel(
+    const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+    const float* __restrict__ cos_sin, const int* __restrict__ positions, const int* __restrict__ seq_index,
+    const int* __restrict__ block_table, int table_stride, int page_size, __nv_bfloat16* __restrict__ k_pool,
+    __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ q_out, int n_tokens, int nq, int nkv, int row_stride,
+    int write_kv, int* __restrict__ status) {
+    constexpr int hd = 128, PASSES = HEADS_PER_WARP / 2;
+    wait_for_prior_kernels();
+    allow_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = nq + (write_kv ? 2 * nkv : 0);
+    const int groups = (heads_total + HEADS_PER_WARP - 1) / HEADS_PER_WARP;
+    const long long item = (long long)blockIdx.x * WARPS + warp;
+    if (item >= (long long)n_tokens * groups) return;
+    const int t = (int)(item / groups), head0 = (int)(item - (long long)t * groups) * HEADS_PER_WARP;
+    const int sub = lane >> 4, l16 = lane & 15;       // which of the pass's two heads, and where in it
+    const __nv_bfloat16* src = qkv + (size_t)t * row_stride + l16 * 8;
+    uint4 raw[PASSES];
+#pragma unroll
+    for (int u = 0; u < PASSES; ++u) {
+        const int head = head0 + 2 * u + sub;
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (head < heads_total) raw[u] = *reinterpret_cast<const uint4*>(src + (size_t)head * hd);
+    }
+    // cosines and sines of the pairs (j, j + 64) that this lane's eight numbers belong to
+    const int j = (l16 & 7) * 8;
+    float cs[8], sn[8];
+    {
+        const float4 c0 = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * hd + j);
+        const float4 c1 = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * hd + j + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * hd + 64 + j);
+        const float4 s1 = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * hd + 64 + j + 4);
+        cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    long long slot_row = -1;   // the row of the pools' [pages * nkv * page_size] rows that kv head 0 of this token has
+    if (head0 + HEADS_PER_WARP > nq && write_kv) {
+        const int pos = positions[t];
+        const int page = block_table[(size_t)seq_index[t] * table_stride + pos / page_size];
+        if (page < 0) {  // the host reserves pages before the step; never write through a hole
+            if (lane == 0) atomicExch(status, 1);
+        } else {
+            slot_row = (long long)page * nkv * page_size + pos % page_size;
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < PASSES; ++u) {
+        const int head = head0 + 2 * u + sub;
+        const bool live = head < heads_total;
+        const bool is_q = head < nq, is_v = head >= nq + nkv;
+        __nv_bfloat16* dst = nullptr;
+        if (live) {
+            if (is_q) dst = q_out + ((size_t)t * nq + head) * hd + l16 * 8;
+            else if (slot_row >= 0)
+                dst = (is_v ? v_pool : k_pool) + (size_t)(slot_row + (long long)((head - nq) % nkv) * page_size) * hd + l16 * 8;
+        }
+        const uint32_t rw[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+        // every lane takes part in the shuffles, whatever its head is
+        const bool normed = live && !is_v && (is_q ? q_norm != nullptr : k_norm != nullptr);
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (normed) {
+            const float inv = rsqrtf(ss / (float)hd + eps);
+            const float* w = (is_q ? q_norm : k_norm) + l16 * 8;   // (the same 512 bytes for every warp: they stay in L1)
+            const float4 a = *reinterpret_cast<const float4*>(w), b = *reinterpret_cast<const float4*>(w + 4);
+            v[0] = v[0] * inv * a.x; v[1] = v[1] * inv * a.y; v[2] = v[2] * inv * a.z; v[3] = v[3] * inv * a.w;
+            v[4] = v[4] * inv * b.x; v[5] = v[5] * inv * b.y; v[6] = v[6] * inv * b.z; v[7] = v[7] * inv * b.w;
+        }
+        float out[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 8);
+            // lanes 0..7 of a head hold x[j] (partner x[j + 64] eight lanes on): out = a cos - b sin
+            // lanes 8..15 hold x[j + 64] (partner x[j]):                          out = b cos + a sin
+            out[i] = is_v ? v[i] : (l16 < 8 ? v[i] * cs[i] - other * sn[i] : v[i] * cs[i] + other * sn[i]);
+        }
+        if (dst) {
+            if (is_v) {
+                *reinterpret_cast<uint4*>(dst) = raw[u];   // values pass through
+            } else {
+                uint32_t ow[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    __nv_bfloat162 r = __floats2bfloat162_rn(out[2 * i], out[2 * i + 1]);
+                    ow[i] = *reinterpret_cast<uint32_t*>(&r);
+                }
+                *reinterpret_cast<uint4*>(dst) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
+        }
+    }
+}
 }  // namespace
 
 RMX_API int rmx_rope_table(const int* positions, const float* inv_freq, float* cos_sin, int n_tokens, int rotary_dim,
@@ -228,6 +335,14 @@ RMX_API int rmx_qk_rope_cache(const void* qkv, const float* q_norm, const float*
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_BF16 && hd == 128 && rotary_dim == 128 && cos_sin != nullptr && row_stride % 4 == 0 &&
         ((uintptr_t)qkv & 7) == 0 && items < (1LL << 30)) {
+        if (n_tokens >= 256 && row_stride % 8 == 0 && ((uintptr_t)qkv & 15) == 0) {   // prompt portions
+            const long long warps = (long long)n_tokens * ((heads_total + HEADS_PER_WARP - 1) / HEADS_PER_WARP);
+            RMX_CHECK_LAUNCHED(launch_dependent(qk_rope_cache_128_wide_kernel, dim3((unsigned)((warps + WARPS - 1) / WARPS)), dim3(WARPS * 32), 0, s,
+                (const __nv_bfloat16*)qkv, q_norm, k_norm, eps, cos_sin, positions, seq_index, block_table, table_stride, page_size,
+                (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, n_tokens, nq, nkv, row_stride, write_kv, status),
+                "qk_rope_cache_128_wide");
+            return 0;
+        }
         const unsigned blocks128 = (unsigned)((items + (long long)WARPS * PER_WARP - 1) / (WARPS * PER_WARP));
         RMX_CHECK_LAUNCHED(launch_dependent(qk_rope_cache_128_kernel, dim3(blocks128), dim3(WARPS * 32), 0, s,
             (const __nv_bfloat16*)qkv, q_norm, k_norm, eps, cos_sin, positions, seq_index, block_table, table_stride, page_size,

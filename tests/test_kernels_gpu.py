@@ -691,3 +691,47 @@ def test_gemm_qkv_heads_finishes_the_projection_like_the_separate_kernels(m, nq,
     assert (q1 == q2).double().mean().item() > 0.98
     if not write_kv:
         assert torch.equal(k2, pools()[0]) and torch.equal(v2, pools()[1])
+
+
+@pytest.mark.parametrize("nq, nkv, page, norm, write_kv", [(32, 8, 64, True, True), (5, 3, 16, True, True), (4, 4, 8, False, True),
+                                                           (6, 2, 32, True, False)])
+def test_qk_rope_cache_for_prompt_portions_agrees_with_the_general_kernel(nq, nkv, page, norm, write_kv):
+    """Heads of 128 in bfloat16 and a few hundred tokens take a kernel of their own (a warp per token and eight
+    heads); the general kernel (a warp per token and head, its own sines) is the reference: a last bit apart."""
+    hd, rot = 128, 128
+    torch.manual_seed(nq + page)
+    lengths, new = [400, 37, 290], [310, 1, 150]
+    n_tok = sum(new)
+    n_pages = sum(-(-n // page) for n in lengths) + 2
+    table = torch.full((3, max(-(-n // page) for n in lengths)), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages).tolist()
+    for s, n in enumerate(lengths):
+        for i in range(-(-n // page)):
+            table[s, i] = perm.pop()
+    pos, sidx = [], []
+    for s, (n, c) in enumerate(zip(lengths, new)):
+        pos += list(range(n - c, n))
+        sidx += [s] * c
+    positions = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    seq_index = torch.tensor(sidx, dtype=torch.int32, device=DEV)
+    qkv = rnd((n_tok, (nq + 2 * nkv) * hd), torch.bfloat16, 1.0, 3)
+    qn = (1 + 0.2 * torch.randn(hd)).to(DEV) if norm else None
+    kn = (1 + 0.2 * torch.randn(hd)).to(DEV) if norm else None
+    inv_freq = (1e6 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float().to(DEV)
+    angles = torch.empty(n_tok, rot, device=DEV)
+    ops().rope_table(positions, inv_freq, rot, angles)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    results = []
+    for table_given in (None, angles):
+        k_pool = torch.full((n_pages, nkv, page, hd), 5.0, dtype=torch.bfloat16, device=DEV)
+        v_pool = torch.full_like(k_pool, -2.0)
+        q_out = torch.full((n_tok, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops().qk_rope_cache(qkv, qn, kn, 1e-6, inv_freq, rot, positions, seq_index, table.to(DEV), page, k_pool, v_pool, q_out,
+                            nq, nkv, hd, write_kv, status, cos_sin=table_given)
+        results.append((q_out, k_pool, v_pool))
+    assert status.item() == 0
+    for a, b in zip(*results):
+        a, b = a.double(), b.double()
+        assert bool(((a - b).abs() <= 2 ** -7 * torch.maximum(a.abs(), b.abs()) + 1e-6).all())
+    assert torch.equal(results[0][2], results[1][2])
+    assert (results[0][0] == results[1][0]).double().mean().item() > 0.98
