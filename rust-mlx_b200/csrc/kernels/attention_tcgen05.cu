@@ -7,8 +7,12 @@
 // A block takes two neighbouring tiles, which share every key and value tile it fetches.
 //
 //   warp 0   producer: Q once and then K/V tiles by TMA (tensor-map boxes, 128-byte swizzle) into a ring
-//   warp 1   issues the MMAs: S = Q K^T into tensor memory (two buffers per query tile: the next key tile's
-//            scores are formed while the softmax warps work on this one's), later O += P V
+//   warps 1 and 10  issue the MMAs (warp 10 the scores, warp 1 O += P V, so that neither waits for what the
+//            other waits for): S = Q K^T into tensor memory, for two neighbouring key tiles at once (an MMA of 128
+//            rows by 64 columns takes as long as one of 128 columns, so the scores of a pair of key tiles cost
+//            what one tile's would; the pair's key tiles lie in neighbouring slots of the ring, which makes them
+//            one operand of 128 rows); the next pair's scores are formed as soon as the softmax warps have read
+//            this pair's into registers; later O += P V, tile by tile
 //   warps 2-5 and 6-9  softmax of the first and the second query tile: every thread owns one row (one lane
 //            of tensor memory): it reads its 64 scores, masks where the tile touches the diagonal or the
 //            window's edge, keeps the running maximum and sum in float, writes its probabilities as bfloat16
@@ -27,14 +31,14 @@
 
 namespace {
 constexpr int HD = 128, BM = 128, BN = 64;
-constexpr int STAGES = 3;
-constexpr int THREADS = 320;   // producer, MMA issuer, 4 softmax warps for each of the block's two query tiles
+constexpr int STAGES = 4;                   // slots of the key/value ring, one key tile (and its value tile) each; pairs 0|1 and 2|3
+constexpr int THREADS = 352;   // producer, O += P V issuer, 4 softmax warps for each of the block's two query tiles, score issuer
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int Q_BYTES = BM * HD * 2;        // 32 KB: two boxes of [128 rows][64 columns]
 constexpr int KV_BYTES = BN * HD * 2;       // 16 KB per key tile, the same per value tile
 constexpr int P_BYTES = BM * BN * 2;        // 16 KB
-constexpr int TILE_COLS = 256;              // per query tile: S (two buffers) in columns 0..63 and 64..127, O in 128..255
+constexpr int TILE_COLS = 256;              // per query tile: S of a pair of key tiles in columns 0..63 and 64..127, O in 128..255
 constexpr int TMEM_COLS = 512;              // two query tiles: all of an SM's tensor memory
 constexpr int O_COL = 128;
 
@@ -153,9 +157,14 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_smem = base;                               // [2 tiles][2 boxes][128 rows][128 B]
-    unsigned char* kv_smem = q_smem + 2 * Q_BYTES;              // [STAGES][K tile | V tile], each [2 boxes][64 rows][128 B]
+    // keys: [2 halves of d][STAGES slots][64 rows][128 B], so that the same half of two neighbouring slots is one
+    // run of 128 rows; values: [STAGES slots][2 halves of d][64 rows][128 B]
+    unsigned char* kv_smem = q_smem + 2 * Q_BYTES;
+    unsigned char* k_smem = kv_smem;
+    unsigned char* v_smem = kv_smem + STAGES * KV_BYTES;
     unsigned char* p_smem = kv_smem + STAGES * 2 * KV_BYTES;    // [2 tiles][128 rows][128 B]
-    __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2][2], p_full[2], o_done[2];
+    // keys come and go by pairs of slots (a pair's scores are one group of MMAs), values slot by slot
+    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[STAGES], v_empty[STAGES], s_full[2], s_read[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int s_failed, s_tile[3], s_warp_total[THREADS / 32];
 
@@ -165,12 +174,14 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
         s_failed = 0;
         mbar_init(&q_full, 1);
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&kv_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
         }
         for (int t = 0; t < 2; ++t) {
-            mbar_init(&s_full[t][0], 1);
-            mbar_init(&s_full[t][1], 1);
+            mbar_init(&k_full[t], 1);
+            mbar_init(&k_empty[t], 1);
+            mbar_init(&s_full[t], 1);
+            mbar_init(&s_read[t], 4);      // one arrival per softmax warp of the tile
             mbar_init(&p_full[t], 128);
             mbar_init(&o_done[t], 1);
         }
@@ -251,84 +262,110 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
             tma_3d(q_smem + t * Q_BYTES + Q_BYTES / 2, &map_q, &q_full, 64, kvh * p.group, tok0 + t * p.tq);
         }
         const int boxes = BN / p.box_rows;
-        for (int i = 0; i < n_kt; ++i) {
-            const int st = i % STAGES, round = i / STAGES, kt = kt_lo + i;
-            if (round > 0 && !mbar_wait(&kv_empty[st], (round - 1) & 1)) { atomicExch(&s_failed, 1); break; }
+        // the boxes of key tile i (keys when `keys`, else values) into slot i % STAGES; returns their bytes
+        auto fetch = [&](int i, bool keys, uint64_t* bar, bool count_only) {
+            const int st = i % STAGES, kt = kt_lo + i;
             uint32_t bytes = 0;
             for (int b = 0; b < boxes; ++b) {
                 const int kp = kt * BN + b * p.box_rows;
                 if (kp > pos_last || kp + p.box_rows <= lo_first) continue;
-                if (table[kp >> p.page_shift] >= 0) bytes += 2u * p.box_rows * HD * 2u;
-                else atomicExch(p.status, 2);
-            }
-            mbar_expect_tx(&kv_full[st], bytes);
-            unsigned char* kd = kv_smem + st * 2 * KV_BYTES;
-            unsigned char* vd = kd + KV_BYTES;
-            for (int b = 0; b < boxes; ++b) {
-                const int kp = kt * BN + b * p.box_rows;
-                if (kp > pos_last || kp + p.box_rows <= lo_first) continue;
                 const int page = table[kp >> p.page_shift];
-                if (page < 0) continue;
+                if (page < 0) {
+                    if (count_only) atomicExch(p.status, 2);
+                    continue;
+                }
+                bytes += p.box_rows * HD * 2u;
+                if (count_only) continue;
                 const int row = (page * p.nkv + kvh) * p.page_size + (kp & (p.page_size - 1));
 #pragma unroll
                 for (int cb = 0; cb < 2; ++cb) {
-                    tma_2d(kd + cb * (KV_BYTES / 2) + b * p.box_rows * 128, &map_k, &kv_full[st], cb * 64, row);
-                    tma_2d(vd + cb * (KV_BYTES / 2) + b * p.box_rows * 128, &map_v, &kv_full[st], cb * 64, row);
+                    if (keys) tma_2d(k_smem + st * (KV_BYTES / 2) + cb * (STAGES * KV_BYTES / 2) + b * p.box_rows * 128, &map_k, bar, cb * 64, row);
+                    else tma_2d(v_smem + st * KV_BYTES + cb * (KV_BYTES / 2) + b * p.box_rows * 128, &map_v, bar, cb * 64, row);
                 }
             }
-        }
-    } else if (warp == 1 && lane == 0 && seq >= 0) {
-        // ---- MMA issuer
-        const uint32_t id_s = idesc(BN, false), id_o = idesc(HD, true);
-        const int n_t = two ? 2 : 1;
-        // S = Q K^T of key tile i for query tile t into its score buffer i & 1: the reduction runs over d, 8 steps of
-        // 16; d 0..63 lie in the first box of a tile, 64..127 in the second
-        auto scores = [&](int t, int i) {
-            const uint32_t q_addr = smem_u32(q_smem + t * Q_BYTES);
-            const uint32_t k_addr = smem_u32(kv_smem + (i % STAGES) * 2 * KV_BYTES);
-#pragma unroll
-            for (int kk = 0; kk < HD / 16; ++kk) {
-                const uint32_t qa = q_addr + (kk >> 2) * (Q_BYTES / 2) + (kk & 3) * 32;
-                const uint32_t ka = k_addr + (kk >> 2) * (KV_BYTES / 2) + (kk & 3) * 32;
-                umma(tmem + t * TILE_COLS + (i & 1) * BN, desc_kmajor(qa), desc_kmajor(ka), id_s, kk > 0);
-            }
-            umma_commit(&s_full[t][i & 1]);
+            return bytes;
         };
-        bool ok = mbar_wait(&q_full, 0);
-        if (ok && n_kt > 0) {
-            ok = mbar_wait(&kv_full[0], 0);
-            if (ok) {
-                fence_after();
-                for (int t = 0; t < n_t; ++t) scores(t, 0);
-            }
-        }
+        bool ok = true;
         for (int i = 0; i < n_kt && ok; ++i) {
-            const int st = i % STAGES;
-            const bool more = i + 1 < n_kt;
-            if (more) {
-                if (!mbar_wait(&kv_full[(i + 1) % STAGES], ((i + 1) / STAGES) & 1)) { ok = false; break; }
-                fence_after();
+            if ((i & 1) == 0) {   // the keys of the pair of tiles i, i + 1: their slots are free once the scores of the pair before last are formed
+                const int j = i >> 1, last = min(i + 2, n_kt);
+                if (j >= 2 && !mbar_wait(&k_empty[j & 1], ((j >> 1) - 1) & 1)) { ok = false; break; }
+                uint32_t bytes = 0;
+                for (int ii = i; ii < last; ++ii) bytes += fetch(ii, true, nullptr, true);
+                mbar_expect_tx(&k_full[j & 1], bytes);
+                for (int ii = i; ii < last; ++ii) fetch(ii, true, &k_full[j & 1], false);
             }
-            const uint32_t v_addr = smem_u32(kv_smem + st * 2 * KV_BYTES) + KV_BYTES;
-            for (int t = 0; t < n_t && ok; ++t) {
-                // the next key tile's scores for this query tile are formed while its softmax warps work on this one's
-                // (that buffer is free: the probabilities of tile i - 1 were made from it before the last O += P V)
-                if (more) scores(t, i + 1);
-                if (!mbar_wait(&p_full[t], i & 1)) { ok = false; break; }
-                fence_after();
-                // O += P V: the reduction runs over the tile's 64 keys, 4 steps of 16; V is [key][d], MN-major:
-                // blocks of 64 d are 8 KB apart, groups of 8 keys 1 KB
-                const uint32_t p_addr = smem_u32(p_smem + t * P_BYTES);
-#pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk)
-                    umma(tmem + t * TILE_COLS + O_COL, desc_kmajor(p_addr + kk * 32),
-                         desc_mnmajor(v_addr + kk * 2048, KV_BYTES / 2, 1024), id_o, i > 0 || kk > 0);
-                umma_commit(&o_done[t]);
-            }
-            umma_commit(&kv_empty[st]);   // both query tiles are done with this stage once these MMAs have finished
+            const int st = i % STAGES, round = i / STAGES;
+            if (round > 0 && !mbar_wait(&v_empty[st], (round - 1) & 1)) { ok = false; break; }
+            mbar_expect_tx(&v_full[st], fetch(i, false, nullptr, true));
+            fetch(i, false, &v_full[st], false);
         }
         if (!ok) atomicExch(&s_failed, 1);
-    } else if (warp >= 2 && seq >= 0 && (warp < 6 || two)) {
+    } else if (warp == 10 && lane == 0 && seq >= 0) {
+        // ---- issuer of the score MMAs.  One thread issues them all, so what it executes per MMA counts: the operand
+        // descriptors are formed before the loop (those of Q do not change; those of K differ by the pair's address,
+        // which is added to the descriptor's low bits), and the loops are unrolled.
+        const uint32_t id_s = idesc(2 * BN, false);
+        const int n_t = two ? 2 : 1;
+        uint64_t q_desc[2][HD / 16];
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk)
+                q_desc[t][kk] = desc_kmajor(smem_u32(q_smem + t * Q_BYTES) + (kk >> 2) * (Q_BYTES / 2) + (kk & 3) * 32);
+        const uint64_t k_desc0 = desc_kmajor(smem_u32(k_smem));
+        const int n_pairs = (n_kt + 1) / 2;
+        bool ok = mbar_wait(&q_full, 0);
+        for (int j = 0; j < n_pairs && ok; ++j) {
+            // S = Q K^T of the key tiles 2 j and 2 j + 1 (slots 2 (j & 1) and the next: 128 rows of keys) for each query
+            // tile into its 128 score columns: the reduction runs over d, 8 steps of 16; d 0..63 lie in the first half
+            // of the key region, 64..127 in the second.  (If the pair's second tile does not exist, its columns are
+            // never read.)  The columns are free once the softmax warps have read the pair before into registers.
+            if (!mbar_wait(&k_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
+            fence_after();
+            const uint64_t k_desc = k_desc0 + (uint64_t)(((j & 1) * 2 * (KV_BYTES / 2)) >> 4);
+            for (int t = 0; t < n_t && ok; ++t) {
+                if (j > 0 && !mbar_wait(&s_read[t], (j - 1) & 1)) { ok = false; break; }
+                fence_after();
+                const uint32_t d_addr = tmem + t * TILE_COLS;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    umma(d_addr, t == 0 ? q_desc[0][kk] : q_desc[1][kk],
+                         k_desc + (uint64_t)(((kk >> 2) * (STAGES * KV_BYTES / 2) + (kk & 3) * 32) >> 4), id_s, kk > 0);
+                umma_commit(&s_full[t]);
+            }
+            umma_commit(&k_empty[j & 1]);   // the pair's key slots are free once these MMAs have finished
+        }
+        if (!ok) atomicExch(&s_failed, 1);
+    } else if (warp == 1 && lane == 0 && seq >= 0) {
+        // ---- issuer of O += P V: the reduction runs over a tile's 64 keys, 4 steps of 16; V is [key][d], MN-major:
+        // blocks of 64 d are 8 KB apart, groups of 8 keys 1 KB
+        const uint32_t id_o = idesc(HD, true);
+        const int n_t = two ? 2 : 1;
+        uint64_t p_desc[2][BN / 16];
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk) p_desc[t][kk] = desc_kmajor(smem_u32(p_smem + t * P_BYTES) + kk * 32);
+        const uint64_t v_desc0 = desc_mnmajor(smem_u32(v_smem), KV_BYTES / 2, 1024);
+        bool ok = true;
+        for (int i = 0; i < n_kt && ok; ++i) {
+            const int st = i % STAGES;
+            if (!mbar_wait(&v_full[st], (i / STAGES) & 1)) { ok = false; break; }
+            const uint64_t v_desc = v_desc0 + (uint64_t)((st * KV_BYTES) >> 4);
+            for (int t = 0; t < n_t && ok; ++t) {
+                if (!mbar_wait(&p_full[t], i & 1)) { ok = false; break; }
+                fence_after();
+                const uint32_t d_addr = tmem + t * TILE_COLS + O_COL;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk)
+                    umma(d_addr, t == 0 ? p_desc[0][kk] : p_desc[1][kk], v_desc + (uint64_t)((kk * 2048) >> 4), id_o, i > 0 || kk > 0);
+                umma_commit(&o_done[t]);
+            }
+            umma_commit(&v_empty[st]);   // both query tiles are done with this slot's values once these MMAs have finished
+        }
+        if (!ok) atomicExch(&s_failed, 1);
+    } else if (warp >= 2 && warp < 10 && seq >= 0 && (warp < 6 || two)) {
         // ---- softmax of query tile t: thread owns row r of the tile = lane r of tensor memory
         const int t = warp < 6 ? 0 : 1;
         const int quad = warp & 3;
@@ -346,9 +383,11 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
         bool ok = true;
         for (int i = 0; i < n_kt; ++i) {
             const int kt = kt_lo + i;
-            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t][i & 1], (i >> 1) & 1));
-            if (!ok) break;
-            fence_after();
+            if ((i & 1) == 0) {   // the scores of the pair of key tiles i, i + 1
+                ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], (i >> 1) & 1));
+                if (!ok) break;
+                fence_after();
+            }
             float s[BN];
 #pragma unroll
             for (int c = 0; c < BN; c += 32) {
@@ -357,6 +396,11 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; ++j) s[c + j] = __uint_as_float(v[j]);
+            }
+            if ((i & 1) || i + 1 == n_kt) {   // the pair's scores are in registers: the next pair's may overwrite them
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_read[t]);
             }
             // a tile that every row of this warp sees whole (below the diagonal, inside the window) needs no mask:
             // the maximum is taken over the raw scores and the scale goes into the exponent's multiply-add
@@ -419,7 +463,10 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
             // not reach the sum, not even multiplied by zero.  Only the tile that holds the end has such keys; the
             // first query tile's warps clear them (both tiles' MMAs wait for these warps' arrival or come after it).
             if (t == 0 && kt * BN + BN - 1 > pos_last) {
-                unsigned char* vd = kv_smem + (i % STAGES) * 2 * KV_BYTES + KV_BYTES;
+                // (the values must have arrived, or they would land on top of the zeros)
+                ok = __all_sync(0xffffffffu, mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1));
+                if (!ok) break;
+                unsigned char* vd = v_smem + (i % STAGES) * KV_BYTES;
                 const int first_bad = pos_last + 1 - kt * BN;
                 for (int idx = quad * 32 + lane; idx < (BN - first_bad) * 16; idx += 128) {
                     const int row = first_bad + idx / 16, c = idx % 16;   // 16 chunks of 16 bytes per row: two boxes of 8
