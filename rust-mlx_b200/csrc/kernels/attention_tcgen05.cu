@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
     __shared__ int s_failed, s_tile[3], s_warp_total[THREADS / 32];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = blockIdx.y;
+    const int kvh = blockIdx.x;   // the kv head runs fastest, so that blocks start in the order of their tiles
     if (tid == 0) {
         s_failed = 0;
         mbar_init(&q_full, 1);
@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
                 if (w < warp) before += s_warp_total[w];
                 total += s_warp_total[w];
             }
-            const int mine = (int)(gridDim.x - 1 - blockIdx.x) - (before + incl - pairs);
+            const int mine = (int)(gridDim.y - 1 - blockIdx.y) - (before + incl - pairs);
             if (pairs > 0 && mine >= 0 && mine < pairs) {
                 s_tile[0] = sq;
                 s_tile[1] = a + mine * pair_tokens;
@@ -609,7 +609,7 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
     const int group = nq / nkv;
     RMX_REQUIRE(rmx_attention_tcgen05_supports(hd, group, page_size),
                 "attention_tcgen05: head_dim %d, group %d, page size %d is not built", hd, group, page_size);
-    RMX_REQUIRE(table_stride > 0 && window >= 0 && n_tiles > 0 && n_seqs > 0 && pool_pages > 0 && nkv <= 65535,
+    RMX_REQUIRE(table_stride > 0 && window >= 0 && n_tiles > 0 && n_tiles <= 65535 && n_seqs > 0 && pool_pages > 0,
                 "attention_tcgen05: bad geometry");
     RMX_REQUIRE(scale > 0.f, "attention_tcgen05: the scale must be positive (the maximum is taken before scaling)");
     RMX_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pool & 127) == 0 && ((uintptr_t)v_pool & 127) == 0,
@@ -634,7 +634,8 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
         if (e != cudaSuccess) RMX_FAIL("attention_tcgen05: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
-    attention_tcgen05_kernel<<<dim3(n_tiles, nkv), THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    // blocks are handed to the SMs in the order x, then y: all kv heads of the tile that sees the most keys first
+    attention_tcgen05_kernel<<<dim3(nkv, n_tiles), THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
     RMX_CHECK_LAUNCH("attention_tcgen05");
     return 0;
 }
