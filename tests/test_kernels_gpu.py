@@ -491,7 +491,7 @@ def test_attention_flash_rows_do_not_depend_on_the_batch():
     assert torch.equal(out2, out[33:40])
 
 
-@pytest.mark.parametrize("splits", [None, 1, 4])
+@pytest.mark.parametrize("splits", [None, 1, 4, 7, 12])   # 2..8: merged inside a cluster; more: through global memory
 @pytest.mark.parametrize("nq, nkv, hd, page, window, new_len", [
     (4, 2, 16, 16, 0, 1), (6, 2, 32, 8, 20, 1), (32, 8, 128, 64, 0, 1), (16, 1, 128, 16, 0, 1), (8, 2, 64, 4, 50, 4),
     (5, 5, 96, 2, 0, 16), (64, 8, 128, 64, 0, 2), (6, 3, 64, 8, 70, 3), (12, 4, 128, 32, 33, 1), (4, 4, 64, 128, 0, 2),
