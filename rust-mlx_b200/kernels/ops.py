@@ -40,7 +40,8 @@ def _ptr(t, dtype=None, name="tensor"):
 
 
 def _stream():
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current stream of the current device as the kernels' void* (the raw handle: this runs once per launch)."""
+    return c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 def _launched(n=1):
@@ -431,8 +432,16 @@ def _own_workspace():
     return _scratch
 
 
+_supported = {}
+
+
 def tcgen05_supported(m: int, n: int, k: int) -> bool:
-    return bool(kernels_library().rmx_gemm_tcgen05_supports(c_int(m), c_int(n), c_int(k)))
+    key = (m, n, k)
+    if key not in _supported:
+        if len(_supported) > 65536:
+            _supported.clear()
+        _supported[key] = bool(kernels_library().rmx_gemm_tcgen05_supports(c_int(m), c_int(n), c_int(k)))
+    return _supported[key]
 
 
 def tcgen05_splits(m: int, n: int, k: int) -> int:
