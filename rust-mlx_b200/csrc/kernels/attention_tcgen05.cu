@@ -4,7 +4,8 @@
 // head of the group) pair, 128 / group tokens by `group` heads, so the heads that share a kv head share
 // every key and value tile.  Keys are visited in tiles of 64 aligned to absolute positions.
 //
-// A block takes two neighbouring tiles, which share every key and value tile it fetches.
+// A block takes two neighbouring tiles, which share every key and value tile it fetches (or one, for steps so
+// small that SMs would be left without work).
 //
 //   warp 0   producer: Q once and then K/V tiles by TMA (tensor-map boxes, 128-byte swizzle) into a ring
 //   warps 1 and 10  issue the MMAs (warp 10 the scores, warp 1 O += P V, so that neither waits for what the
@@ -18,8 +19,9 @@
 //            window's edge, keeps the running maximum and sum in float, writes its probabilities as bfloat16
 //            into shared memory for the second MMA, and rescales its row of O when the maximum moved
 //
-// S and O live in tensor memory (2 x 64 + 128 columns).  Tiles late in a sequence see more keys: they are
-// handed out first, so that the longest blocks do not run last.  V is used as it lies in the cache, [key][d], through an
+// S and O live in tensor memory (per query tile 128 columns of scores, a pair of key tiles, and 128 of O).  Tiles
+// late in a sequence see more keys: blocks start in the order of their tiles' lengths, all kv heads of the longest
+// tile first, so that the longest blocks do not run last.  V is used as it lies in the cache, [key][d], through an
 // MN-major operand descriptor.  Every wait on a barrier is bounded: a block that gives up records status 3,
 // frees its tensor memory and ends.
 #include <cuda.h>
