@@ -1047,6 +1047,33 @@ int launch_tma_as(const FlashParams& p, int n_tiles, long long pool_rows, cudaSt
     return 0;
 }
 
+// Whether this device can hold a cluster of `size` blocks of the decoding kernel at once (asked once per size).
+template <int HD>
+bool cluster_possible(int size) {
+    static int known[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};   // 0: not asked, 1: yes, -1: no
+    if (size < 2 || size > 8) return false;
+    if (known[size] == 0) {
+        constexpr size_t smem = 1024 + (size_t)DSTAGES * 2 * 64 * HD * 2 + (size_t)16 * (HD + 8) * 2 + (size_t)16 * HD * 4 + 8 * 16 + 8 * 16 * 8;
+        cudaFuncSetAttribute(attention_tma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, size);
+        cfg.blockDim = dim3(DTHREADS);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = size;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, attention_tma_kernel<HD, true>, &cfg);
+        if (e != cudaSuccess) cudaGetLastError();
+        known[size] = e == cudaSuccess && clusters > 0 ? 1 : -1;
+    }
+    return known[size] > 0;
+}
+
 template <int HD>
 int launch_tma(const FlashParams& p, int n_tiles, bool keysplit, long long pool_rows, cudaStream_t s) {
     return keysplit ? launch_tma_as<HD, true>(p, n_tiles, pool_rows, s) : launch_tma_as<HD, false>(p, n_tiles, pool_rows, s);
@@ -1097,7 +1124,8 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
         // The decoding arrangement combines its splits itself: up to 8 as a thread-block cluster, through
         // distributed shared memory; more (up to 128) through the partial buffers, the last block to finish adding
         // them, if the caller gave counters.
-        if (keysplit && n_splits >= 2 && n_splits <= 8) p.cluster = 1;
+        if (keysplit && n_splits >= 2 && n_splits <= 8 && (hd == 64 ? cluster_possible<64>(n_splits) : cluster_possible<128>(n_splits)))
+            p.cluster = 1;
         else if (keysplit && n_splits <= 128) p.counters = counters;
         rc = hd == 64 ? launch_tma<64>(p, n_tiles, keysplit, pool_rows, s) : launch_tma<128>(p, n_tiles, keysplit, pool_rows, s);
         if (rc == 0 && (p.cluster || p.counters)) return 0;
