@@ -22,6 +22,7 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "rope128.cuh"
 
 namespace {
 constexpr int BM = 64, BN = 64, NWARPS = 4, THREADS = NWARPS * 32;
@@ -69,6 +70,17 @@ struct FlashParams {
     int n_seqs, n_tokens, nq, nkv, group, tq, table_stride, page_size, page_shift, window, n_splits;
     float scale_log2;
     int cluster;                   // the splits of a (sequence, kv head) are one thread-block cluster (decoding by TMA)
+    // Decoding by TMA, heads of 128, one token a sequence: the kernel may take the projection's rows as they come
+    // ([q heads | k heads | v heads] of every token) and, while it waits for its first keys, norm and rotate its own
+    // query heads and its token's key and store key and value into their page (see rope128.cuh)
+    const __nv_bfloat16* qkv;      // [tokens, qkv_stride], or null: `q` holds finished queries and the pages are written
+    const float* q_norm;           // [128] or null
+    const float* k_norm;
+    const float* cos_sin;          // [tokens][128]
+    __nv_bfloat16* k_store;        // the pools again, to write; null: the layer reads another layer's cache
+    __nv_bfloat16* v_store;
+    float eps;
+    int qkv_stride;
 };
 
 template <int HD, bool KEYSPLIT>
@@ -436,7 +448,8 @@ __device__ __forceinline__ const __nv_bfloat16* swz(const __nv_bfloat16* tile, i
     return tile + (col >> 6) * (64 * 64) + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3);
 }
 
-template <int HD, bool KEYSPLIT>
+// FINISH: built for p.qkv (decoding that finishes the projection itself); the other builds carry none of that code.
+template <int HD, bool KEYSPLIT, bool FINISH = false>
 __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                 const __grid_constant__ CUtensorMap map_v,
                                                                 const FlashParams p, int box_rows) {
@@ -547,14 +560,44 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
     const int n_mine = kt_begin < kt_end ? kt_end - kt_begin : 0;
 
     // Q rows (zeros beyond the tile's rows), fetched by the computing warps; the producer does not wait for them
+    uint2 k_new = make_uint2(0u, 0u), v_new = make_uint2(0u, 0u);   // the token's own key and value (fused decoding)
+    bool have_new = false;
     if (warp < NWARPS) {
-        for (int idx = tid; idx < QROWS * CHUNKS; idx += NWARPS * 32) {
-            const int r = idx / CHUNKS, c = idx - r * CHUNKS;
-            const bool valid = r < rows_valid;
-            const int tok = valid ? r / p.group : 0, g = valid ? r - tok * p.group : 0;
-            cp_async16(Qs + r * STRIDE + c * 8, p.q + ((size_t)(tok0 + tok) * p.nq + kvh * p.group + g) * HD + c * 8, valid);
+        if constexpr (FINISH) {
+            // one token a sequence: its `group` query heads are the tile's rows; a warp takes a head at a time
+            const __nv_bfloat16* row = p.qkv + (size_t)tok0 * p.qkv_stride;
+            const float* cs = p.cos_sin + (size_t)tok0 * 128;
+            for (int g = warp; g < QROWS; g += NWARPS) {
+                uint2 qv = make_uint2(0u, 0u);
+                if (g < p.group)
+                    qv = rope128_head(*reinterpret_cast<const uint2*>(row + (size_t)(kvh * p.group + g) * 128 + lane * 4), p.q_norm, p.eps, cs, lane);
+                *reinterpret_cast<uint2*>(Qs + g * STRIDE + lane * 4) = qv;
+            }
+            // the block whose keys end with the token's own forms its key and stores key and value: the warp that
+            // will work on the 16 keys around the token's place keeps them, to put them into the tile it gets by
+            // TMA (which may have read the page before these stores landed)
+            if (p.k_store != nullptr && kt_hi >= kt_begin && kt_hi < kt_end && warp == ((pos0 & (BN - 1)) >> 4)) {
+                k_new = rope128_head(*reinterpret_cast<const uint2*>(row + (size_t)(p.nq + kvh) * 128 + lane * 4), p.k_norm, p.eps, cs, lane);
+                v_new = *reinterpret_cast<const uint2*>(row + (size_t)(p.nq + p.nkv + kvh) * 128 + lane * 4);
+                have_new = true;
+                const int page = table[pos0 >> p.page_shift];
+                if (page < 0) {  // the host reserves pages before the step; never write through a hole
+                    if (lane == 0) atomicExch(p.status, 1);
+                } else {
+                    const size_t at = (((size_t)page * p.nkv + kvh) * p.page_size + (pos0 & (p.page_size - 1))) * 128 + lane * 4;
+                    *reinterpret_cast<uint2*>(p.k_store + at) = k_new;
+                    *reinterpret_cast<uint2*>(p.v_store + at) = v_new;
+                }
+            }
+        } else {
+            for (int idx = tid; idx < QROWS * CHUNKS; idx += NWARPS * 32) {
+                const int r = idx / CHUNKS, c = idx - r * CHUNKS;
+                const bool valid = r < rows_valid;
+                const int tok = valid ? r / p.group : 0, g = valid ? r - tok * p.group : 0;
+                cp_async16(Qs + r * STRIDE + c * 8, p.q + ((size_t)(tok0 + tok) * p.nq + kvh * p.group + g) * HD + c * 8, valid);
+            }
+            cp_async_commit();
         }
-        cp_async_commit();
     }
 
     if (warp == NWARPS) {
@@ -623,6 +666,18 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
     for (int i = 0; i < n_mine && warp < NWARPS; ++i) {
         const int kt = kt_begin + i, stage = i % STAGES;
         if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], (i / STAGES) & 1))) { atomicExch(&s_failed, 1); break; }
+        if (FINISH && have_new && kt == kt_hi) {
+            // the token's own key and value into the tile, whatever the TMA found at their place
+            if constexpr (HD == 128) {
+                __nv_bfloat16* kb = KV + stage * 2 * TILE_ELEMS;
+                const int r = pos0 & (BN - 1), col = lane * 4;
+                __nv_bfloat16* kp = const_cast<__nv_bfloat16*>(swz<HD>(kb, r, col & ~7)) + (col & 7);
+                __nv_bfloat16* vp = const_cast<__nv_bfloat16*>(swz<HD>(kb + TILE_ELEMS, r, col & ~7)) + (col & 7);
+                *reinterpret_cast<uint2*>(kp) = k_new;
+                *reinterpret_cast<uint2*>(vp) = v_new;
+            }
+            __syncwarp();
+        }
         if (warp_active) {
             const __nv_bfloat16* kbase = KV + stage * 2 * TILE_ELEMS;
             const __nv_bfloat16* vbase = kbase + TILE_ELEMS;
@@ -1006,7 +1061,7 @@ int pool_map(CUtensorMap* map, const void* base, long long rows, int hd, int box
     return 0;
 }
 
-template <int HD, bool KEYSPLIT>
+template <int HD, bool KEYSPLIT, bool FINISH = false>
 int launch_tma_as(const FlashParams& p, int n_tiles, long long pool_rows, cudaStream_t s) {
     const int box_rows = p.page_size < BN ? p.page_size : BN;
     CUtensorMap mk, mv;
@@ -1018,7 +1073,7 @@ int launch_tma_as(const FlashParams& p, int n_tiles, long long pool_rows, cudaSt
                             (KEYSPLIT ? (size_t)16 * HD * 4 + 8 * 16 + 8 * 16 * 8 : 0);
     static bool raised = false;
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tma_kernel<HD, KEYSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_tma_kernel<HD, KEYSPLIT, FINISH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RMX_FAIL("attention_tma: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
@@ -1039,10 +1094,10 @@ int launch_tma_as(const FlashParams& p, int n_tiles, long long pool_rows, cudaSt
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = rmx_dependent_launch_enabled() ? 2 : 1;
-        RMX_CHECK_LAUNCHED(cudaLaunchKernelEx(&cfg, attention_tma_kernel<HD, KEYSPLIT>, mk, mv, p, box_rows), "attention_tma (cluster)");
+        RMX_CHECK_LAUNCHED(cudaLaunchKernelEx(&cfg, attention_tma_kernel<HD, KEYSPLIT, FINISH>, mk, mv, p, box_rows), "attention_tma (cluster)");
         return 0;
     }
-    RMX_CHECK_LAUNCHED(launch_dependent(attention_tma_kernel<HD, KEYSPLIT>, grid, dim3(DTHREADS), smem, s, mk, mv, p, box_rows),
+    RMX_CHECK_LAUNCHED(launch_dependent(attention_tma_kernel<HD, KEYSPLIT, FINISH>, grid, dim3(DTHREADS), smem, s, mk, mv, p, box_rows),
                        "attention_tma");
     return 0;
 }
@@ -1076,6 +1131,8 @@ bool cluster_possible(int size) {
 
 template <int HD>
 int launch_tma(const FlashParams& p, int n_tiles, bool keysplit, long long pool_rows, cudaStream_t s) {
+    if constexpr (HD == 128)
+        if (keysplit && p.qkv) return launch_tma_as<HD, true, true>(p, n_tiles, pool_rows, s);
     return keysplit ? launch_tma_as<HD, true>(p, n_tiles, pool_rows, s) : launch_tma_as<HD, false>(p, n_tiles, pool_rows, s);
 }
 }  // namespace
@@ -1086,6 +1143,9 @@ RMX_API int rmx_attention_flash_supports(int hd, int group) {
     return hd_ok && group >= 1 && group <= 16 ? 1 : 0;
 }
 
+// qkv (or null): the projection's rows [tokens, qkv_stride] = [q heads | k heads | v heads] before norm and rotation;
+// then q is not read, and the kernel norms (q_norm, k_norm: [128] floats or null, eps) and rotates (cos_sin:
+// [tokens][128], cosines then sines) each sequence's one token itself and, with write_kv, stores its key and value.
 // max_q_len: the most tokens any sequence brings to this step (0: unknown).  pool_pages: pages in k_pool / v_pool
 // (0: unknown; the TMA path for decoding is then not taken).
 // n_tiles: the number of query tiles of the batch, sum over sequences of ceil(tokens / (64 / group)).
@@ -1095,7 +1155,8 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
                                 const int* positions, const int* block_table, int table_stride, int page_size,
                                 void* out, float* part_o, float* part_ml, unsigned int* counters, int n_seqs, int n_tokens, int n_tiles,
                                 int nq, int nkv, int hd, int window, float scale, int n_splits, int max_q_len,
-                                int pool_pages, int* status, void* stream) {
+                                int pool_pages, const void* qkv, int qkv_stride, const float* q_norm, const float* k_norm,
+                                float eps, const float* cos_sin, int write_kv, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_flash: %d query heads over %d kv heads", nq, nkv);
     const int group = nq / nkv;
@@ -1108,6 +1169,9 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     p.q = (const __nv_bfloat16*)q; p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
     p.q_start = q_start; p.positions = positions; p.block_table = block_table; p.out = (__nv_bfloat16*)out;
     p.part_o = part_o; p.part_ml = part_ml; p.status = status; p.counters = nullptr; p.cluster = 0;
+    p.qkv = (const __nv_bfloat16*)qkv; p.qkv_stride = qkv_stride; p.q_norm = q_norm; p.k_norm = k_norm; p.eps = eps; p.cos_sin = cos_sin;
+    p.k_store = qkv && write_kv ? (__nv_bfloat16*)const_cast<void*>(k_pool) : nullptr;
+    p.v_store = qkv && write_kv ? (__nv_bfloat16*)const_cast<void*>(v_pool) : nullptr;
     p.n_seqs = n_seqs; p.n_tokens = n_tokens; p.nq = nq; p.nkv = nkv; p.group = group; p.tq = BM / group;
     p.table_stride = table_stride; p.page_size = page_size; p.window = window; p.n_splits = n_splits;
     p.page_shift = 0;
@@ -1118,8 +1182,16 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     const bool keysplit = max_q_len > 0 && max_q_len * group <= 16;
     int rc;
     // at the head sizes of real models keys and values come by TMA (pool_pages tells the pool's extent)
-    if (pool_pages > 0 && page_size >= 8 && (hd == 64 || hd == 128) && (!keysplit || n_tiles == n_seqs) &&
-        ((uintptr_t)k_pool & 127) == 0 && ((uintptr_t)v_pool & 127) == 0) {
+    const bool by_tma = pool_pages > 0 && page_size >= 8 && (hd == 64 || hd == 128) && (!keysplit || n_tiles == n_seqs) &&
+                        ((uintptr_t)k_pool & 127) == 0 && ((uintptr_t)v_pool & 127) == 0;
+    if (qkv) {
+        RMX_REQUIRE(by_tma && keysplit && hd == 128 && max_q_len == 1 && n_tokens == n_seqs && cos_sin != nullptr,
+                    "attention_flash: the projection's rows are taken as they come only when decoding one token a sequence by TMA with heads of 128");
+        RMX_REQUIRE(qkv_stride >= (nq + 2 * nkv) * 128 && qkv_stride % 4 == 0 && ((uintptr_t)qkv & 7) == 0, "attention_flash: bad projection rows");
+    } else {
+        RMX_REQUIRE(q != nullptr, "attention_flash: no queries");
+    }
+    if (by_tma) {
         const long long pool_rows = (long long)pool_pages * nkv * page_size;
         // The decoding arrangement combines its splits itself: up to 8 as a thread-block cluster, through
         // distributed shared memory; more (up to 128) through the partial buffers, the last block to finish adding
@@ -1147,3 +1219,8 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
 }
 
 RMX_API int rmx_attention_flash_tile_tokens(int group) { return BM / group; }
+
+// Whether a decoding step (one token a sequence) may hand rmx_attention_flash the projection's rows as they come.
+RMX_API int rmx_attention_flash_takes_projection(int hd, int group, int page_size, int rotary_dim) {
+    return hd == 128 && rotary_dim == 128 && group >= 1 && group <= 16 && page_size >= 8 && (page_size & (page_size - 1)) == 0 ? 1 : 0;
+}

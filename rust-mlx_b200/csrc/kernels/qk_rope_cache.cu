@@ -16,6 +16,7 @@
 // rope_table_kernel forms them once per step ([token][cos of j | sin of j], float, with the same
 // float product and the same sincosf), and the kernels here read them when the table is given.
 #include "common.cuh"
+#include "rope128.cuh"
 
 namespace {
 constexpr int WARPS = 4;
@@ -165,35 +166,7 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_128_kernel(
             *reinterpret_cast<uint2*>(dst[u] + lane * 4) = raw[u];
             continue;
         }
-        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u].x));
-        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u].y));
-        float v[4] = {lo.x, lo.y, hi.x, hi.y};
-        if (norm_w[u]) {
-            float ss = v[0] * v[0];
-            ss += v[1] * v[1];
-            ss += v[2] * v[2];
-            ss += v[3] * v[3];
-            ss = warp_sum(ss);
-            const float inv = rsqrtf(ss / (float)hd + eps);
-            const float4 w = *reinterpret_cast<const float4*>(norm_w[u] + lane * 4);
-            v[0] = v[0] * inv * w.x; v[1] = v[1] * inv * w.y; v[2] = v[2] * inv * w.z; v[3] = v[3] * inv * w.w;
-        }
-        const int j = (lane & 15) * 4;   // index of the pair (j, j + 64) this lane's numbers belong to
-        const float4 cs = *reinterpret_cast<const float4*>(cos_sin + (size_t)tok[u] * hd + j);
-        const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)tok[u] * hd + 64 + j);
-        const float c[4] = {cs.x, cs.y, cs.z, cs.w}, s_[4] = {sn.x, sn.y, sn.z, sn.w};
-        float out[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-            // lanes 0..15 hold x[j] (partner x[j + 64] comes from lane + 16): out = a cos - b sin
-            // lanes 16..31 hold x[j + 64] (partner x[j]):                      out = b cos + a sin
-            out[i] = lane < 16 ? v[i] * c[i] - other * s_[i] : v[i] * c[i] + other * s_[i];
-        }
-        __nv_bfloat162 o01 = __floats2bfloat162_rn(out[0], out[1]), o23 = __floats2bfloat162_rn(out[2], out[3]);
-        uint2 packed;
-        packed.x = *reinterpret_cast<uint32_t*>(&o01);
-        packed.y = *reinterpret_cast<uint32_t*>(&o23);
+        const uint2 packed = rope128_head(raw[u], norm_w[u], eps, cos_sin + (size_t)tok[u] * hd, lane);
         *reinterpret_cast<uint2*>(dst[u] + lane * 4) = packed;
     }
 }

@@ -326,10 +326,17 @@ def _short_and_long(batch, group: int):
     return found
 
 
-def attention(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=None):
+def attention(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=None,
+              projection=None):
     """Picks the attention kernel for the dtype, head size and shape of the step.  A step that mixes decoded
-    tokens with prompt portions runs as two launches, each kind with the kernel made for it."""
+    tokens with prompt portions runs as two launches, each kind with the kernel made for it.  ``projection``
+    (see ``decode_takes_projection``): the q/k/v rows before norm and rotation, which the decoding kernel then
+    finishes itself; ``q`` is not read."""
     group = nq // nkv
+    if projection is not None:
+        attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
+                        projection=projection)
+        return
     if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, group):
         runs = _short_and_long(batch, group)
         if runs is not None:
@@ -393,9 +400,21 @@ def flash_splits(n_tiles: int, nkv: int, max_seq_len: int) -> int:
 use_tma = True   # decoding fetches keys and values by TMA where the kernel is built for it
 
 
+fused_decode_rope = True   # a decoding attention norms and rotates its own token while it waits for its first keys
+
+
+def decode_takes_projection(batch, dtype, hd: int, group: int, page_size: int, rotary_dim: int, cos_sin) -> bool:
+    """Whether this step's attention may be handed the q/k/v projection's rows as they come: every sequence brings
+    one token, heads of 128 all rotated, bfloat16, pages the TMA kernel takes."""
+    return (fused_decode_rope and use_tma and dtype == torch.bfloat16 and cos_sin is not None
+            and getattr(batch, "max_q_len", 0) == 1 and batch.n_seqs == batch.positions.shape[0]
+            and bool(kernels_library().rmx_attention_flash_takes_projection(c_int(hd), c_int(group), c_int(page_size), c_int(rotary_dim))))
+
+
 def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
-                    n_splits=None):
-    """Tensor-core attention over pages for bfloat16 (prompt portions and decoded tokens alike)."""
+                    n_splits=None, projection=None):
+    """Tensor-core attention over pages for bfloat16 (prompt portions and decoded tokens alike).  ``projection``:
+    (qkv rows, q_norm, k_norm, eps, cos_sin, write_kv) for a decoding step whose kernel finishes the projection."""
     lib = kernels_library()
     group = nq // nkv
     tq = 64 // group
@@ -403,20 +422,24 @@ def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
     n_tiles = sum(-(-(starts[i + 1] - starts[i]) // tq) for i in range(batch.n_seqs))
     if n_splits is None:
         n_splits = getattr(batch, "forced_splits", None) or flash_splits(n_tiles, nkv, batch.max_seq_len)
-    n = q.shape[0]
+    n = out.shape[0]
+    qkv, q_norm, k_norm, eps, cos_sin, write_kv = projection if projection is not None else (None, None, None, 0.0, None, False)
     part_o = part_ml = counters = None
     if n_splits > 1:
         part_o = workspace.get("attn_part_o", (n_splits, n * nq, hd), torch.float32)
         part_ml = workspace.get("attn_part_ml", (n_splits, n * nq, 2), torch.float32)
         counters = workspace.get_zeroed("attn_counters", (max(4096, batch.n_seqs * nkv),), torch.int32)
     check(lib.rmx_attention_flash(
-        _ptr(q, torch.bfloat16, "q"), _ptr(k_pool, torch.bfloat16, "k_pool"), _ptr(v_pool, torch.bfloat16, "v_pool"),
+        _ptr(q if qkv is None else None, torch.bfloat16, "q"), _ptr(k_pool, torch.bfloat16, "k_pool"), _ptr(v_pool, torch.bfloat16, "v_pool"),
         _ptr(batch.q_start, torch.int32, "q_start"), _ptr(batch.positions, torch.int32, "positions"),
         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
         _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml), _ptr(counters), c_int(batch.n_seqs), c_int(n),
         c_int(n_tiles),
         c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(n_splits),
-        c_int(getattr(batch, "max_q_len", 0)), c_int(k_pool.shape[0] if use_tma else 0), _ptr(batch.status, torch.int32, "status"), _stream()))
+        c_int(getattr(batch, "max_q_len", 0)), c_int(k_pool.shape[0] if use_tma else 0),
+        _ptr(qkv, torch.bfloat16, "qkv"), c_int(qkv.stride(0) if qkv is not None else 0), _ptr(q_norm, torch.float32, "q_norm"),
+        _ptr(k_norm, torch.float32, "k_norm"), c_float(eps), _ptr(cos_sin, torch.float32, "cos_sin"), c_int(1 if write_kv else 0),
+        _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched(2 if n_splits > 1 else 1)
 
 

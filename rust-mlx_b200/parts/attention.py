@@ -65,6 +65,7 @@ class AttentionMixer(Mixer):
         nq, nkv, hd = self.heads, self.kv_heads, self.head_dim
         q = ws.get("q_rot", (n, nq * hd), dt)
         angles = self.position.angles(batch)
+        projection = None
         if ops.qkv_heads_supported(n, hd, self.position.rotary_dim, dt, angles):
             # few rows: the product norms, rotates and stores its heads itself
             ops.gemm_qkv_heads(x, self.w_qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, angles,
@@ -74,13 +75,17 @@ class AttentionMixer(Mixer):
         else:
             qkv = ws.get("qkv", (n, (nq + 2 * nkv) * hd), dt)
             ops.linear(x, self.w_qkv, qkv, ws, batch.status)
-            ops.qk_rope_cache(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.position.inv_freq,
-                              self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
-                              cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, hd, not cache.read_only,
-                              batch.status, angles)
+            if ops.decode_takes_projection(batch, dt, hd, nq // nkv, cache.page_size, self.position.rotary_dim, angles):
+                # decoding: the attention kernel norms, rotates and stores its own token while it waits for its keys
+                projection = (qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, angles, not cache.read_only)
+            else:
+                ops.qk_rope_cache(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.position.inv_freq,
+                                  self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
+                                  cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, hd, not cache.read_only,
+                                  batch.status, angles)
         o = ws.get("attn_out", (n, nq * hd), dt)
         ops.attention(q, cache.k_pool, cache.v_pool, batch, cache.block_table, cache.page_size, o, nq, nkv, hd,
-                      cache.window, self.scale, ws)
+                      cache.window, self.scale, ws, projection=projection)
         y = ws.get("mixer_out", (n, self.width), dt)
         ops.linear(o, self.w_o, y, ws, batch.status)
         return y

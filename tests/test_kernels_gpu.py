@@ -735,3 +735,52 @@ def test_qk_rope_cache_for_prompt_portions_agrees_with_the_general_kernel(nq, nk
         assert bool(((a - b).abs() <= 2 ** -7 * torch.maximum(a.abs(), b.abs()) + 1e-6).all())
     assert torch.equal(results[0][2], results[1][2])
     assert (results[0][0] == results[1][0]).double().mean().item() > 0.98
+
+
+@pytest.mark.parametrize("splits", [None, 1, 4, 12])
+@pytest.mark.parametrize("nq, nkv, page, norm, write_kv", [(32, 8, 64, True, True), (16, 1, 16, True, True), (8, 8, 8, False, True),
+                                                           (12, 4, 32, True, False)])
+def test_decoding_attention_that_finishes_the_projection_itself(nq, nkv, page, norm, write_kv, splits):
+    """One token a sequence, heads of 128: the decoding kernel given the q/k/v rows as the projection leaves them
+    (it norms and rotates its token, stores key and value, and puts them into the tile it fetched) against the
+    separate kernel followed by the same attention kernel: the same bits in the output and in the pages."""
+    from rust_mlx_b200.engine.workspace import Workspace
+    hd, rot = 128, 128
+    torch.manual_seed(nq * 10 + page)
+    lengths = [200, 17, 64, 65, 700, 1, 128]
+    new = [1] * len(lengths)
+    k0, v0, table, ks, vs = paged_setup(lengths, nkv, hd, page, torch.bfloat16, seed=nq + page)
+    n = len(lengths)
+    positions = torch.tensor([l - 1 for l in lengths], dtype=torch.int32, device=DEV)
+    seq_index = torch.arange(n, dtype=torch.int32, device=DEV)
+    qkv = rnd((n, (nq + 2 * nkv) * hd), torch.bfloat16, 1.0, 9)
+    qn = (1 + 0.2 * torch.randn(hd)).to(DEV) if norm else None
+    kn = (1 + 0.2 * torch.randn(hd)).to(DEV) if norm else None
+    inv_freq = (1e6 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float().to(DEV)
+    angles = torch.empty(n, rot, device=DEV)
+    ops().rope_table(positions, inv_freq, rot, angles)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    batch = _Batch(lengths, new, status)
+    ws = Workspace(DEV)
+    scale = hd ** -0.5
+    # separately: the pages get the token's key and value, q its rotated queries; then attention
+    k1, v1 = k0.clone(), v0.clone()
+    q1 = torch.empty(n, nq * hd, dtype=torch.bfloat16, device=DEV)
+    ops().qk_rope_cache(qkv, qn, kn, 1e-6, inv_freq, rot, positions, seq_index, table, page, k1, v1, q1, nq, nkv, hd, write_kv,
+                        status, cos_sin=angles)
+    out1 = torch.full((n, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops().attention_flash(q1, k1, v1, batch, table, page, out1, nq, nkv, hd, 0, scale, ws, n_splits=splits)
+    # in one: the token's slot in the pages holds NaN until the kernel stores there
+    k2, v2 = k0.clone(), v0.clone()
+    if write_kv:
+        for s, l in enumerate(lengths):
+            k2[table[s, (l - 1) // page], :, (l - 1) % page] = float("nan")
+            v2[table[s, (l - 1) // page], :, (l - 1) % page] = float("nan")
+    out2 = torch.full_like(out1, float("nan"))
+    ops().attention_flash(None, k2, v2, batch, table, page, out2, nq, nkv, hd, 0, scale, ws, n_splits=splits,
+                          projection=(qkv, qn, kn, 1e-6, angles, write_kv))
+    assert status.item() == 0
+    assert not torch.isnan(out2.float()).any()
+    assert torch.equal(out1, out2)
+    # (bit patterns: slots that no request holds are NaN in both)
+    assert torch.equal(k1.view(torch.int16), k2.view(torch.int16)) and torch.equal(v1.view(torch.int16), v2.view(torch.int16))
