@@ -470,14 +470,19 @@ def tcgen05_supported(m: int, n: int, k: int) -> bool:
 def tcgen05_splits(m: int, n: int, k: int) -> int:
     """How many slices of K share a tile of 128 weight rows.  The product is bound by reading the
     weight: what matters is that enough blocks are resident to keep loads in flight on every SM
-    (about one block per SM; measured on Qwen3-8B shapes), not that the last wave is full.  So:
-    the fewest slices that give at least 128 blocks, at most 8 (a cluster), each slice keeping at
-    least 4 k-blocks of 64."""
+    (measured on Qwen3-8B shapes), not that the last wave is full.  So: the fewest slices that
+    give at least 128 blocks; as many as give 192 blocks where each slice then still has 24
+    k-blocks of 64 (long reductions: the down projection); at most 8 (a cluster), each slice
+    keeping at least 4 k-blocks."""
     tiles = -(-n // 128)
     k_blocks = -(-k // 64)
     if tiles >= 128:
         return 1
-    return max(1, min(-(-128 // tiles), 8, k_blocks // 4))
+    splits = -(-128 // tiles)
+    more = -(-192 // tiles)
+    if more <= 8 and k_blocks // more >= 24:
+        splits = more
+    return max(1, min(splits, 8, k_blocks // 4))
 
 
 def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False, swiglu=False):
