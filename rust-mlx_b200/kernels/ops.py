@@ -185,6 +185,7 @@ tcgen05_policy = "auto"
 # loads start while that kernel ends.
 dependent_launch = True
 _tuned = {}   # (n, k, padded rows) -> True if the tcgen05 kernel was faster
+_tuned_splits = {}   # (n, k, padded rows) -> the number of K slices that was fastest
 
 
 def _mpad(m: int) -> int:
@@ -239,11 +240,20 @@ def autotune_linears(weights: list, workspace=None, rows=(8, 32, 64), log=None) 
             a = torch.randn(m, k, device=ws[0].device).to(torch.bfloat16)
             out = torch.empty(m, n, dtype=torch.bfloat16, device=ws[0].device)
             calls = max(4, min(len(ws), 12))
-            mine = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], out, workspace), calls)
+            # the kernel's own choice first: how many slices of K share a tile (the rule's count and its neighbours)
+            rule = min(tcgen05_splits(m, n, k), 8 if m <= 32 else 4)
+            best = None
+            for splits in sorted({max(1, rule - 1), rule, min(rule + 1, 8 if m <= 32 else 4), min(rule + 2, 8 if m <= 32 else 4)}):
+                if splits > max(1, -(-k // 64) // 4):
+                    continue
+                t = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], out, workspace, splits=splits, dependent=True), calls)
+                if best is None or t < best[0]:
+                    best = (t, splits)
+            mine, _tuned_splits[key] = best
             lib = _graph_time(lambda i: torch.mm(a, ws[i % len(ws)].t(), out=out), calls)
             _tuned[key] = mine < lib
             if log is not None:
-                log(f"product [{m} x {k}] . [{n} x {k}]^T: tcgen05 {mine:.1f} us, library {lib:.1f} us")
+                log(f"product [{m} x {k}] . [{n} x {k}]^T: tcgen05 {mine:.1f} us with {best[1]} slices of K, library {lib:.1f} us")
     return dict(_tuned)
 
 
@@ -502,7 +512,9 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
         raise KernelError("gemm_tcgen05: the result is bfloat16 or float32")
     ws = workspace if workspace is not None else _own_workspace()
     if splits is None:
-        splits = tcgen05_splits(m, n, k)
+        splits = _tuned_splits.get((n, k, _mpad(m))) if not swiglu else None
+        if splits is None:
+            splits = tcgen05_splits(m, n, k)
         if cluster:
             splits = min(splits, 8 if m <= 32 else 4)
     partial = counters = None
