@@ -281,7 +281,9 @@ def autotune_fused_swiglu(weights: list, workspace=None, rows=(8, 32, 64), log=N
                 torch.mm(a, ws[i % len(ws)].t(), out=gu)
                 swiglu(gu, act, 64)
             lib = _graph_time(lib_pair, calls)
-            _tuned[key] = mine < lib
+            # inside a step the fused product also spares a kernel's start and end, which this timing of the pair
+            # alone does not show: it is taken unless the pair is clearly faster
+            _tuned[key] = mine < lib * 1.05
             if log is not None:
                 log(f"gate/up [{m} x {k}] . [{n} x {k}]^T + SwiGLU: fused tcgen05 {mine:.1f} us, library + pointwise {lib:.1f} us")
     return dict(_tuned)
