@@ -135,6 +135,13 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restri
                                         const int* __restrict__ rows, const float* __restrict__ w, float eps,
                                         T* __restrict__ x, int width, int write_h) {
     __shared__ float scratch[32];
+    // the norm's weight does not come from the kernel before this one: it is fetched before the wait for it
+    float4 g[CHUNKS];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        g[c] = i < width ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     wait_for_prior_kernels();
     allow_dependents();
     const int r = blockIdx.x;
@@ -167,10 +174,8 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restri
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
         const int i = (c * blockDim.x + threadIdx.x) * 4;
-        if (i < width) {
-            const float4 g = *reinterpret_cast<const float4*>(w + i);
-            store4(xrow + i, make_float4(v[c].x * inv * g.x, v[c].y * inv * g.y, v[c].z * inv * g.z, v[c].w * inv * g.w));
-        }
+        if (i < width)
+            store4(xrow + i, make_float4(v[c].x * inv * g[c].x, v[c].y * inv * g[c].y, v[c].z * inv * g[c].z, v[c].w * inv * g[c].w));
     }
 }
 
