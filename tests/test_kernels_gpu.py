@@ -738,9 +738,10 @@ def test_qk_rope_cache_for_prompt_portions_agrees_with_the_general_kernel(nq, nk
 
 
 @pytest.mark.parametrize("splits", [None, 1, 4, 12])
-@pytest.mark.parametrize("nq, nkv, page, norm, write_kv", [(32, 8, 64, True, True), (16, 1, 16, True, True), (8, 8, 8, False, True),
-                                                           (12, 4, 32, True, False)])
-def test_decoding_attention_that_finishes_the_projection_itself(nq, nkv, page, norm, write_kv, splits):
+@pytest.mark.parametrize("nq, nkv, page, norm, write_kv, window", [
+    (32, 8, 64, True, True, 0), (16, 1, 16, True, True, 0), (8, 8, 8, False, True, 0), (12, 4, 32, True, False, 0),
+    (32, 8, 64, True, True, 100), (8, 2, 16, True, True, 65)])
+def test_decoding_attention_that_finishes_the_projection_itself(nq, nkv, page, norm, write_kv, window, splits):
     """One token a sequence, heads of 128: the decoding kernel given the q/k/v rows as the projection leaves them
     (it norms and rotates its token, stores key and value, and puts them into the tile it fetched) against the
     separate kernel followed by the same attention kernel: the same bits in the output and in the pages."""
@@ -769,7 +770,7 @@ def test_decoding_attention_that_finishes_the_projection_itself(nq, nkv, page, n
     ops().qk_rope_cache(qkv, qn, kn, 1e-6, inv_freq, rot, positions, seq_index, table, page, k1, v1, q1, nq, nkv, hd, write_kv,
                         status, cos_sin=angles)
     out1 = torch.full((n, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops().attention_flash(q1, k1, v1, batch, table, page, out1, nq, nkv, hd, 0, scale, ws, n_splits=splits)
+    ops().attention_flash(q1, k1, v1, batch, table, page, out1, nq, nkv, hd, window, scale, ws, n_splits=splits)
     # in one: the token's slot in the pages holds NaN until the kernel stores there
     k2, v2 = k0.clone(), v0.clone()
     if write_kv:
@@ -777,7 +778,7 @@ def test_decoding_attention_that_finishes_the_projection_itself(nq, nkv, page, n
             k2[table[s, (l - 1) // page], :, (l - 1) % page] = float("nan")
             v2[table[s, (l - 1) // page], :, (l - 1) % page] = float("nan")
     out2 = torch.full_like(out1, float("nan"))
-    ops().attention_flash(None, k2, v2, batch, table, page, out2, nq, nkv, hd, 0, scale, ws, n_splits=splits,
+    ops().attention_flash(None, k2, v2, batch, table, page, out2, nq, nkv, hd, window, scale, ws, n_splits=splits,
                           projection=(qkv, qn, kn, 1e-6, angles, write_kv))
     assert status.item() == 0
     assert not torch.isnan(out2.float()).any()
