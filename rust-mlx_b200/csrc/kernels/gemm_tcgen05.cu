@@ -556,7 +556,7 @@ int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K,
     const int n_tiles = (N + TILE_N - 1) / TILE_N;
     const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     // flags: 1 = reduce split-K inside a cluster when it can be (no scratch needed); 2 = programmatic dependent launch
-    const int stages = mpad == 64 ? 4 : 5;
+    const int stages = mpad == 64 ? 4 : (mpad == 16 ? 6 : 5);
     const bool fits = (size_t)(splits - 1) * mpad * TILE_N * 4 <= (size_t)stages * (TILE_N * TILE_K * 2 + mpad * TILE_K * 2);
     const bool cluster = (flags & 1) && splits >= 2 && splits <= 8 && fits;
     const bool dependent = (flags & 2) != 0;
@@ -573,7 +573,7 @@ int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K,
     p.heads = HeadsEpilogue{};
     if (heads) p.heads = *heads;
     // stages sized so that two blocks fit an SM: more blocks in flight smooth the last wave
-    if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s, cluster, dependent);
+    if (mpad == 16) return launch<16, 6>(mw, ma, p, n_tiles, s, cluster, dependent);
     if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s, cluster, dependent);
     return launch<64, 4>(mw, ma, p, n_tiles, s, cluster, dependent);
 }
