@@ -147,6 +147,12 @@ struct Params {
     int n_seqs, nq, nkv, group, tq, table_stride, page_size, page_shift, window, box_rows;
     int per_block;   // query tiles a block takes: 2 (they share each key tile) or, for small steps, 1 (more blocks)
     float scale_log2;
+    // With n_splits > 1 (a step so small that whole tiles would leave SMs without work) blockIdx.z takes one of that
+    // many runs of the tile's key tiles and leaves its share, O not yet divided by the row's sum, with the row's
+    // (reference maximum, sum); a second kernel adds the shares.
+    int n_splits, n_rows;          // n_rows = tokens * nq
+    float* part_o;                 // [n_splits][n_rows][HD]
+    float* part_ml;                // [n_splits][n_rows][2]
 };
 
 // One block: two neighbouring query tiles (A and B, 128 rows each) of one sequence against one kv head.  Both use
@@ -253,6 +259,12 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
         pos_last = pos0 + n_tok - 1;
         kt_lo = lo_first / BN;
         n_kt = pos_last / BN - kt_lo + 1;
+        if (p.n_splits > 1) {   // this block's run of the key tiles (it may be empty)
+            const int per = (n_kt + p.n_splits - 1) / p.n_splits;
+            const int first = min(n_kt, (int)blockIdx.z * per), last = min(n_kt, first + per);
+            kt_lo += first;
+            n_kt = last - first;
+        }
     }
     const bool two = n_tok > p.tq;   // the second tile has rows
 
@@ -479,13 +491,32 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
             fence_before();
             mbar_arrive(&p_full[t]);
         }
-        if (ok && n_kt > 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(&o_done[t], (n_kt - 1) & 1));
-            if (ok) {
-                fence_after();
+        if (ok && n_kt > 0) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[t], (n_kt - 1) & 1));
+        if (ok) {
+            fence_after();
+            const int g = r - tok * p.group;
+            const size_t row = (size_t)(tile_tok0 + tok) * p.nq + kvh * p.group + g;
+            if (p.n_splits > 1) {
+                // this run's share of the row (a run without keys leaves maximum -inf and sum 0, and no numbers)
+                float* dst = p.part_o + ((size_t)blockIdx.z * p.n_rows + row) * HD;
+                if (n_kt > 0) {
+#pragma unroll
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(lane_addr + O_COL + c, v);
+                        tmem_ld_wait();
+                        if (row_ok) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(dst + c + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                                      __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        }
+                    }
+                }
+                if (row_ok) *reinterpret_cast<float2*>(p.part_ml + ((size_t)blockIdx.z * p.n_rows + row) * 2) = make_float2(m, l);
+            } else if (n_kt > 0) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                const int g = r - tok * p.group;
-                __nv_bfloat16* dst = p.out + ((size_t)(tile_tok0 + tok) * p.nq + kvh * p.group + g) * HD;
+                __nv_bfloat16* dst = p.out + row * HD;
 #pragma unroll
                 for (int c = 0; c < HD; c += 32) {
                     uint32_t v[32];
@@ -512,6 +543,32 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
     __syncthreads();
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
     if (tid == 0 && s_failed) atomicExch(p.status, 3);
+}
+
+// out[row] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the runs z of the row's keys, in run order.
+__global__ void __launch_bounds__(128) attention_tcgen05_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                                      __nv_bfloat16* __restrict__ out, int n_rows, int n_splits,
+                                                                      int first_row, int rows) {
+    const int lane = threadIdx.x & 31;
+    if (blockIdx.x * 4 + (threadIdx.x >> 5) >= rows) return;
+    const int row = first_row + blockIdx.x * 4 + (threadIdx.x >> 5);
+    float M = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((size_t)z * n_rows + row) * 2]);
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int z = 0; z < n_splits; ++z) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((size_t)z * n_rows + row) * 2);
+        if (ml.x == -INFINITY) continue;
+        const float f = exp2f(ml.x - M);
+        const float4 v = *reinterpret_cast<const float4*>(part_o + ((size_t)z * n_rows + row) * HD + lane * 4);
+        L += f * ml.y;
+        acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    uint2 o;
+    o.x = pack_bf16(acc.x * inv, acc.y * inv);
+    o.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + (size_t)row * HD + lane * 4) = o;
 }
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -601,10 +658,14 @@ RMX_API int rmx_attention_tcgen05_tile_tokens(int group) { return BM / group; }
 // or 1 (twice the blocks: for steps so small that two tiles a block would leave SMs without work).
 // n_tiles: the number of blocks: sum over sequences of ceil(tokens / (tiles_per_block * 128 / group)).
 // pool_pages: pages in k_pool / v_pool.
+// n_splits > 1: every tile's keys in that many runs, one block each (blockIdx.z), added by a second kernel; part_o
+// [n_splits, n_tokens * nq, 128] and part_ml [n_splits, n_tokens * nq, 2] floats are their scratch; the sequences
+// given hold the step's tokens first_token .. first_token + run_tokens - 1 (only their rows of `out` are written).
 RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* q_start,
                                   const int* positions, const int* block_table, int table_stride, int page_size,
                                   void* out, int n_seqs, int n_tokens, int n_tiles, int tiles_per_block, int nq, int nkv,
-                                  int hd, int window, float scale, int pool_pages, int* status, void* stream) {
+                                  int hd, int window, float scale, int pool_pages, int n_splits, float* part_o, float* part_ml,
+                                  int first_token, int run_tokens, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(tiles_per_block == 1 || tiles_per_block == 2, "attention_tcgen05: a block takes 1 or 2 tiles, not %d", tiles_per_block);
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tcgen05: %d query heads over %d kv heads", nq, nkv);
@@ -621,6 +682,8 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
     p.n_seqs = n_seqs; p.nq = nq; p.nkv = nkv; p.group = group; p.tq = BM / group; p.table_stride = table_stride;
     p.page_size = page_size; p.window = window; p.box_rows = page_size < BN ? page_size : BN;
     p.per_block = tiles_per_block;
+    RMX_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (part_o && part_ml)), "attention_tcgen05: %d runs of keys need room for their shares", n_splits);
+    p.n_splits = n_splits; p.n_rows = n_tokens * nq; p.part_o = part_o; p.part_ml = part_ml;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2 = scale * LOG2E;
@@ -637,7 +700,13 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
         raised = true;
     }
     // blocks are handed to the SMs in the order x, then y: all kv heads of the tile that sees the most keys first
-    attention_tcgen05_kernel<<<dim3(nkv, n_tiles), THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    attention_tcgen05_kernel<<<dim3(nkv, n_tiles, n_splits), THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
     RMX_CHECK_LAUNCH("attention_tcgen05");
+    if (n_splits > 1) {
+        RMX_REQUIRE(first_token >= 0 && run_tokens > 0 && first_token + run_tokens <= n_tokens, "attention_tcgen05: the tokens of this launch are not among the step's");
+        attention_tcgen05_merge_kernel<<<(run_tokens * nq + 3) / 4, 128, 0, (cudaStream_t)stream>>>(part_o, part_ml, (__nv_bfloat16*)out, p.n_rows, n_splits,
+                                                                                                  first_token * nq, run_tokens * nq);
+        RMX_CHECK_LAUNCH("attention_tcgen05_merge");
+    }
     return 0;
 }

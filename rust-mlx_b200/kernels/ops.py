@@ -363,7 +363,7 @@ def _attention_bf16(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
     group = nq // nkv
     if (q.dtype == torch.bfloat16 and use_tcgen05_attention and getattr(batch, "max_q_len", 0) * group > 16
             and tcgen05_attention_supported(hd, group, page_size)):
-        attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale)
+        attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=workspace)
         return
     if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, nq // nkv):
         attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace)
@@ -598,25 +598,49 @@ def tcgen05_attention_supported(hd: int, group: int, page_size: int) -> bool:
     return bool(kernels_library().rmx_attention_tcgen05_supports(c_int(hd), c_int(group), c_int(page_size)))
 
 
-def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, per_block=None):
-    """Prompt portions: S = Q K^T and O += P V as tcgen05 MMAs with accumulators in tensor memory.  A block takes
-    two neighbouring tiles of 128 rows, which share the key tiles it fetches, unless that leaves SMs without work
-    (a portion of a few hundred tokens): then one tile a block."""
+def tcgen05_attention_shape(counts: list, nkv: int, group: int, max_seq_len: int) -> tuple:
+    """(query tiles a block, runs of keys) for prompt portions of ``counts`` tokens: two neighbouring tiles of 128
+    rows a block (they share the key tiles it fetches); where that leaves SMs without work, the tiles' keys in as
+    many runs as fill them (each of at least 12 key tiles of 64, at most 8 runs: measured, shorter runs cost more
+    in the second kernel that adds them than they gain), or failing that one tile a block."""
+    tile = 128 // group
+    pairs = sum(-(-c // (2 * tile)) for c in counts) * nkv
+    if pairs >= _sm_count():
+        return 2, 1
+    runs = min(_sm_count() // pairs, -(-max_seq_len // 64) // 12, 8)
+    if runs >= 2:
+        return 2, runs
+    return 1, 1
+
+
+def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, per_block=None,
+                      n_splits=None, workspace=None):
+    """Prompt portions: S = Q K^T and O += P V as tcgen05 MMAs with accumulators in tensor memory (see
+    ``tcgen05_attention_shape`` for how the work is divided; ``per_block`` and ``n_splits`` override it)."""
     lib = kernels_library()
     tile = 128 // (nq // nkv)
     starts = batch.q_start_host
-    if per_block is None:
-        pairs = sum(-(-(starts[i + 1] - starts[i]) // (2 * tile)) for i in range(batch.n_seqs))
-        per_block = 2 if pairs * nkv >= _sm_count() else 1
-    n_tiles = sum(-(-(starts[i + 1] - starts[i]) // (per_block * tile)) for i in range(batch.n_seqs))
+    counts = [starts[i + 1] - starts[i] for i in range(batch.n_seqs)]
+    if per_block is None and n_splits is None:
+        per_block, n_splits = tcgen05_attention_shape(counts, nkv, nq // nkv, batch.max_seq_len)
+        if workspace is None:
+            n_splits = 1
+    per_block = 2 if per_block is None else per_block
+    n_splits = 1 if n_splits is None else n_splits
+    n_tiles = sum(-(-c // (per_block * tile)) for c in counts)
+    part_o = part_ml = None
+    if n_splits > 1:
+        ws = workspace if workspace is not None else _own_workspace()
+        part_o = ws.get("attn_part_o", (n_splits, q.shape[0] * nq, hd), torch.float32)
+        part_ml = ws.get("attn_part_ml", (n_splits, q.shape[0] * nq, 2), torch.float32)
     check(lib.rmx_attention_tcgen05(
         _ptr(q, torch.bfloat16, "q"), _ptr(k_pool, torch.bfloat16, "k_pool"), _ptr(v_pool, torch.bfloat16, "v_pool"),
         _ptr(batch.q_start, torch.int32, "q_start"), _ptr(batch.positions, torch.int32, "positions"),
         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
         _ptr(out, torch.bfloat16, "out"), c_int(batch.n_seqs), c_int(q.shape[0]), c_int(n_tiles), c_int(per_block),
-        c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(k_pool.shape[0]),
-        _ptr(batch.status, torch.int32, "status"), _stream()))
-    _launched()
+        c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(k_pool.shape[0]), c_int(n_splits),
+        _ptr(part_o), _ptr(part_ml), c_int(starts[0]), c_int(starts[-1] - starts[0]), _ptr(batch.status, torch.int32, "status"), _stream()))
+    _launched(2 if n_splits > 1 else 1)
 
 
 def set_dependent_launch(on: bool) -> None:

@@ -584,11 +584,12 @@ def test_gemm_tcgen05_refuses_what_it_cannot_do():
 
 @pytest.mark.parametrize("nq, nkv, page, window", [(32, 8, 64, 0), (8, 8, 16, 0), (16, 1, 8, 0), (4, 2, 32, 50), (8, 2, 128, 0),
                                                    (32, 8, 64, 300)])
-@pytest.mark.parametrize("per_block", [1, 2])
-def test_attention_tcgen05_over_pages(nq, nkv, page, window, per_block):
+@pytest.mark.parametrize("per_block, runs", [(1, 1), (2, 1), (2, 3), (1, 2)])
+def test_attention_tcgen05_over_pages(nq, nkv, page, window, per_block, runs):
     """Prompt portions on the tcgen05 tensor cores (head size 128): several sequences whose portions span
     more than one tile of 128 rows and several key tiles, beside short ones; NaN in every slot of the pool
-    that must not be read.  With two query tiles a block (they share the key tiles) and with one."""
+    that must not be read.  With two query tiles a block (they share the key tiles) and with one; with every
+    tile's keys in one run and in several (some of which are empty for short sequences)."""
     hd = 128
     torch.manual_seed(nq * 100 + page)
     lengths = [300, 40, 33, 130, 700, 64, 1]
@@ -600,7 +601,7 @@ def test_attention_tcgen05_over_pages(nq, nkv, page, window, per_block):
     batch = _Batch(lengths, new, status)
     out = torch.full_like(q, float("nan"))
     scale = hd ** -0.5
-    ops().attention_tcgen05(q, k_pool, v_pool, batch, table, page, out, nq, nkv, hd, window, scale, per_block=per_block)
+    ops().attention_tcgen05(q, k_pool, v_pool, batch, table, page, out, nq, nkv, hd, window, scale, per_block=per_block, n_splits=runs)
     assert status.item() == 0
     at = 0
     for s, (n, c) in enumerate(zip(lengths, new)):

@@ -64,3 +64,14 @@ def test_mixed_steps_divide_into_decoded_tokens_and_portions(ops):
     # with 16 query heads per kv head only single tokens are short
     short, long_ = ops._short_and_long(batch_of([1, 2, 200], [5, 6, 200]), 16)
     assert (short.first, short.last, long_.first, long_.last) == (0, 1, 1, 3)
+
+
+def test_division_of_prompt_attention(ops):
+    # (tiles a block, runs of keys) at 8 kv heads, 4 query heads each (32 tokens a tile)
+    assert ops.tcgen05_attention_shape([2048], 8, 4, 2048) == (2, 1)       # 256 blocks: enough
+    assert ops.tcgen05_attention_shape([512], 8, 4, 3072) == (2, 2)        # 64 blocks, 48 key tiles: two runs
+    assert ops.tcgen05_attention_shape([256], 8, 4, 3072) == (2, 4)
+    assert ops.tcgen05_attention_shape([512], 8, 4, 1024) == (1, 1)        # too few keys to share: one tile a block
+    assert ops.tcgen05_attention_shape([512], 8, 4, 8192) == (2, 2)
+    assert ops.tcgen05_attention_shape([64], 8, 4, 65536) == (2, 8)
+    assert ops.tcgen05_attention_shape([40, 40, 40], 2, 16, 40) == (1, 1)
