@@ -133,6 +133,28 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+// Two floats in one 64-bit register, for the instructions that work on such pairs, and the maximum of three.
+__device__ __forceinline__ uint64_t pair(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpair(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma_pair(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add_pair(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -422,7 +444,7 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
             float mx = -INFINITY;
             if (whole) {
 #pragma unroll
-                for (int j = 0; j < BN; ++j) mx = fmaxf(mx, s[j]);
+                for (int j = 0; j < BN; j += 2) mx = max3(mx, s[j], s[j + 1]);
                 mx *= p.scale_log2;
             } else {
 #pragma unroll
@@ -441,15 +463,21 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
             const float corr = m_new == -INFINITY ? 1.f : ex2(m - m_new);
             const float neg_ref = m_new == -INFINITY ? 0.f : -m_new;
             m = m_new;
-            float sum = 0.f;
+            // exponents and the row's sum two numbers at a time (fma and add on pairs of floats)
+            const uint64_t scale2 = pair(p.scale_log2, p.scale_log2), ref2 = pair(neg_ref, neg_ref);
+            uint64_t sum2 = pair(0.f, 0.f);
             uint32_t pk[BN / 2];
 #pragma unroll
             for (int j = 0; j < BN; j += 2) {
-                const float a = ex2(fmaf(s[j], p.scale_log2, neg_ref)), b = ex2(fmaf(s[j + 1], p.scale_log2, neg_ref));
-                sum += a + b;
+                float e0, e1;
+                unpair(fma_pair(pair(s[j], s[j + 1]), scale2, ref2), e0, e1);
+                const float a = ex2(e0), b = ex2(e1);
+                sum2 = add_pair(sum2, pair(a, b));
                 pk[j / 2] = pack_bf16(a, b);
             }
-            l = l * corr + sum;
+            float sum_even, sum_odd;
+            unpair(sum2, sum_even, sum_odd);
+            l = l * corr + (sum_even + sum_odd);
             if (i > 0) {
                 // the MMA that used the last probabilities and added into O has finished
                 ok = __all_sync(0xffffffffu, mbar_wait(&o_done[t], (i - 1) & 1));
