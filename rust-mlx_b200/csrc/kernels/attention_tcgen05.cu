@@ -290,53 +290,78 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
     }
     const bool two = n_tok > p.tq;   // the second tile has rows
 
-    if (warp == 0 && lane == 0 && seq >= 0) {
-        // ---- producer
-        mbar_expect_tx(&q_full, two ? 2 * Q_BYTES : Q_BYTES);
-        for (int t = 0; t < (two ? 2 : 1); ++t) {
-            tma_3d(q_smem + t * Q_BYTES, &map_q, &q_full, 0, kvh * p.group, tok0 + t * p.tq);
-            tma_3d(q_smem + t * Q_BYTES + Q_BYTES / 2, &map_q, &q_full, 64, kvh * p.group, tok0 + t * p.tq);
-        }
-        const int boxes = BN / p.box_rows;
-        // the boxes of key tile i (keys when `keys`, else values) into slot i % STAGES; returns their bytes
-        auto fetch = [&](int i, bool keys, uint64_t* bar, bool count_only) {
-            const int st = i % STAGES, kt = kt_lo + i;
-            uint32_t bytes = 0;
-            for (int b = 0; b < boxes; ++b) {
-                const int kp = kt * BN + b * p.box_rows;
-                if (kp > pos_last || kp + p.box_rows <= lo_first) continue;
-                const int page = table[kp >> p.page_shift];
-                if (page < 0) {
-                    if (count_only) atomicExch(p.status, 2);
-                    continue;
-                }
-                bytes += p.box_rows * HD * 2u;
-                if (count_only) continue;
-                const int row = (page * p.nkv + kvh) * p.page_size + (kp & (p.page_size - 1));
-#pragma unroll
-                for (int cb = 0; cb < 2; ++cb) {
-                    if (keys) tma_2d(k_smem + st * (KV_BYTES / 2) + cb * (STAGES * KV_BYTES / 2) + b * p.box_rows * 128, &map_k, bar, cb * 64, row);
-                    else tma_2d(v_smem + st * KV_BYTES + cb * (KV_BYTES / 2) + b * p.box_rows * 128, &map_v, bar, cb * 64, row);
-                }
+    if (warp == 0 && seq >= 0) {
+        // ---- producer.  A copy brings one box (a page's keys or values of one tile, or 64 of them if pages are
+        // larger) of one half of d; the copies of a group (a pair of key tiles, or one value tile: at most 32) are
+        // issued by as many lanes at once, because a thread that issues them one after another takes longer than the
+        // tensor cores take for the tile.  The warp holds the part of the block table that the copies are about to
+        // need in registers (three runs of 32 entries, the last one still on its way), so that no copy waits for a
+        // load of its page's number from global memory.
+        constexpr uint32_t FULL = 0xffffffffu;
+        if (lane == 0) {
+            mbar_expect_tx(&q_full, two ? 2 * Q_BYTES : Q_BYTES);
+            for (int t = 0; t < (two ? 2 : 1); ++t) {
+                tma_3d(q_smem + t * Q_BYTES, &map_q, &q_full, 0, kvh * p.group, tok0 + t * p.tq);
+                tma_3d(q_smem + t * Q_BYTES + Q_BYTES / 2, &map_q, &q_full, 64, kvh * p.group, tok0 + t * p.tq);
             }
-            return bytes;
+        }
+        int win = ((kt_lo * BN) >> p.page_shift) & ~31;   // the table entry that lane 0 of `cur` holds
+        auto entries = [&](int first) {
+            const int e = first + lane;
+            return e < p.table_stride ? table[e] : -1;
+        };
+        int cur = entries(win), nxt = entries(win + 32), far = entries(win + 64);
+        auto wait = [&](uint64_t* bar, uint32_t parity) {
+            int done = lane == 0 ? (int)mbar_wait(bar, parity) : 1;
+            return __shfl_sync(FULL, done, 0) != 0;
+        };
+        // this lane's copy within a group: which tile of the group, which box of the tile, which half of d
+        const int boxes = BN / p.box_rows, per_tile = 2 * boxes;
+        const int my_tile = lane / per_tile, my_box = (lane % per_tile) >> 1, my_half = lane & 1;
+        const uint32_t copy_bytes = p.box_rows * 64 * 2u;
+        // the copies of tiles first .. first + n - 1 (keys when `keys`, else values) into their slots, counted by `bar`
+        auto fetch = [&](int first, int n, bool keys, uint64_t* bar) {
+            // move the table's registers on so that the group's last entry lies in them (no group reaches back more
+            // than 32 entries behind the furthest entry asked for so far)
+            const int e_last = min((kt_lo + first + n) * BN - 1, pos_last) >> p.page_shift;
+            while (e_last >= win + 64) {
+                cur = nxt;
+                nxt = far;
+                win += 32;
+                far = entries(win + 64);
+            }
+            const int i = first + my_tile, kp = (kt_lo + i) * BN + my_box * p.box_rows, e = kp >> p.page_shift;
+            const int a = __shfl_sync(FULL, cur, e & 31), b = __shfl_sync(FULL, nxt, e & 31);
+            const int page = e < win + 32 ? a : b;
+            bool mine = my_tile < n && kp <= pos_last && kp + p.box_rows > lo_first;
+            if (mine && page < 0) {   // a page the request does not hold: an error of the caller
+                atomicExch(p.status, 2);
+                mine = false;
+            }
+            const uint32_t copies = __popc(__ballot_sync(FULL, mine));
+            if (lane == 0) mbar_expect_tx(bar, copies * copy_bytes);
+            __syncwarp();
+            if (mine) {
+                const int st = i % STAGES;
+                const int row = (page * p.nkv + kvh) * p.page_size + (kp & (p.page_size - 1));
+                unsigned char* dst = keys ? k_smem + st * (KV_BYTES / 2) + my_half * (STAGES * KV_BYTES / 2)
+                                          : v_smem + st * KV_BYTES + my_half * (KV_BYTES / 2);
+                tma_2d(dst + my_box * p.box_rows * 128, keys ? &map_k : &map_v, bar, my_half * 64, row);
+            }
+            __syncwarp();
         };
         bool ok = true;
         for (int i = 0; i < n_kt && ok; ++i) {
             if ((i & 1) == 0) {   // the keys of the pair of tiles i, i + 1: their slots are free once the scores of the pair before last are formed
-                const int j = i >> 1, last = min(i + 2, n_kt);
-                if (j >= 2 && !mbar_wait(&k_empty[j & 1], ((j >> 1) - 1) & 1)) { ok = false; break; }
-                uint32_t bytes = 0;
-                for (int ii = i; ii < last; ++ii) bytes += fetch(ii, true, nullptr, true);
-                mbar_expect_tx(&k_full[j & 1], bytes);
-                for (int ii = i; ii < last; ++ii) fetch(ii, true, &k_full[j & 1], false);
+                const int j = i >> 1;
+                if (j >= 2 && !wait(&k_empty[j & 1], ((j >> 1) - 1) & 1)) { ok = false; break; }
+                fetch(i, min(2, n_kt - i), true, &k_full[j & 1]);
             }
             const int st = i % STAGES, round = i / STAGES;
-            if (round > 0 && !mbar_wait(&v_empty[st], (round - 1) & 1)) { ok = false; break; }
-            mbar_expect_tx(&v_full[st], fetch(i, false, nullptr, true));
-            fetch(i, false, &v_full[st], false);
+            if (round > 0 && !wait(&v_empty[st], (round - 1) & 1)) { ok = false; break; }
+            fetch(i, 1, false, &v_full[st]);
         }
-        if (!ok) atomicExch(&s_failed, 1);
+        if (!ok && lane == 0) atomicExch(&s_failed, 1);
     } else if (warp == 10 && lane == 0 && seq >= 0) {
         // ---- issuer of the score MMAs.  One thread issues them all, so what it executes per MMA counts: the operand
         // descriptors are formed before the loop (those of Q do not change; those of K differ by the pair's address,

@@ -612,6 +612,31 @@ def test_attention_tcgen05_over_pages(nq, nkv, page, window, per_block, runs):
         at += c
 
 
+@pytest.mark.parametrize("page, window, runs", [(8, 0, 1), (8, 600, 3), (16, 1000, 1), (8, 0, 4)])
+def test_attention_tcgen05_walks_long_block_tables(page, window, runs):
+    """Block tables of some hundred entries (the copying warp keeps a run of them in registers and moves on
+    along the table): a long sequence with a short portion, one taken whole, with and without a window (whose
+    first key lies far inside the table), in one run of keys and in several."""
+    nq, nkv, hd = 8, 2, 128
+    lengths, new = [2100, 1300, 70], [140, 1300, 3]
+    k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, torch.bfloat16, seed=page + window)
+    torch.manual_seed(window + runs)
+    qs = [torch.randn(c, nq, hd).to(torch.bfloat16) for c in new]
+    q = torch.cat(qs).to(DEV).reshape(-1, nq * hd)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full_like(q, float("nan"))
+    ops().attention_tcgen05(q, k_pool, v_pool, _Batch(lengths, new, status), table, page, out, nq, nkv, hd, window, hd ** -0.5,
+                            n_splits=runs)
+    assert status.item() == 0
+    at = 0
+    for s, (n, c) in enumerate(zip(lengths, new)):
+        want = plain_attention(qs[s], ks[s], vs[s], torch.arange(n - c, n), window, hd ** -0.5)
+        got = out[at:at + c].double().cpu().reshape(c, nq, hd)
+        assert not torch.isnan(got).any(), (s, n, c)
+        assert ((got - want).abs() <= 1e-2 * (1 + want.abs())).all(), (s, n, c, (got - want).abs().max().item())
+        at += c
+
+
 def test_attention_tcgen05_finds_a_far_key_and_respects_the_window_edge():
     nq, nkv, hd, page, n = 8, 2, 128, 16, 900
     k_pool, v_pool, table, ks, vs = paged_setup([n], nkv, hd, page, torch.bfloat16, seed=8)
