@@ -602,36 +602,38 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
 
     if (warp == NWARPS) {
         __syncwarp();   // the table's head is in shared memory
-        if (lane == 0) {
-            // ---- producer: per tile, 64 / box_rows boxes of rows by HD / 64 boxes of columns, for K and for V
-            const int boxes = BN / box_rows;
-            auto entry = [&](int j) { return KEYSPLIT && j < TABLE_KEPT ? s_table[j] : table[j]; };
-            for (int i = 0; i < n_mine; ++i) {
-                const int st = i % STAGES, round = i / STAGES, kt = kt_begin + i;
-                if (round > 0 && !mbar_wait(&empty_bar[st], (round - 1) & 1)) { atomicExch(&s_failed, 1); break; }
-                uint32_t bytes = 0;
-                for (int b = 0; b < boxes; ++b) {
-                    const int kp = kt * BN + b * box_rows;
-                    if (kp > pos_last || kp + box_rows <= lo_first) continue;
-                    if (entry(kp >> p.page_shift) >= 0) bytes += 2u * box_rows * HD * 2u;
-                    else atomicExch(p.status, 2);
-                }
-                mbar_expect_tx(&full_bar[st], bytes);
-                __nv_bfloat16* kd = KV + st * 2 * TILE_ELEMS;
-                __nv_bfloat16* vd = kd + TILE_ELEMS;
-                for (int b = 0; b < boxes; ++b) {
-                    const int kp = kt * BN + b * box_rows;
-                    if (kp > pos_last || kp + box_rows <= lo_first) continue;
-                    const int page = entry(kp >> p.page_shift);
-                    if (page < 0) continue;
-                    const int row = (page * p.nkv + kvh) * p.page_size + (kp & (p.page_size - 1));
-#pragma unroll
-                    for (int cb = 0; cb < HD / 64; ++cb) {
-                        tma_box(kd + cb * 64 * 64 + b * box_rows * 64, &map_k, &full_bar[st], cb * 64, row);
-                        tma_box(vd + cb * 64 * 64 + b * box_rows * 64, &map_v, &full_bar[st], cb * 64, row);
-                    }
-                }
+        // ---- producer: per tile, 64 / box_rows boxes of rows by HD / 64 boxes of columns, for K and for V: at most
+        // 32 copies, which as many lanes issue at once (one thread issuing them in turn is slower than the tiles
+        // are used up when pages are small)
+        constexpr int PER_BOX = 2 * (HD / 64);
+        const int boxes = BN / box_rows;
+        const int my_box = lane / PER_BOX, my_cb = (lane % PER_BOX) >> 1;
+        const bool my_v = lane & 1;
+        auto entry = [&](int j) { return KEYSPLIT && j < TABLE_KEPT ? s_table[j] : table[j]; };
+        for (int i = 0; i < n_mine; ++i) {
+            const int st = i % STAGES, round = i / STAGES, kt = kt_begin + i;
+            int ok = 1;
+            if (round > 0 && lane == 0) ok = mbar_wait(&empty_bar[st], (round - 1) & 1);
+            if (!__shfl_sync(0xffffffffu, ok, 0)) {
+                if (lane == 0) atomicExch(&s_failed, 1);
+                break;
             }
+            const int kp = kt * BN + my_box * box_rows;
+            bool mine = my_box < boxes && kp <= pos_last && kp + box_rows > lo_first;
+            const int page = mine ? entry(kp >> p.page_shift) : 0;
+            if (mine && page < 0) {
+                atomicExch(p.status, 2);
+                mine = false;
+            }
+            const uint32_t copies = __popc(__ballot_sync(0xffffffffu, mine));
+            if (lane == 0) mbar_expect_tx(&full_bar[st], copies * (uint32_t)box_rows * 64u * 2u);
+            __syncwarp();
+            if (mine) {
+                __nv_bfloat16* dst = KV + st * 2 * TILE_ELEMS + (my_v ? TILE_ELEMS : 0) + my_cb * 64 * 64 + my_box * box_rows * 64;
+                const int row = (page * p.nkv + kvh) * p.page_size + (kp & (p.page_size - 1));
+                tma_box(dst, my_v ? &map_v : &map_k, &full_bar[st], my_cb * 64, row);
+            }
+            __syncwarp();
         }
         __syncwarp();
     } else {
