@@ -328,7 +328,7 @@ def main():
                    "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"],
                    "vocab": raw["vocab_size"], "global_batch": a.batch, "seq_len": CONTEXT, "max_context": MAX_CONTEXT,
                    "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (15 GB of weights per step), no flush",
+                   "l2": f"inputs larger than L2 ({weight_bytes / 1e9:.0f} GB of weights per step), no flush",
                    "peaks": pk["source"]},
         "gpu_launches": launches, "clocks": clock_info,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
