@@ -26,10 +26,20 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     // argmax, lowest index on ties; NaN never wins
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = tid; i < vocab; i += THREADS) {
-        const float v = row[i];
+    auto take = [&](float v, int i) {
         if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    };
+    // four logits a load where the row starts on a 16-byte boundary, several loads in flight
+    const int n4 = (reinterpret_cast<uintptr_t>(row) & 15) == 0 ? vocab / 4 : 0;
+#pragma unroll 4
+    for (int i = tid; i < n4; i += THREADS) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(row) + i);
+        take(v.x, 4 * i);
+        take(v.y, 4 * i + 1);
+        take(v.z, 4 * i + 2);
+        take(v.w, 4 * i + 3);
     }
+    for (int i = 4 * n4 + tid; i < vocab; i += THREADS) take(row[i], i);
     s_val[tid] = best;
     s_idx[tid] = best_i;
     __syncthreads();
