@@ -6,9 +6,12 @@ folder), ``--prompt-ids`` (a JSON file holding an array of token ids),
 128, ``--ignore-eos``, ``--output`` (the JSON report; standard output if absent).
 runs, max-tokens and prefill-chunk must be positive (src/bin/infer.rs:62-65); one
 warm-up run of ``--warmup-tokens`` tokens comes before the timed runs (108-112,
-150-154) and every run starts from an empty cache (155).  Text prompts, chat
-templates and streaming need a tokenizer and are not offered: prompts are token
-ids.  Added: ``--dtype``, ``--temperature``, ``--seed``, ``--random-weights``,
+150-154) and every run starts from an empty cache (155).  ``--stream`` prints the
+tokens of the timed runs as they are generated (the reference prints their text,
+177-185: here token ids, space separated, ``i:id`` when there are several prompts)
+and, like the reference, leaves the report out of standard output (222).  Text
+prompts and chat templates need a tokenizer and are not offered: prompts are
+token ids.  Added: ``--dtype``, ``--temperature``, ``--seed``, ``--random-weights``,
 ``--page-size``, ``--cache-tokens``, ``--max-batch-tokens``; ``--prompt-ids`` may
 also hold an array of arrays, which are then generated as one batch.
 """
@@ -30,6 +33,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--prefill-chunk", type=int, default=128)
     ap.add_argument("--ignore-eos", action="store_true")
     ap.add_argument("--output", help="write the JSON report here instead of standard output")
+    ap.add_argument("--stream", action="store_true", help="print token ids as they are generated (timed runs only)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--temperature", type=float, default=0.0, help="0 is greedy")
     ap.add_argument("--seed", type=int, default=0)
@@ -73,7 +77,13 @@ def main(argv=None) -> int:
         warmup = run == 0
         limit = a.warmup_tokens if warmup else a.max_tokens
         torch.cuda.reset_peak_memory_stats()
-        r = engine.generate_detailed(prompts, max_tokens=max(limit, 1), **options)
+        on_token = None
+        if a.stream and not warmup:
+            def on_token(i, tok):
+                print(f"{i}:{tok}" if len(prompts) > 1 else tok, end=" ", flush=True)
+        r = engine.generate_detailed(prompts, max_tokens=max(limit, 1), on_token=on_token, **options)
+        if on_token is not None:
+            print(flush=True)
         tps = (r.generated_tokens - len(prompts)) / r.decode_seconds if r.decode_seconds > 0 else 0.0
         print(f"{'warmup' if warmup else 'run'} {run}: prompt={r.prompt_tokens} output={r.generated_tokens} "
               f"prefill={r.prefill_seconds:.3f}s decode={tps:.2f} tok/s", file=sys.stderr)
@@ -98,7 +108,7 @@ def main(argv=None) -> int:
     if a.output:
         with open(a.output, "w") as fh:
             fh.write(text)
-    else:
+    elif not a.stream:
         print(text)
     return 0
 

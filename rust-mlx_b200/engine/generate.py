@@ -45,7 +45,7 @@ class _Launched:
 def generate(engine, prompts: list, *, max_tokens: int = 256, temperature: float = 0.0, seed: int = 0,
              ignore_eos: bool = False, prefill_chunk: int = 128, max_batch_tokens: int | None = None,
              max_seqs: int | None = None, max_context: int = 0, eos_token_ids=None,
-             run_ahead: bool = True) -> GenerationResult:
+             run_ahead: bool = True, on_token=None) -> GenerationResult:
     """Generate up to ``max_tokens`` tokens after each prompt (lists of token ids).
 
     An end-of-sequence token ends a request and is not part of its output, as in the
@@ -57,7 +57,10 @@ def generate(engine, prompts: list, *, max_tokens: int = 256, temperature: float
     it, so the host's work for a step (scheduling, tables, launch) hides behind the GPU's work
     on the step before.  A request that turns out to have ended (end-of-sequence) has then
     been given one step too many; that step's token is dropped and its cache position is
-    never read."""
+    never read.
+
+    ``on_token(i, token)`` is called for every token of prompt ``i`` as soon as the host has
+    it (the reference's ``--stream`` prints pieces at that moment, src/bin/infer.rs:177-185)."""
     if max_tokens <= 0 or prefill_chunk <= 0:
         raise ValueError("max_tokens and prefill_chunk must be positive")
     n = len(prompts)
@@ -137,6 +140,8 @@ def generate(engine, prompts: list, *, max_tokens: int = 256, temperature: float
                 first_done += 1
             out[i].append(tok)
             known[i].append(tok)
+            if on_token is not None:
+                on_token(i, tok)
             if len(out[i]) >= max_tokens:
                 done[i] = True
                 sched.finish(rids[i])

@@ -184,6 +184,9 @@ def test_python_entry_point_and_command_line(workdir):
     assert [r["tokens"] for r in report["runs"]] == [want, want]
     assert report["prompt_ids"] == p and report["runs"][0]["generated_tokens"] == 5
     assert subprocess.run(cmd[:-2] + ["--runs", "0"], capture_output=True).returncode != 0
+    # --stream: the timed runs' ids on standard output as they come, and no report there
+    streamed = subprocess.run(cmd[:-2] + ["--stream"], capture_output=True, text=True, timeout=300, check=True).stdout
+    assert [[int(t) for t in line.split()] for line in streamed.strip().splitlines()] == [want, want]
 
 
 def test_refusals(workdir):
