@@ -970,11 +970,12 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
     if (tid == 0) p.counters[seq * p.nkv + kvh] = 0;   // zero again for the next launch
 }
 
-// out[row] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the splits, in split order.
+// out[row] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the splits, in split order, for the rows from
+// first_row on that the grid covers (the other rows of the step belong to another call).
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       __nv_bfloat16* __restrict__ out, int rows, int hd, int n_splits) {
+                                       __nv_bfloat16* __restrict__ out, int rows, int hd, int n_splits, int first_row) {
     allow_dependents();
-    const int row = blockIdx.x;
+    const int row = first_row + blockIdx.x;
     float M = -INFINITY;
     for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((size_t)z * rows + row) * 2]);
     float L = 0.f;
@@ -1158,8 +1159,13 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
                                 void* out, float* part_o, float* part_ml, unsigned int* counters, int n_seqs, int n_tokens, int n_tiles,
                                 int nq, int nkv, int hd, int window, float scale, int n_splits, int max_q_len,
                                 int pool_pages, const void* qkv, int qkv_stride, const float* q_norm, const float* k_norm,
-                                float eps, const float* cos_sin, int write_kv, int* status, void* stream) {
+                                float eps, const float* cos_sin, int write_kv, int first_token, int run_tokens, int* status,
+                                void* stream) {
     if (n_tokens == 0) return 0;
+    // first_token, run_tokens: the tokens of the sequences given here (a step's sequences may be given in several
+    // calls, each with a run of them; q, out and the partial sums are those of the whole step)
+    RMX_REQUIRE(first_token >= 0 && run_tokens > 0 && first_token + run_tokens <= n_tokens, "attention_flash: tokens %d + %d of %d",
+                first_token, run_tokens, n_tokens);
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_flash: %d query heads over %d kv heads", nq, nkv);
     const int group = nq / nkv;
     RMX_REQUIRE(rmx_attention_flash_supports(hd, group), "attention_flash: head_dim %d with group %d is not built", hd, group);
@@ -1214,7 +1220,8 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     }
     if (rc != 0) return rc;
     if (n_splits > 1) {
-        attention_merge_kernel<<<n_tokens * nq, hd >= 128 ? 128 : 64, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, n_tokens * nq, hd, n_splits);
+        attention_merge_kernel<<<run_tokens * nq, hd >= 128 ? 128 : 64, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, n_tokens * nq, hd, n_splits,
+                                                                                first_token * nq);
         RMX_CHECK_LAUNCH("attention_merge");
     }
     return 0;

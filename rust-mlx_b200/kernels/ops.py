@@ -451,7 +451,7 @@ def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
         c_int(getattr(batch, "max_q_len", 0)), c_int(k_pool.shape[0] if use_tma else 0),
         _ptr(qkv, torch.bfloat16, "qkv"), c_int(qkv.stride(0) if qkv is not None else 0), _ptr(q_norm, torch.float32, "q_norm"),
         _ptr(k_norm, torch.float32, "k_norm"), c_float(eps), _ptr(cos_sin, torch.float32, "cos_sin"), c_int(1 if write_kv else 0),
-        _ptr(batch.status, torch.int32, "status"), _stream()))
+        c_int(starts[0]), c_int(starts[batch.n_seqs] - starts[0]), _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched(2 if n_splits > 1 else 1)
 
 

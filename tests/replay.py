@@ -87,6 +87,32 @@ def mixed(requests: dict, live: int = 4, sizes=(5, 1, 9, 2, 1, 1, 6, 3, 1, 1, 1,
     return steps
 
 
+def random_cuts(requests: dict, seed: int, live: int = 4, largest: int = 300) -> list:
+    """Up to ``live`` requests at a time, every step a random choice of them (at least one), each with a
+    portion of random size: mostly single tokens and small portions, now and then one of up to ``largest``."""
+    rng = np.random.RandomState(seed)
+    waiting = list(requests.items())
+    running = []  # [rid, toks, at]
+    steps = []
+    while waiting or running:
+        while waiting and len(running) < live:
+            rid, toks = waiting.pop(0)
+            running.append([rid, toks, 0])
+        chosen = [r for r in running if rng.rand() < 0.7] or [running[rng.randint(len(running))]]
+        entries, end = [], []
+        for r in chosen:
+            kind = rng.rand()
+            c = 1 if kind < 0.4 else int(rng.randint(2, 20)) if kind < 0.75 else int(rng.randint(20, largest + 1))
+            c = min(c, len(r[1]) - r[2])
+            entries.append({"id": r[0], "tokens": r[1][r[2]:r[2] + c], "want": list(range(c))})
+            r[2] += c
+            if r[2] == len(r[1]):
+                end.append(r[0])
+        running = [r for r in running if r[2] < len(r[1])]
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+    return steps
+
+
 def tokens_needed(steps: list, page: int = 64) -> int:
     """The most tokens live requests hold at any time, each rounded up to ``page``."""
     held, peak = {}, 0

@@ -612,6 +612,35 @@ def test_attention_tcgen05_over_pages(nq, nkv, page, window, per_block, runs):
         at += c
 
 
+@pytest.mark.parametrize("nq, nkv, hd", [(6, 2, 64), (8, 2, 64), (6, 2, 128), (8, 2, 128)])
+@pytest.mark.parametrize("lengths, new", [([644, 1], [196, 1]), ([1, 644], [1, 196]), ([39, 39, 288], [1, 1, 12]),
+                                          ([288, 39, 39], [12, 1, 1]), ([700, 50], [196, 2]), ([298, 63, 5], [150, 1, 5])])
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_of_a_mixed_step_in_two_launches(nq, nkv, hd, lengths, new, window):
+    """``ops.attention`` gives the decoded tokens of a mixed step to the key-split kernel and the portions to
+    the kernel for portions, each launch with a run of the step's sequences; q, the output and the partial sums
+    of split keys are the whole step's.  Long contexts, so that keys are split and the shares have to be added
+    for the launch's own rows only (the other rows belong to the other launch)."""
+    from rust_mlx_b200.engine.workspace import Workspace
+    k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, 32, torch.bfloat16, seed=hd + nq)
+    torch.manual_seed(len(lengths) + window)
+    qs = [torch.randn(c, nq, hd).to(torch.bfloat16) for c in new]
+    q = torch.cat(qs).to(DEV).reshape(-1, nq * hd)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    batch = _Batch(lengths, new, status)
+    batch.seq_lens_host, batch.per_step = list(lengths), {}
+    out = torch.full_like(q, float("nan"))
+    ops().attention(q, k_pool, v_pool, batch, table, 32, out, nq, nkv, hd, window, hd ** -0.5, workspace=Workspace(DEV))
+    assert status.item() == 0
+    at = 0
+    for s, (n, c) in enumerate(zip(lengths, new)):
+        want = plain_attention(qs[s], ks[s], vs[s], torch.arange(n - c, n), window, hd ** -0.5)
+        got = out[at:at + c].double().cpu().reshape(c, nq, hd)
+        assert not torch.isnan(got).any(), (s, n, c)
+        assert ((got - want).abs() <= 1e-2 * (1 + want.abs())).all(), (s, n, c, (got - want).abs().max().item())
+        at += c
+
+
 @pytest.mark.parametrize("page, window, runs", [(8, 0, 1), (8, 600, 3), (16, 1000, 1), (8, 0, 4)])
 def test_attention_tcgen05_walks_long_block_tables(page, window, runs):
     """Block tables of some hundred entries (the copying warp keeps a run of them in registers and moves on
