@@ -54,6 +54,31 @@ def test_bfloat16_greedy_follows_the_plain_bfloat16_restatement(workdir):
             ids.append(t)
 
 
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_bfloat16_generation_at_real_head_sizes(workdir, name):
+    """Heads of 64 and of 128 in bfloat16 through ``generate``: decode steps are captured graphs (batch sizes
+    that change as requests end), the decoding attention splits the keys of the longer requests and, with heads
+    of 128, norms and rotates its own token; every chosen token must be (nearly) the plain argmax given the
+    same history, and generation in lockstep without graphs must choose the same tokens."""
+    raw, page = tiny.CONFIGS[name]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=21))
+    ps = tiny.prompts(raw["vocab_size"], [300, 5, 129, 64, 230], seed=9)
+    pm = plain.PlainModel(folder, rounding="bfloat16")
+    eng = engine(folder, "bfloat16", page, tokens=4096)
+    limits = [24, 9, 17, 30, 12]
+    got = [None] * len(ps)
+    r = eng.generate(ps, max_tokens=max(limits), prefill_chunk=96, ignore_eos=True)
+    for i, (p, g) in enumerate(zip(ps, r)):
+        ids = list(p)
+        for t in g[:limits[i]]:
+            logits = pm.logits(ids)[-1]
+            assert logits[t] >= logits.max() - 4e-2, (name, i, len(ids))
+            ids.append(t)
+    graphs, eng.graphs = eng.graphs, None
+    assert eng.generate(ps, max_tokens=max(limits), prefill_chunk=96, ignore_eos=True, run_ahead=False) == r
+    eng.graphs = graphs
+
+
 def test_long_decoding_and_the_first_tokens(workdir):
     """200 decoded tokens across many page edges, teacher-forced against the plain logits, and
     the very first positions of a sequence (one token, two tokens)."""
@@ -164,6 +189,32 @@ def test_pages_run_out_during_generation_requests_are_computed_again(workdir):
     assert r.tokens == want
     assert r.preemptions > 0
     assert eng.pools.table.live() == 0 and eng.pools.table.free_pages(0) == 7
+
+
+@pytest.mark.parametrize("name, seed", [("A", 1), ("A", 2), ("B", 3), ("B", 4)])
+def test_random_workloads_through_the_scheduler(workdir, name, seed):
+    """A dozen requests of random lengths through ``generate`` with random portions, budgets and seats, in a
+    cache too small for all of them (so that requests wait, are preempted and computed again), running a step
+    ahead and in lockstep: in float32 every request's greedy tokens are the plain implementation's."""
+    import random
+    rng = random.Random(seed)
+    raw, page = tiny.CONFIGS[name]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=40 + seed))
+    lengths = [rng.choice([1, 2, 3, 7, 16, 17, 31, 40, 64, 65, 90]) for _ in range(12)]
+    ps = tiny.prompts(raw["vocab_size"], lengths, seed=seed)
+    n = rng.randint(3, 20)
+    pm = plain.PlainModel(folder)
+    want = [pm.greedy(p, n) for p in ps]
+    longest = -(-(max(lengths) + n) // page) * page
+    for run_ahead in (True, False):
+        tokens = longest + rng.randint(1, 6) * page                 # room for the longest request and a little more
+        eng = engine(folder, "float32", page, tokens=tokens, requests=rng.randint(2, 6))
+        chunk = rng.choice([1, 3, 8, 32, 200])
+        r = eng.generate_detailed(ps, max_tokens=n, prefill_chunk=chunk, max_batch_tokens=rng.choice([None, chunk + 4]),
+                                  run_ahead=run_ahead)
+        assert r.tokens == want, (run_ahead, tokens, chunk)
+        eng.pools.table.check()
+        assert eng.pools.table.live() == 0 and eng.pools.table.free_pages(0) == eng.pools.num_pages
 
 
 def test_python_entry_point_and_command_line(workdir):
