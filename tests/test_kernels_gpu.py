@@ -520,6 +520,39 @@ def test_attention_flash_decoding_arrangement(nq, nkv, hd, page, window, new_len
         at += c
 
 
+@pytest.mark.parametrize("hd, window", [(128, 0), (64, 0), (128, 30000)])
+def test_decoding_attention_over_a_very_long_context(hd, window):
+    """One decoded token of one request against 70,000 keys: the rule then splits the keys more than eight
+    ways (no cluster is that large: the shares go through global memory and the last block adds them), and
+    the block table (more than a thousand pages) is longer than what a block keeps of it in shared memory.
+    A needle far back: one key that the query is scaled to find."""
+    from rust_mlx_b200.engine.workspace import Workspace
+    nq, nkv, page, n = 8, 2, 64, 70000
+    assert ops().flash_splits(1, nkv, n) > 8
+    k_pool, v_pool, table, ks, vs = paged_setup([n, 40], nkv, hd, page, torch.bfloat16, seed=hd)
+    torch.manual_seed(1)
+    needle = 41234
+    qs = [torch.randn(1, nq, hd).to(torch.bfloat16), torch.randn(1, nq, hd).to(torch.bfloat16)]
+    qs[0][0, :, 7] = 30.0
+    k_pool[table[0, needle // page].item(), :, needle % page, :] = 0
+    k_pool[table[0, needle // page].item(), :, needle % page, 7] = 30.0
+    ks[0][needle] = 0
+    ks[0][needle, :, 7] = 30.0
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for lengths, new, which in (([n], [1], [0]), ([n, 40], [1, 1], [0, 1])):
+        q = torch.cat([qs[i] for i in which]).to(DEV).reshape(-1, nq * hd)
+        out = torch.full_like(q, float("nan"))
+        ops().attention_flash(q, k_pool, v_pool, _Batch(lengths, new, status), table[:len(lengths)], page, out, nq, nkv, hd, window,
+                              hd ** -0.5, Workspace(DEV))
+        assert status.item() == 0
+        for row, i in enumerate(which):
+            want = plain_attention(qs[i], ks[i], vs[i], torch.tensor([lengths[row] - 1]), window, hd ** -0.5)
+            got = out[row].double().cpu().reshape(1, nq, hd)
+            assert ((got - want).abs() <= 1e-2 * (1 + want.abs())).all(), (lengths, i, (got - want).abs().max().item())
+        if window == 0:   # the needle was found: the first request's output is its value
+            assert (out[0].float().cpu().reshape(nq, hd) - vs[0][needle].float().repeat_interleave(nq // nkv, 0)).abs().max() < 3e-2
+
+
 @pytest.mark.parametrize("m, n, k, splits", [
     (1, 128, 64, 1), (16, 128, 128, 1), (1, 6144, 4096, None), (8, 4096, 4096, 4), (8, 24576, 4096, None),
     (3, 509, 96, 1), (17, 1000, 136, 2), (33, 4096, 12288, None), (64, 2048, 4096, 1), (64, 1100, 520, 3),
@@ -612,7 +645,7 @@ def test_attention_tcgen05_over_pages(nq, nkv, page, window, per_block, runs):
         at += c
 
 
-@pytest.mark.parametrize("nq, nkv, hd", [(6, 2, 64), (8, 2, 64), (6, 2, 128), (8, 2, 128)])
+@pytest.mark.parametrize("nq, nkv, hd", [(6, 2, 64), (8, 2, 64), (6, 2, 128), (8, 2, 128), (6, 2, 32), (4, 2, 96), (4, 4, 16)])
 @pytest.mark.parametrize("lengths, new", [([644, 1], [196, 1]), ([1, 644], [1, 196]), ([39, 39, 288], [1, 1, 12]),
                                           ([288, 39, 39], [12, 1, 1]), ([700, 50], [196, 2]), ([298, 63, 5], [150, 1, 5])])
 @pytest.mark.parametrize("window", [0, 70])
