@@ -3,6 +3,8 @@
 // The residual stream is float32 in every run; activations that kernels hand to one
 // another are in the compute type T (float or bfloat16).  Sums of squares, rsqrt and the
 // scaling are done in float and rounded once.
+#include <type_traits>
+
 #include "common.cuh"
 
 // Four consecutive numbers as floats (the address is 16-byte aligned for float, 8 for bfloat16).
@@ -183,7 +185,11 @@ template <typename T>
 int launch_add_rmsnorm(float* h, const T* delta, const int* rows, const float* w, float eps, T* x, int n_rows, int width,
                        int write_h, cudaStream_t s) {
     const int groups = width / 4;
-    if ((width & 3) == 0 && groups <= 1024 && n_rows <= 256) {
+    // Which arrangement runs decides the order in which a row's squares are added.  In the 32-bit path that order
+    // may depend on the width only (the same bits however a step is cut), so the number of rows chooses between
+    // the arrangements for bfloat16 alone.
+    const bool by_rows = !std::is_same<T, float>::value;
+    if ((width & 3) == 0 && groups <= 1024 && (n_rows <= 256 || !by_rows)) {
         // few rows (decoding): as many threads as the row has groups of four, so that a row's latency is one load
         const int threads = (groups + 31) / 32 * 32;
         RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, s, h, delta, rows, w, eps,

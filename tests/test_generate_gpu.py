@@ -54,7 +54,7 @@ def test_bfloat16_greedy_follows_the_plain_bfloat16_restatement(workdir):
             ids.append(t)
 
 
-@pytest.mark.parametrize("name", ["C", "D"])
+@pytest.mark.parametrize("name", ["C", "D", "E"])
 def test_bfloat16_generation_at_real_head_sizes(workdir, name):
     """Heads of 64 and of 128 in bfloat16 through ``generate``: decode steps are captured graphs (batch sizes
     that change as requests end), the decoding attention splits the keys of the longer requests and, with heads
@@ -66,8 +66,10 @@ def test_bfloat16_generation_at_real_head_sizes(workdir, name):
     pm = plain.PlainModel(folder, rounding="bfloat16")
     eng = engine(folder, "bfloat16", page, tokens=4096)
     limits = [24, 9, 17, 30, 12]
-    got = [None] * len(ps)
+    # a short request first: its decode graph points into a workspace that the longer prompts then outgrow
+    first = eng.generate([ps[1]], max_tokens=4, ignore_eos=True)[0]
     r = eng.generate(ps, max_tokens=max(limits), prefill_chunk=96, ignore_eos=True)
+    assert r[1][:4] == first
     for i, (p, g) in enumerate(zip(ps, r)):
         ids = list(p)
         for t in g[:limits[i]]:

@@ -85,7 +85,7 @@ def test_heads_finished_in_the_products_epilogue(workdir, way, monkeypatch):
         assert tiny.max_abs(got[rid], ref[rid]) < TOL["bfloat16"], (way, rid)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_float32_ways_agree_bit_for_bit(workdir, name):
     raw, page, folder, reqs, ref = cached_setup(workdir, name, "float32")
     results = []
@@ -104,7 +104,7 @@ LONG = [700, 333, 1100, 64, 257, 5]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name, seed", [("C", 1), ("C", 2), ("D", 3), ("B", 4)])
+@pytest.mark.parametrize("name, seed", [("C", 1), ("C", 2), ("D", 3), ("B", 4), ("E", 5), ("E", 6)])
 def test_random_cuts_of_long_requests(workdir, name, seed, dtype):
     """Requests of up to 1,100 tokens (many key tiles, block tables of dozens of pages) cut at random: single
     tokens, small portions and portions of some hundred tokens of up to four requests in a step, a request
@@ -114,21 +114,30 @@ def test_random_cuts_of_long_requests(workdir, name, seed, dtype):
     lies 0.04 to 0.08 from the exact logits itself (measured here, per request), so two bfloat16 evaluations
     of the same formulas cannot be asked to agree to 2e-2 in every one of half a million logits: the engine
     must be as close to the restatement as the restatement is to the exact values (and to 2e-2 where that is
-    more).  A wrong, stale or missing key moves logits by 0.5 and more (the weights are sharpened)."""
+    more).  A wrong, stale or missing key moves logits by 0.5 and more (the weights are sharpened).
+
+    In float32 the random cuts must give the bits that each request gives alone and whole; against the plain
+    implementation (float64) the bound is 1e-4 here: reductions over up to 1,100 keys and three layers of them
+    (unit roundoff 6e-8, times the square root of the terms, times some thirty reductions in a row, times what
+    sharpened weights and norms amplify), where a product in reduced precision would show as 1e-3."""
     raw, page = tiny.CONFIGS[name]
     folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=30 + seed, store="float32"))
     reqs = {f"q{i}": p for i, p in enumerate(tiny.prompts(raw["vocab_size"], LONG, seed=seed))}
     pm = plain.PlainModel(folder, rounding=None if dtype == "float32" else "bfloat16")
     exact = plain.PlainModel(folder)
     steps = replay.random_cuts(reqs, seed)
-    assert max(len(e["tokens"]) for s in steps for e in s["entries"]) > 128 and max(len(s["entries"]) for s in steps) == 4
+    assert max(len(e["tokens"]) for s in steps for e in s["entries"]) > 128 and max(len(s["entries"]) for s in steps) >= 3
     eng = engine_for(folder, dtype, page, replay.tokens_needed(steps, page))
     got = replay.run_engine(eng, steps)
     eng.pools.table.check()
     assert eng.pools.table.live() == 0
+    if dtype == "float32":
+        alone = replay.run_engine(engine_for(folder, dtype, page, max(-(-n // page) * page for n in LONG)), replay.whole(reqs))
+        for rid in reqs:
+            assert torch.equal(got[rid], alone[rid]), rid
     for rid, toks in reqs.items():
         want = pm.logits(toks)
-        bound = TOL[dtype] if dtype == "float32" else max(TOL[dtype], tiny.max_abs(want.float(), exact.logits(toks).float()))
+        bound = 1e-4 if dtype == "float32" else max(TOL[dtype], tiny.max_abs(want.float(), exact.logits(toks).float()))
         assert tiny.max_abs(got[rid], want.float()) < bound, (rid, len(toks), bound)
 
 

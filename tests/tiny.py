@@ -39,7 +39,16 @@ TINY_D = dict(
     rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
 PAGE_D = 64
 
-CONFIGS = {"A": (TINY_A, PAGE_A), "B": (TINY_B, PAGE_B), "C": (TINY_C, PAGE_C), "D": (TINY_D, PAGE_D)}
+# E: head 128 with a window and small pages (four copies a key tile, pages handed back while a prompt runs), group 2
+TINY_E = dict(
+    model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, hidden_size=192,
+    num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=320, vocab_size=411,
+    rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=4096,
+    use_sliding_window=True, sliding_window=100, max_window_layers=1)
+PAGE_E = 16
+
+CONFIGS = {"A": (TINY_A, PAGE_A), "B": (TINY_B, PAGE_B), "C": (TINY_C, PAGE_C), "D": (TINY_D, PAGE_D),
+           "E": (TINY_E, PAGE_E)}
 
 
 def make_folder(tmp_path, raw: dict, seed: int = 0, store: str = "float32") -> str:
