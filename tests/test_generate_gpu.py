@@ -193,7 +193,7 @@ def test_pages_run_out_during_generation_requests_are_computed_again(workdir):
     assert eng.pools.table.live() == 0 and eng.pools.table.free_pages(0) == 7
 
 
-@pytest.mark.parametrize("name, seed", [("A", 1), ("A", 2), ("B", 3), ("B", 4)])
+@pytest.mark.parametrize("name, seed", [("A", 1), ("A", 2), ("B", 3), ("B", 4), ("C", 5), ("E", 6)])
 def test_random_workloads_through_the_scheduler(workdir, name, seed):
     """A dozen requests of random lengths through ``generate`` with random portions, budgets and seats, in a
     cache too small for all of them (so that requests wait, are preempted and computed again), running a step
