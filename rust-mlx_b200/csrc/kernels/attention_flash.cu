@@ -492,9 +492,14 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
     // (the matching wait stands before the first store into another block's shared memory: every block of the
     // cluster has started by then)
     if (KEYSPLIT && p.cluster) asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-    // everything above needs nothing from the kernels before this one; queries, keys and tables do
+    // Everything above needs nothing from the kernels before this one; the queries do, and so do the keys and
+    // values of the step's own tokens where a kernel before this one stores them.  A kernel that finishes the
+    // projection itself (FINISH) stores its token's key and value itself and patches them into the tile it
+    // fetched: whatever else it reads of the pools was written by earlier steps, and the step's tables and
+    // positions were uploaded before the step's first kernel.  So there only the warps that read the projection
+    // wait, and the producer's copies of keys and values run while the kernel before this one still ends.
     allow_dependents();
-    wait_for_prior_kernels();
+    if (!FINISH) wait_for_prior_kernels();
     int seq, tok0, n_tok, pos0;
     if constexpr (KEYSPLIT) {   // one tile per sequence
         seq = blockIdx.x;
@@ -564,6 +569,7 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
     bool have_new = false;
     if (warp < NWARPS) {
         if constexpr (FINISH) {
+            wait_for_prior_kernels();
             // one token a sequence: its `group` query heads are the tile's rows; a warp takes a head at a time
             const __nv_bfloat16* row = p.qkv + (size_t)tok0 * p.qkv_stride;
             const float* cs = p.cos_sin + (size_t)tok0 * 128;
