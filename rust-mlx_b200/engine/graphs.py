@@ -11,6 +11,8 @@ Graphs are dropped when a workspace buffer they point into is reallocated.
 """
 from __future__ import annotations
 
+import gc
+
 import torch
 
 from .batch import BatchLayout, check_sequences
@@ -108,6 +110,12 @@ class DecodeGraphs:
         torch.cuda.synchronize()
         cap.generation = e.workspace.generation
         e.workspace.frozen = True
+        # While a stream is being captured nothing may free pinned memory, events or graphs: the collector
+        # could do just that in the middle of the capture if it found an engine that is no longer used (its
+        # staging buffers and graphs) and so make the capture invalid.  It runs now and rests meanwhile.
+        collecting = gc.isenabled()
+        gc.collect()
+        gc.disable()
         try:
             before = e.ops.launch_count
             graph = torch.cuda.CUDAGraph()
@@ -115,6 +123,8 @@ class DecodeGraphs:
                 self._step(cap)
             e._launches_per_graph[key] = e.ops.launch_count - before
         finally:
+            if collecting:
+                gc.enable()
             e.workspace.frozen = False
         cap.graph = graph
         self.graphs[key] = cap

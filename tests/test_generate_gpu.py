@@ -81,6 +81,34 @@ def test_bfloat16_generation_at_real_head_sizes(workdir, name):
     eng.graphs = graphs
 
 
+def test_graph_capture_is_not_disturbed_by_the_collector(workdir):
+    """Garbage that holds pinned memory and events (what an engine that is no longer used leaves behind) and a
+    collector set to run at every opportunity: freeing such things while a decode step is being captured would
+    make the capture invalid, so the capture collects first and keeps the collector off meanwhile."""
+    import gc
+    raw, page = tiny.CONFIGS["D"]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=21))
+    ps = tiny.prompts(raw["vocab_size"], [40, 70, 9], seed=2)
+    eng = engine(folder, "bfloat16", page, tokens=1024)
+
+    class Holder:
+        pass
+    for _ in range(64):
+        h = Holder()
+        h.me, h.buf, h.event = h, torch.empty(4096, dtype=torch.int32, pin_memory=True), torch.cuda.Event()
+    del h
+    old = gc.get_threshold()
+    gc.set_threshold(1, 1, 1)
+    try:
+        got = eng.generate(ps, max_tokens=6, ignore_eos=True)
+    finally:
+        gc.set_threshold(*old)
+    assert eng.graphs is not None and eng.graphs.captures > 0
+    graphs, eng.graphs = eng.graphs, None
+    assert eng.generate(ps, max_tokens=6, ignore_eos=True, run_ahead=False) == got
+    eng.graphs = graphs
+
+
 def test_long_decoding_and_the_first_tokens(workdir):
     """200 decoded tokens across many page edges, teacher-forced against the plain logits, and
     the very first positions of a sequence (one token, two tokens)."""
