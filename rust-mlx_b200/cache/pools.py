@@ -100,6 +100,16 @@ class CachePools:
             grp.state[:, slot].zero_()
         return slot
 
+    def reset_state(self, slots: list) -> None:
+        """The fixed-size state of ``slots`` starts from zero (on the current stream).  Whoever admits requests
+        without ``open`` (the scheduler takes slots from the page table itself) calls this for every request whose
+        first tokens are about to run."""
+        if not slots or not self.state_groups:
+            return
+        index = torch.tensor(slots, dtype=torch.long, device=self.state_groups[0].state.device)
+        for grp in self.state_groups:
+            grp.state.index_fill_(1, index, 0)
+
     def view(self, cache_id: int, batch, read_only: bool):
         g, i = self._where[cache_id]
         grp = self.groups[g]

@@ -97,22 +97,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
-// What the third epilogue needs: the product is the fused q/k/v projection of a model whose heads have 128
-// numbers, so a tile of 128 weight rows is one head.  See qk_rope_cache.cu for the formulas.
-struct HeadsEpilogue {
-    const float* q_norm;         // [128] or null
-    const float* k_norm;         // [128] or null
-    const float* cos_sin;        // [M][rotary_dim]: cosines then sines of every token's angles
-    const int* positions;        // [M]
-    const int* seq_index;        // [M]
-    const int* block_table;      // [seqs, table_stride]
-    __nv_bfloat16* k_pool;       // [pages, nkv, page_size, 128]
-    __nv_bfloat16* v_pool;
-    __nv_bfloat16* q_out;        // [M, nq, 128]
-    float eps;
-    int rotary_dim, table_stride, page_size, nq, nkv, write_kv;
-};
-
 struct GemmParams {
     void* c;                 // [M, ldc] bfloat16 or float
     float* partial;          // [splits, MPAD, n_tiles * 128] floats (splits > 1)
@@ -122,9 +106,6 @@ struct GemmParams {
     int dependent;           // launched as a programmatic dependent: wait for the grid before before reading A
     int epilogue;            // 0: C = product.  1: the tile's rows are 64 gate rows then their 64 up rows;
                              //    C[M, N / 2] = silu(gate) * up, formed in float and rounded once.
-                             // 2: the tile is a head of the q/k/v projection: q heads are normed, rotated and
-                             //    written to heads.q_out, k heads likewise into the pages, v heads copied there
-    HeadsEpilogue heads;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -144,8 +125,7 @@ __device__ __forceinline__ void st_cluster(float* local, uint32_t rank, float v)
 
 // CLUSTER: the slices of K of one tile form a thread-block cluster (grid.y == cluster size == splits); they
 // hand their partial sums to the first block through distributed shared memory, no global scratch.
-// HEADS: built with the q/k/v heads epilogue (p.epilogue == 2); the other builds carry none of its code.
-template <int MPAD, int STAGES, bool CLUSTER, bool HEADS>
+template <int MPAD, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_constant__ CUtensorMap map_w,
                                                               const __grid_constant__ CUtensorMap map_a,
                                                               const GemmParams p) {
@@ -158,7 +138,6 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
     __shared__ uint32_t tmem_base_smem;
     __shared__ int s_failed, s_last;
-    __shared__ long long s_dst_row[HEADS ? MPAD : 1];   // epilogue 2: the row of the pool that token t's key or value goes to
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x, split = blockIdx.y;
@@ -208,15 +187,6 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
             tma_load_2d(dst, &map_w, &full_bar[s], k0, tile * TILE_N);
             tma_load_2d(dst + W_BYTES, &map_a, &full_bar[s], k0, 0);
         }
-    } else if (HEADS && warp == 3 && tile >= p.heads.nq) {
-        // ---- meanwhile: where the tokens' keys or values go (the step's tables were written before the kernels of
-        // the step began, so they may be read without waiting for the kernel before this one)
-        for (int t = lane; t < p.M; t += 32) {
-            const int pos = p.heads.positions[t];
-            const int page = p.heads.block_table[(size_t)p.heads.seq_index[t] * p.heads.table_stride + pos / p.heads.page_size];
-            const int kvh = (tile - p.heads.nq) % p.heads.nkv;
-            s_dst_row[t] = page < 0 ? -1 : ((long long)page * p.heads.nkv + kvh) * p.heads.page_size + pos % p.heads.page_size;
-        }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer
         const uint32_t idesc = umma_idesc(MPAD);
@@ -258,7 +228,7 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_acc), "r"(TMEM_COLS));
     const bool failed = s_failed != 0;
     if (failed && tid == 0) atomicExch(p.status, 3);
-    if (!CLUSTER && failed) return;   // (inside a cluster a block that failed still joins the barriers below)
+    // (a block that failed still joins the cluster's barriers, or the tile's counter, below)
 
     if constexpr (CLUSTER) {
         // every block's MMAs are done (its shared-memory stages are free); the slices hand their sums to the
@@ -287,9 +257,13 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
             if (t < p.M) mine[(size_t)t * ldp + n] = acc[t];
         __threadfence();
         __syncthreads();
-        if (tid == 0) s_last = atomicAdd(&p.counters[tile], 1u) == (unsigned)p.splits - 1;
+        // a block that gave up still counts, so that the counter is zero again for the next launch
+        if (tid == 0) {
+            s_last = atomicAdd(&p.counters[tile], 1u) == (unsigned)p.splits - 1;
+            if (s_last) p.counters[tile] = 0;
+        }
         __syncthreads();
-        if (!s_last) return;
+        if (!s_last || failed) return;
         __threadfence();
 #pragma unroll
         for (int t = 0; t < MPAD; ++t) acc[t] = 0.f;
@@ -299,84 +273,7 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
             for (int t = 0; t < MPAD; ++t)
                 if (t < p.M) acc[t] += __ldcg(src + (size_t)t * ldp + n);
         }
-        if (tid == 0) p.counters[tile] = 0;  // ready for the next launch
-    }
-    if constexpr (HEADS) {
-        // One head: thread tid holds number tid of the head for every token.  The product is rounded to bfloat16
-        // first, as the separate kernel would read it; the norm and the rotation are float; one rounding at the end.
-        const HeadsEpilogue& h = p.heads;
-        const bool is_q = tile < h.nq, is_v = tile >= h.nq + h.nkv;
-        if (!is_q && !h.write_kv) return;
-        float* sums = reinterpret_cast<float*>(tiles);            // [4 warps][MPAD]
-        float* xs = sums + 4 * MPAD;                              // [MPAD][128]
-        if (CLUSTER) __syncthreads();                             // the first block has read the other slices' sums from there
-#pragma unroll
-        for (int t = 0; t < MPAD; ++t) acc[t] = __bfloat162float(__float2bfloat16_rn(acc[t]));
-        const float* w = is_q ? h.q_norm : h.k_norm;
-        if (!is_v && w) {
-            const float wj = w[tid];
-#pragma unroll
-            for (int t = 0; t < MPAD; ++t) {
-                if (t < p.M) {
-                    const float ss = warp_sum(acc[t] * acc[t]);
-                    if (lane == 0) sums[warp * MPAD + t] = ss;
-                }
-            }
-            __syncthreads();
-#pragma unroll
-            for (int t = 0; t < MPAD; ++t) {
-                if (t < p.M) {
-                    const float ss = sums[t] + sums[MPAD + t] + sums[2 * MPAD + t] + sums[3 * MPAD + t];
-                    acc[t] = acc[t] * rsqrtf(ss / (float)TILE_N + h.eps) * wj;
-                }
-            }
-        }
-        const int half = h.rotary_dim >> 1;
-        if (!is_v && half > 0) {
-            // (the cosines and sines are asked for before the barrier: their way from L2 is not waited for after it)
-            const bool low = tid < half;
-            const int j = low ? tid : tid - half, partner = low ? tid + half : tid - half;
-            constexpr int EARLY = MPAD <= 16 ? MPAD : 1;   // with few rows there are registers to spare for this
-            float cs[EARLY], sn[EARLY];
-#pragma unroll
-            for (int t = 0; t < MPAD; ++t) {
-                xs[t * TILE_N + tid] = acc[t];
-                if (MPAD <= 16 && t < p.M && tid < h.rotary_dim) {
-                    cs[t % EARLY] = h.cos_sin[(size_t)t * h.rotary_dim + j];
-                    sn[t % EARLY] = h.cos_sin[(size_t)t * h.rotary_dim + half + j];
-                }
-            }
-            __syncthreads();
-            if (tid < h.rotary_dim) {
-#pragma unroll
-                for (int t = 0; t < MPAD; ++t) {
-                    if (t < p.M) {
-                        const float c = MPAD <= 16 ? cs[t % EARLY] : h.cos_sin[(size_t)t * h.rotary_dim + j];
-                        const float s_ = MPAD <= 16 ? sn[t % EARLY] : h.cos_sin[(size_t)t * h.rotary_dim + half + j];
-                        const float other = xs[t * TILE_N + partner];
-                        acc[t] = low ? acc[t] * c - other * s_ : acc[t] * c + other * s_;
-                    }
-                }
-            }
-        }
-        if (is_q) {
-#pragma unroll
-            for (int t = 0; t < MPAD; ++t)
-                if (t < p.M) h.q_out[((size_t)t * h.nq + tile) * TILE_N + tid] = __float2bfloat16_rn(acc[t]);
-        } else {
-            __nv_bfloat16* pool = is_v ? h.v_pool : h.k_pool;
-#pragma unroll
-            for (int t = 0; t < MPAD; ++t) {
-                if (t < p.M) {
-                    const long long row = s_dst_row[t];
-                    if (row < 0) {  // the host reserves pages before the step; never write through a hole
-                        if (tid == 0) atomicExch(p.status, 1);
-                    } else {
-                        pool[(size_t)row * TILE_N + tid] = __float2bfloat16_rn(acc[t]);
-                    }
-                }
-            }
-        }
+    } else if (failed) {
         return;
     }
     if (p.epilogue == 1) {
@@ -484,14 +381,17 @@ int encode_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, i
     return 0;
 }
 
-template <int MPAD, int STAGES, bool CLUSTER, bool HEADS>
+template <int MPAD, int STAGES, bool CLUSTER>
 int launch_as(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int n_tiles, bool dependent, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * (TILE_N * TILE_K * 2 + MPAD * TILE_K * 2) + 1024;
-    static bool raised = false;
-    if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_swapab_kernel<MPAD, STAGES, CLUSTER, HEADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // a function's attributes are kept per device: raise the limit once on each
+    static bool raised[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) RMX_FAIL("gemm_tcgen05: no current device");
+    if (!raised[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_swapab_kernel<MPAD, STAGES, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RMX_FAIL("gemm_tcgen05: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-        raised = true;
+        raised[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_tiles, p.splits);
@@ -516,7 +416,7 @@ int launch_as(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p,
     cfg.numAttrs = n_attrs;
     GemmParams q = p;
     q.dependent = dependent ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_swapab_kernel<MPAD, STAGES, CLUSTER, HEADS>, mw, ma, q);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_swapab_kernel<MPAD, STAGES, CLUSTER>, mw, ma, q);
     if (e != cudaSuccess) RMX_FAIL("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
@@ -525,12 +425,8 @@ int launch_as(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p,
 template <int MPAD, int STAGES>
 int launch(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p, int n_tiles, cudaStream_t s,
            bool cluster = false, bool dependent = false) {
-    if (p.epilogue == 2) {
-        if (cluster) return launch_as<MPAD, STAGES, true, true>(mw, ma, p, n_tiles, dependent, s);
-        return launch_as<MPAD, STAGES, false, true>(mw, ma, p, n_tiles, dependent, s);
-    }
-    if (cluster) return launch_as<MPAD, STAGES, true, false>(mw, ma, p, n_tiles, dependent, s);
-    return launch_as<MPAD, STAGES, false, false>(mw, ma, p, n_tiles, dependent, s);
+    if (cluster) return launch_as<MPAD, STAGES, true>(mw, ma, p, n_tiles, dependent, s);
+    return launch_as<MPAD, STAGES, false>(mw, ma, p, n_tiles, dependent, s);
 }
 }  // namespace
 
@@ -546,7 +442,7 @@ RMX_API long long rmx_gemm_tcgen05_scratch_floats(int M, int N, int splits) {
 namespace {
 int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
                      int out_float, int splits, float* partial, unsigned int* counters, int* status,
-                     int flags, const HeadsEpilogue* heads, cudaStream_t s) {
+                     int flags, cudaStream_t s) {
     if (M == 0 || N == 0) return 0;
     RMX_REQUIRE(rmx_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05: M=%d N=%d K=%d is outside 1..64 rows, K %% 8 == 0", M, N, K);
     RMX_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0,
@@ -560,7 +456,7 @@ int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K,
     const bool fits = (size_t)(splits - 1) * mpad * TILE_N * 4 <= (size_t)stages * (TILE_N * TILE_K * 2 + mpad * TILE_K * 2);
     const bool cluster = (flags & 1) && splits >= 2 && splits <= 8 && fits;
     const bool dependent = (flags & 2) != 0;
-    const int epilogue = heads ? 2 : ((flags & 4) ? 1 : 0);   // flags: 4 = SwiGLU over blocks of 64 gate rows and 64 up rows
+    const int epilogue = (flags & 4) ? 1 : 0;   // flags: 4 = SwiGLU over blocks of 64 gate rows and 64 up rows
     RMX_REQUIRE(epilogue != 1 || N % 128 == 0, "gemm_tcgen05: the SwiGLU epilogue needs N to be a multiple of 128, got %d", N);
     RMX_REQUIRE(splits == 1 || cluster || (partial && counters), "gemm_tcgen05: split-K needs scratch");
     CUtensorMap mw, ma;
@@ -570,8 +466,6 @@ int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K,
     p.c = C; p.partial = partial; p.counters = counters; p.status = status;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
     p.dependent = 0; p.epilogue = epilogue;
-    p.heads = HeadsEpilogue{};
-    if (heads) p.heads = *heads;
     // stages sized so that two blocks fit an SM: more blocks in flight smooth the last wave
     if (mpad == 16) return launch<16, 6>(mw, ma, p, n_tiles, s, cluster, dependent);
     if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s, cluster, dependent);
@@ -584,33 +478,7 @@ int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K,
 RMX_API int rmx_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
                              int out_float, int splits, float* partial, unsigned int* counters, int* status,
                              int flags, void* stream) {
-    return gemm_tcgen05_run(A, W, C, M, N, K, lda, ldw, ldc, out_float, splits, partial, counters, status, flags, nullptr,
-                            (cudaStream_t)stream);
-}
-
-// The fused q/k/v projection of a model with heads of 128 numbers, with what follows it done in the epilogue:
-// W is [(nq + 2 nkv) * 128, K] (q heads, k heads, v heads); per token, q heads are normed (q_norm, k_norm: float
-// [128] or null), rotated (cos_sin: [M][rotary_dim], cosines then sines, as rope_table makes them) and written to
-// q_out [M, nq, 128]; k heads likewise and v heads as they are into the pools' pages (page = block_table[seq_index[t],
-// positions[t] / page_size]; write_kv = 0 leaves the pools alone).  No [M, N] product is written.
-RMX_API int rmx_gemm_tcgen05_qkv_heads(const void* A, const void* W, int M, int K, int lda, int ldw, int nq, int nkv,
-                                       const float* q_norm, const float* k_norm, float eps, const float* cos_sin,
-                                       int rotary_dim, const int* positions, const int* seq_index, const int* block_table,
-                                       int table_stride, int page_size, void* k_pool, void* v_pool, void* q_out,
-                                       int write_kv, int splits, float* partial, unsigned int* counters, int* status,
-                                       int flags, void* stream) {
-    RMX_REQUIRE(nq > 0 && nkv > 0 && rotary_dim >= 0 && rotary_dim <= TILE_N && rotary_dim % 2 == 0 && page_size > 0 && table_stride > 0,
-                "gemm_tcgen05_qkv_heads: bad geometry (rotary_dim %d, page size %d)", rotary_dim, page_size);
-    RMX_REQUIRE(positions && seq_index && block_table && q_out && (rotary_dim == 0 || cos_sin) && (!write_kv || (k_pool && v_pool)),
-                "gemm_tcgen05_qkv_heads: a needed pointer is null");
-    HeadsEpilogue h;
-    h.q_norm = q_norm; h.k_norm = k_norm; h.cos_sin = cos_sin; h.positions = positions; h.seq_index = seq_index;
-    h.block_table = block_table; h.k_pool = (__nv_bfloat16*)k_pool; h.v_pool = (__nv_bfloat16*)v_pool;
-    h.q_out = (__nv_bfloat16*)q_out; h.eps = eps; h.rotary_dim = rotary_dim; h.table_stride = table_stride;
-    h.page_size = page_size; h.nq = nq; h.nkv = nkv; h.write_kv = write_kv;
-    const int N = (nq + 2 * nkv) * TILE_N;
-    return gemm_tcgen05_run(A, W, q_out, M, N, K, lda, ldw, N, 0, splits, partial, counters, status, flags & ~4, &h,
-                            (cudaStream_t)stream);
+    return gemm_tcgen05_run(A, W, C, M, N, K, lda, ldw, ldc, out_float, splits, partial, counters, status, flags, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -672,7 +540,10 @@ RMX_API int rmx_gemm_tcgen05_static(const void* A, const void* W, void* C, int M
         const long long room = RMX_STATIC_SCRATCH_FLOATS / ((long long)mpad * n_tiles * TILE_N);
         long long pick = room;
         if (pick > k_blocks / 8) pick = k_blocks / 8;
-        if (pick > 296 / n_tiles) pick = 296 / n_tiles;
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            RMX_FAIL("gemm_tcgen05_static: the device's SM count cannot be read");
+        if (pick > 2 * sms / n_tiles) pick = 2 * sms / n_tiles;   // two blocks fit an SM
         splits = pick < 1 ? 1 : (int)pick;
     }
     RMX_REQUIRE(splits >= 1 && splits <= k_blocks && splits <= 65535, "gemm_tcgen05_static: %d splits for %d k-blocks", splits, k_blocks);
@@ -694,7 +565,6 @@ RMX_API int rmx_gemm_tcgen05_static(const void* A, const void* W, void* C, int M
     p.c = C; p.partial = scratch.partial; p.counters = scratch.counters; p.status = scratch.status;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
     p.dependent = 0; p.epilogue = 0;
-    p.heads = HeadsEpilogue{};
     if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s);
     if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s);
     return launch<64, 4>(mw, ma, p, n_tiles, s);

@@ -87,7 +87,7 @@ class BatchLayout:
     def fill(self, buf: np.ndarray, seqs: list, pools, vocab_size: int, temperatures=None, uniforms=None) -> dict:
         """Write the arrays of ``seqs`` into ``buf`` (int32, ``total`` long); returns host-side facts."""
         counts = [len(s.tokens) for s in seqs]
-        if self.n_tokens == self.n_seqs == self.n_rows and max(counts) == 1:
+        if self.n_tokens == self.n_seqs == self.n_rows and max(counts) == 1 and all(s.want == [0] for s in seqs):
             return self._fill_decode(buf, seqs, pools, vocab_size, temperatures, uniforms)
         q_start, rows = [0], []
         for s, c in zip(seqs, counts):

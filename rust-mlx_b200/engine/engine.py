@@ -98,7 +98,8 @@ class Engine:
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # the token the last sampling chose for the request in each state slot: a decode step launched before the
         # host has read the step before takes its ids from here
-        self.last_tokens = torch.zeros(max_requests, dtype=torch.int32, device=self.device)
+        # (one word more than there are slots: the spare places of a padded decode graph leave their choice there)
+        self.last_tokens = torch.zeros(max_requests + 1, dtype=torch.int32, device=self.device)
         # the longest sequence a request may reach: the cache's size, the model's stated limit, or the caller's
         limit = self.pools.num_pages * page_size
         stated = getattr(self.config, "max_position_embeddings", 0) or 0

@@ -75,8 +75,12 @@ def generate(engine, prompts: list, *, max_tokens: int = 256, temperature: float
             raise ValueError("token outside vocabulary")
     max_seqs = max_seqs or min(engine.pools.max_requests, max(n, 1))
     budget = max_batch_tokens or max(prefill_chunk, max_seqs)
+    # the scheduler refuses at ``add`` what the engine could not hold later: the caller's limit or the engine's own
+    # (its graphs' block tables are made for that many positions; the last generated token is never fed, so a
+    # request may count one token more than the cache ever holds of it), whichever is smaller
+    limit = min(x for x in (max_context, engine.max_context + 1) if x > 0)
     sched = Scheduler(engine.pools.table, max_seqs=max_seqs, max_batch_tokens=budget, prefill_chunk=prefill_chunk,
-                      max_context=max_context)
+                      max_context=limit)
     rids = [engine._rid(("generate", id(sched), i)) for i in range(n)]
     index = {rid: i for i, rid in enumerate(rids)}
     known = [list(p) for p in prompts]      # token ids the host knows
@@ -94,6 +98,9 @@ def generate(engine, prompts: list, *, max_tokens: int = 256, temperature: float
         """Build the batch of ``entries`` and put it on the stream; the tokens travel to pinned memory behind it."""
         t0 = time.perf_counter()
         seqs, wanting = [], []
+        # a portion that starts at position 0 belongs to a request that was just admitted (or admitted again after
+        # it had stepped back): the scheduler gave it a slot, whose fixed-size state starts from zero
+        engine.pools.reset_state([engine.pools.table.slot(e.req) for e in entries if e.start == 0])
         for e in entries:
             i = index[e.req]
             from_last = owed[i] > 0 and e.start + e.count > len(known[i])

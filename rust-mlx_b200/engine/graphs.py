@@ -19,8 +19,8 @@ from .batch import BatchLayout, check_sequences
 
 
 # Batch sizes that graphs exist for: a step of n sequences runs in the next size up, the spare
-# places repeating the first sequence (the same token to the same position: the same numbers
-# are written twice and the spare results are ignored).  At most half as many places again.
+# places repeating the first sequence (the same token to the same position, sampled with the same
+# numbers: the same values are written twice and the spare results are ignored).  At most half as many places again.
 _BUCKETS = [1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512]
 
 
@@ -53,11 +53,14 @@ class DecodeGraphs:
         real ones); the caller copies it to the host."""
         e = self.engine
         check_sequences(seqs)
+        n_real = len(seqs)
         spare = min(bucket(len(seqs)), e.pools.max_requests + len(seqs)) - len(seqs)
         if spare > 0:
             seqs = list(seqs) + [seqs[0]] * spare
-            temperatures = list(temperatures) + [0.0] * spare if temperatures is not None else None
-            uniforms = list(uniforms) + [0.0] * spare if uniforms is not None else None
+            # a spare place samples with the first sequence's own numbers and leaves its choice in the scrap word
+            # after the last state slot, never in the first sequence's word of ``last_tokens``
+            temperatures = list(temperatures) + [temperatures[0]] * spare if temperatures is not None else None
+            uniforms = list(uniforms) + [uniforms[0]] * spare if uniforms is not None else None
         n = len(seqs)
         longest = max(s.start + 1 for s in seqs)
         if longest > e.max_context:
@@ -69,13 +72,14 @@ class DecodeGraphs:
             del self.graphs[key]
             cap = None
         if cap is None:
-            cap = self._capture(seqs, temperatures, uniforms, key)
+            cap = self._capture(seqs, temperatures, uniforms, key, n_real)
         # staging buffers take turns, so that a caller who does not wait for each step's result
         # never overwrites numbers whose copy to the device is still to come
         cap.turn = (cap.turn + 1) % len(cap.hosts)
         host, event = cap.hosts[cap.turn], cap.events[cap.turn]
         event.synchronize()
         facts = cap.layout.fill(host.numpy(), seqs, e.pools, e.vocab_size, temperatures, uniforms)
+        cap.layout.part(host.numpy(), 10)[n_real:] = e.pools.max_requests
         cap.batch.max_seq_len = facts["max_seq_len"]
         cap.dev.copy_(host, non_blocking=True)
         event.record()
@@ -84,7 +88,7 @@ class DecodeGraphs:
         e.ops.count_launches(e._launches_per_graph.get(key, 0))
         return cap.result
 
-    def _capture(self, seqs, temperatures, uniforms, key) -> _Captured:
+    def _capture(self, seqs, temperatures, uniforms, key, n_real=None) -> _Captured:
         e = self.engine
         n = len(seqs)
         if len(self.graphs) >= self.max_graphs:
@@ -97,6 +101,7 @@ class DecodeGraphs:
         cap.dev = torch.zeros(cap.layout.total, dtype=torch.int32, device=e.device)
         cap.result = torch.zeros(n + 1, dtype=torch.int32, device=e.device)
         facts = cap.layout.fill(cap.hosts[0].numpy(), seqs, e.pools, e.vocab_size, temperatures, uniforms)
+        cap.layout.part(cap.hosts[0].numpy(), 10)[n if n_real is None else n_real:] = e.pools.max_requests
         cap.dev.copy_(cap.hosts[0], non_blocking=True)
         cap.events[0].record()
         cap.batch = cap.layout.views(cap.dev, e._status, facts)

@@ -535,50 +535,6 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
     return status
 
 
-# The q/k/v product of few rows can norm, rotate and store its heads in its epilogue (``gemm_qkv_heads``).
-# Measured at Qwen3-8B sizes it ties with the library's product followed by the separate kernel (within 1 %
-# either way between batch 1 and 16: the library's product is a little faster than this package's at that shape
-# and the separate kernel hides behind it as a programmatic dependent), so it is off unless switched on.
-fused_qkv_heads = False
-
-
-def qkv_heads_supported(m: int, hd: int, rotary_dim: int, dtype, cos_sin) -> bool:
-    """The tcgen05 product can finish the q/k/v projection itself when a head is one tile of 128 weight rows."""
-    return (fused_qkv_heads and tcgen05_policy != "none" and dtype == torch.bfloat16 and hd == 128 and 1 <= m <= 16
-            and rotary_dim % 2 == 0 and (rotary_dim == 0 or cos_sin is not None))
-
-
-def gemm_qkv_heads(x, w_qkv, q_norm, k_norm, eps, cos_sin, rotary_dim, positions, seq_index, block_table, page_size,
-                   k_pool, v_pool, q_out, nq, nkv, write_kv, workspace=None, status=None, dependent=False):
-    """q/k/v projection of up to 64 rows on the tcgen05 tensor cores with per-head RMSNorm, rotation and the write
-    of q rows and of keys and values into their pages done in the product's epilogue (heads of 128 numbers)."""
-    lib = kernels_library()
-    m, k = x.shape
-    n = w_qkv.shape[0]
-    if n != (nq + 2 * nkv) * 128 or w_qkv.shape[1] != k or x.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16:
-        raise KernelError(f"gemm_qkv_heads: {tuple(x.shape)} x {tuple(w_qkv.shape)}^T with {nq}+2*{nkv} heads of 128")
-    if q_out.shape != (m, nq * 128) or q_out.dtype != torch.bfloat16 or not q_out.is_contiguous():
-        raise KernelError("gemm_qkv_heads: q_out must be contiguous bfloat16 [rows, nq * 128]")
-    ws = workspace if workspace is not None else _own_workspace()
-    splits = min(tcgen05_splits(m, n, k), 8 if m <= 32 else 4)
-    partial = counters = None
-    if splits > 1:   # (taken only where the slices' sums do not fit a cluster's shared memory)
-        partial = ws.get("gemm_partial", (lib.rmx_gemm_tcgen05_scratch_floats(c_int(m), c_int(n), c_int(splits)),), torch.float32)
-        counters = ws.get_zeroed("gemm_counters", (max(4096, -(-n // 128)),), torch.int32)
-    if status is None:
-        status = ws.get_zeroed("gemm_status", (1,), torch.int32)
-    check(lib.rmx_gemm_tcgen05_qkv_heads(
-        _ptr(x, name="x"), _ptr(w_qkv, name="w_qkv"), c_int(m), c_int(k), c_int(x.stride(0)), c_int(w_qkv.stride(0)),
-        c_int(nq), c_int(nkv), _ptr(q_norm, torch.float32, "q_norm"), _ptr(k_norm, torch.float32, "k_norm"), c_float(eps),
-        _ptr(cos_sin, torch.float32, "cos_sin"), c_int(rotary_dim), _ptr(positions, torch.int32, "positions"),
-        _ptr(seq_index, torch.int32, "seq_index"), _ptr(block_table, torch.int32, "block_table"),
-        c_int(block_table.shape[1]), c_int(page_size), _ptr(k_pool, torch.bfloat16, "k_pool"),
-        _ptr(v_pool, torch.bfloat16, "v_pool"), _ptr(q_out, torch.bfloat16, "q_out"), c_int(1 if write_kv else 0),
-        c_int(splits), _ptr(partial), _ptr(counters), _ptr(status, torch.int32, "status"),
-        c_int(1 | (2 if dependent else 0)), _stream()))
-    _launched()
-
-
 fused_swiglu = True   # the gate/up product of few rows forms silu(gate) * up in its epilogue
 
 

@@ -66,23 +66,16 @@ class AttentionMixer(Mixer):
         q = ws.get("q_rot", (n, nq * hd), dt)
         angles = self.position.angles(batch)
         projection = None
-        if ops.qkv_heads_supported(n, hd, self.position.rotary_dim, dt, angles):
-            # few rows: the product norms, rotates and stores its heads itself
-            ops.gemm_qkv_heads(x, self.w_qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, angles,
-                               self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
-                               cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, not cache.read_only, ws,
-                               batch.status, dependent=ops.dependent_launch)
+        qkv = ws.get("qkv", (n, (nq + 2 * nkv) * hd), dt)
+        ops.linear(x, self.w_qkv, qkv, ws, batch.status)
+        if ops.decode_takes_projection(batch, dt, hd, nq // nkv, cache.page_size, self.position.rotary_dim, angles):
+            # decoding: the attention kernel norms, rotates and stores its own token while it waits for its keys
+            projection = (qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, angles, not cache.read_only)
         else:
-            qkv = ws.get("qkv", (n, (nq + 2 * nkv) * hd), dt)
-            ops.linear(x, self.w_qkv, qkv, ws, batch.status)
-            if ops.decode_takes_projection(batch, dt, hd, nq // nkv, cache.page_size, self.position.rotary_dim, angles):
-                # decoding: the attention kernel norms, rotates and stores its own token while it waits for its keys
-                projection = (qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, angles, not cache.read_only)
-            else:
-                ops.qk_rope_cache(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.position.inv_freq,
-                                  self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
-                                  cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, hd, not cache.read_only,
-                                  batch.status, angles)
+            ops.qk_rope_cache(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.position.inv_freq,
+                              self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
+                              cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, hd, not cache.read_only,
+                              batch.status, angles)
         o = ws.get("attn_out", (n, nq * hd), dt)
         ops.attention(q, cache.k_pool, cache.v_pool, batch, cache.block_table, cache.page_size, o, nq, nkv, hd,
                       cache.window, self.scale, ws, projection=projection)

@@ -2,7 +2,7 @@
 12288, vocabulary 151936), two layers, random weights: the kernels at the sizes they serve.
 
 float32: logits equal the plain implementation's (run here in float64 on the GPU, with the same
-weights), and are bit-identical whole, in portions and mixed.  bfloat16: every way of cutting stays
+weights), and are bit-identical whole, with the last 32 tokens one by one, in portions and mixed.  bfloat16: every way of cutting stays
 within the bfloat16 tolerance of the plain implementation's bfloat16 restatement.
 """
 import pytest
@@ -37,7 +37,7 @@ def engine_and_weights(dtype, tokens):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_layer_sizes_of_qwen3_8b(dtype):
     reqs = {f"r{i}": p for i, p in enumerate(tiny.prompts(SHAPE_8B["vocab_size"], LENGTHS, seed=3))}
-    steps_by_way = {w: getattr(replay, w)(reqs) for w in ("whole", "portions", "mixed")}
+    steps_by_way = {w: getattr(replay, w)(reqs) for w in ("whole", "tail_one_by_one", "portions", "mixed")}
     eng, tensors = engine_and_weights(dtype, 1024)
     rounding = "bfloat16" if dtype == "bfloat16" else None
     w = {k: v.to(torch.float64) for k, v in tensors.items()}
@@ -59,6 +59,6 @@ def test_layer_sizes_of_qwen3_8b(dtype):
             assert tiny.max_abs(got[rid], ref[rid]) < tol * max(1.0, scale), (way, rid)
         results[way] = got
     if dtype == "float32":
-        for way in ("portions", "mixed"):
+        for way in ("tail_one_by_one", "portions", "mixed"):
             for rid in reqs:
                 assert torch.equal(results[way][rid], results["whole"][rid]), (way, rid)

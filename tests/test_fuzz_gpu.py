@@ -104,7 +104,7 @@ def test_replay_of_random_requests_cut_at_random(workdir, seed):
     implementation restated with bfloat16 roundings as that restatement is to the exact logits (at least 2e-2)."""
     from rust_mlx_b200.engine import Engine
     rng = random.Random(seed)
-    name = rng.choice(["A", "B", "C", "D", "E"])
+    name = rng.choice(["A", "B", "Bw", "C", "D", "E"])
     raw, page = tiny.CONFIGS[name]
     sub = workdir / str(seed)
     sub.mkdir()

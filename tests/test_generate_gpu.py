@@ -131,7 +131,7 @@ def test_long_decoding_and_the_first_tokens(workdir):
 
 
 def test_long_greedy_generation_with_a_window(workdir):
-    raw, page = tiny.CONFIGS["B"]
+    raw, page = tiny.CONFIGS["Bw"]
     folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=12))
     p = tiny.prompts(raw["vocab_size"], [30], seed=2)[0]
     want = plain.PlainModel(folder).greedy(p, 60)
@@ -208,6 +208,91 @@ def test_temperature_sampling_is_seeded_and_independent_of_the_batch(workdir):
     assert mixed[0] == greedy[0] and mixed[2] == greedy[2] and mixed[1] == a[1]
 
 
+@pytest.mark.parametrize("n_prompts", [5, 7])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_sampling_at_batch_sizes_between_graph_sizes(workdir, n_prompts, dtype):
+    """Five and seven requests decode in graphs made for six and eight: the spare places repeat the first request.
+    A spare place must not leave a token of its own where the first request's next step looks for its id, so
+    running a step ahead, in lockstep, with and without graphs all draw the same tokens; in float32 every drawn
+    token is the inverse-CDF choice of the plain softmax for the same uniform number."""
+    from rust_mlx_b200.sampling import uniform
+    raw, page = tiny.CONFIGS["D"]
+    folder = tiny.make_folder(workdir, raw, seed=17)
+    ps = tiny.prompts(raw["vocab_size"], [9, 30, 3, 17, 65, 12, 40][:n_prompts], seed=3)
+    eng = engine(folder, dtype, page, tokens=2048)
+    opts = dict(max_tokens=14, temperature=0.8, seed=9, ignore_eos=True)
+    a = eng.generate(ps, run_ahead=True, **opts)
+    assert eng.graphs is not None and eng.graphs.replays > 0
+    assert any(k[0] == n_prompts + 1 for k in eng.graphs.graphs)   # the padded size was used
+    b = eng.generate(ps, run_ahead=False, **opts)
+    graphs, eng.graphs = eng.graphs, None
+    c = eng.generate(ps, run_ahead=True, **opts)
+    d = eng.generate(ps, run_ahead=False, **opts)
+    eng.graphs = graphs
+    assert a == b == c == d
+    assert len({tuple(t) for t in a}) > 1 and a != eng.generate(ps, **dict(opts, temperature=0.0))
+    if dtype == "float32":
+        pm = plain.PlainModel(folder)
+        for i in (0, 1, n_prompts - 1):
+            ids = list(ps[i])
+            for step, t in enumerate(a[i]):
+                cdf = torch.cumsum(torch.softmax(pm.logits(ids)[-1] / 0.8, -1), 0)
+                u = uniform(9, i, step)
+                lo = cdf[t - 1].item() if t > 0 else 0.0
+                assert lo - 1e-4 <= u <= cdf[t].item() + 1e-4, (i, step)
+                ids.append(t)
+
+
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_forty_requests_decode_together(workdir, name):
+    """Forty live requests: decode graphs of 48 places and fewer as requests end, products of 17 to 64 rows
+    (the tcgen05 product's wider tiles or the library's product), decoding attention that does not split its
+    keys.  float32: the plain implementation's greedy tokens; bfloat16, with graphs and in lockstep without:
+    every chosen token is (nearly) the argmax of the plain bfloat16 restatement given the same history."""
+    import random
+    rng = random.Random(5)
+    raw, page = tiny.CONFIGS[name]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=23))
+    lengths = [rng.choice([3, 9, 17, 33, 64, 65, 100]) for _ in range(40)]
+    ps = tiny.prompts(raw["vocab_size"], lengths, seed=6)
+    limits = [rng.randint(4, 12) for _ in range(40)]
+    pm = plain.PlainModel(folder)
+    want = [pm.greedy(p, n) for p, n in zip(ps, limits)]
+    eng = engine(folder, "float32", page, tokens=40 * 128, requests=48)
+    got = eng.generate(ps, max_tokens=12, prefill_chunk=256, max_batch_tokens=512, ignore_eos=True)
+    assert [g[:n] for g, n in zip(got, limits)] == want
+    assert max(k[0] for k in eng.graphs.graphs) >= 40
+    eng16 = engine(folder, "bfloat16", page, tokens=40 * 128, requests=48)
+    got16 = eng16.generate(ps, max_tokens=12, prefill_chunk=256, max_batch_tokens=512, ignore_eos=True)
+    assert max(k[0] for k in eng16.graphs.graphs) >= 40
+    graphs, eng16.graphs = eng16.graphs, None
+    plain16 = eng16.generate(ps, max_tokens=12, prefill_chunk=256, max_batch_tokens=512, ignore_eos=True, run_ahead=False)
+    eng16.graphs = graphs
+    pm16 = plain.PlainModel(folder, rounding="bfloat16")
+    for i in range(0, 40, 3):
+        for out in (got16, plain16):
+            ids = list(ps[i])
+            for t in out[i][:limits[i]]:
+                logits = pm16.logits(ids)[-1]
+                assert logits[t] >= logits.max() - 4e-2, (name, i, len(ids))
+                ids.append(t)
+
+
+def test_a_request_beyond_the_engines_context_is_refused_at_once(workdir):
+    """``generate`` hands the engine's own context limit to the scheduler: a request that would outgrow it is
+    refused before anything runs, not in the middle of generation."""
+    from rust_mlx_b200.engine import Engine
+    from rust_mlx_b200.engine.scheduler import RequestRejected
+    raw, page = tiny.CONFIGS["A"]
+    folder = tiny.make_folder(workdir, raw, seed=11)
+    eng = Engine(folder, dtype="float32", max_tokens=1024, page_size=page, max_requests=4, max_context=40)
+    ps = tiny.prompts(raw["vocab_size"], [10, 30], seed=1)
+    with pytest.raises(RequestRejected):
+        eng.generate(ps, max_tokens=12)          # 30 + 12 > 40 + 1
+    assert eng.pools.table.live() == 0
+    assert len(eng.generate(ps, max_tokens=11, ignore_eos=True)[1]) == 11
+
+
 def test_pages_run_out_during_generation_requests_are_computed_again(workdir):
     raw, page = tiny.CONFIGS["A"]
     folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=11))
@@ -221,7 +306,7 @@ def test_pages_run_out_during_generation_requests_are_computed_again(workdir):
     assert eng.pools.table.live() == 0 and eng.pools.table.free_pages(0) == 7
 
 
-@pytest.mark.parametrize("name, seed", [("A", 1), ("A", 2), ("B", 3), ("B", 4), ("C", 5), ("E", 6)])
+@pytest.mark.parametrize("name, seed", [("A", 1), ("A", 2), ("B", 3), ("Bw", 4), ("C", 5), ("E", 6)])
 def test_random_workloads_through_the_scheduler(workdir, name, seed):
     """A dozen requests of random lengths through ``generate`` with random portions, budgets and seats, in a
     cache too small for all of them (so that requests wait, are preempted and computed again), running a step

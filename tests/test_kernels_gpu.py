@@ -720,67 +720,6 @@ def test_attention_tcgen05_finds_a_far_key_and_respects_the_window_edge():
     assert status.item() == 0
 
 
-@pytest.mark.parametrize("m, nq, nkv, k, rot, page, norm, write_kv", [
-    (1, 4, 2, 320, 128, 16, True, True), (5, 6, 1, 1032, 64, 8, True, True), (16, 3, 3, 256, 128, 64, False, True),
-    (9, 8, 2, 4096, 0, 32, True, True), (40, 5, 1, 520, 96, 16, True, True), (64, 2, 2, 200, 128, 4, True, True),
-    (7, 4, 2, 320, 128, 16, True, False)])
-def test_gemm_qkv_heads_finishes_the_projection_like_the_separate_kernels(m, nq, nkv, k, rot, page, norm, write_kv):
-    """The q/k/v product whose epilogue norms, rotates and stores heads of 128, against the plain product
-    followed by the separate kernel (same formulas, float, one rounding): q rows and the written slots of the
-    pages agree to a last bit of bfloat16; pages that no token of the step falls into stay as they were."""
-    hd = 128
-    torch.manual_seed(m * 7 + k)
-    lengths = [max(m // 3, 1) + 17, 90, m - 2 * max(m // 3, 1) + 30] if m >= 3 else [33]
-    new = [max(m // 3, 1), max(m // 3, 1), m - 2 * max(m // 3, 1)] if m >= 3 else [m]
-    n_pages = sum(-(-n // page) for n in lengths) + 2
-    table = torch.full((len(lengths), max(-(-n // page) for n in lengths)), -1, dtype=torch.int32)
-    perm = torch.randperm(n_pages).tolist()
-    for s, n in enumerate(lengths):
-        for i in range(-(-n // page)):
-            table[s, i] = perm.pop()
-    pos, sidx = [], []
-    for s, (n, c) in enumerate(zip(lengths, new)):
-        pos += list(range(n - c, n))
-        sidx += [s] * c
-    positions = torch.tensor(pos, dtype=torch.int32, device=DEV)
-    seq_index = torch.tensor(sidx, dtype=torch.int32, device=DEV)
-    table_dev = table.to(DEV)
-    x = rnd((m, k), torch.bfloat16, 1.0, 5)
-    w = rnd(((nq + 2 * nkv) * hd, k), torch.bfloat16, k ** -0.5, 6)
-    qn = (1 + 0.2 * torch.randn(hd)).to(DEV) if norm else None
-    kn = (1 + 0.2 * torch.randn(hd)).to(DEV) if norm else None
-    eps = 1e-6
-    inv_freq = (1e4 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(rot, 1))).float().to(DEV) if rot else None
-    angles = None
-    if rot:
-        angles = torch.empty(m, rot, device=DEV)
-        ops().rope_table(positions, inv_freq, rot, angles)
-    status = torch.zeros(1, dtype=torch.int32, device=DEV)
-
-    def pools():
-        return (torch.full((n_pages, nkv, page, hd), 7.0, dtype=torch.bfloat16, device=DEV),
-                torch.full((n_pages, nkv, page, hd), -3.0, dtype=torch.bfloat16, device=DEV))
-    k1, v1 = pools()
-    qkv = torch.empty(m, w.shape[0], dtype=torch.bfloat16, device=DEV)
-    ops().gemm_tcgen05(x, w, qkv)
-    q1 = torch.empty(m, nq * hd, dtype=torch.bfloat16, device=DEV)
-    ops().qk_rope_cache(qkv, qn, kn, eps, inv_freq, rot, positions, seq_index, table_dev, page, k1, v1, q1, nq, nkv, hd,
-                        write_kv, status, cos_sin=angles)
-    k2, v2 = pools()
-    q2 = torch.full_like(q1, float("nan"))
-    ops().gemm_qkv_heads(x, w, qn, kn, eps, angles, rot, positions, seq_index, table_dev, page, k2, v2, q2, nq, nkv,
-                         write_kv, status=status)
-    assert status.item() == 0
-
-    def close(a, b):   # a last bit of bfloat16 (the sums of squares are added in another order)
-        a, b = a.double(), b.double()
-        return bool(((a - b).abs() <= 2 ** -7 * torch.maximum(a.abs(), b.abs()) + 1e-6).all())
-    assert close(q1, q2) and close(k1, k2) and torch.equal(v1, v2)
-    assert (q1 == q2).double().mean().item() > 0.98
-    if not write_kv:
-        assert torch.equal(k2, pools()[0]) and torch.equal(v2, pools()[1])
-
-
 @pytest.mark.parametrize("nq, nkv, page, norm, write_kv", [(32, 8, 64, True, True), (5, 3, 16, True, True), (4, 4, 8, False, True),
                                                            (6, 2, 32, True, False)])
 def test_qk_rope_cache_for_prompt_portions_agrees_with_the_general_kernel(nq, nkv, page, norm, write_kv):

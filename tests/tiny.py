@@ -2,8 +2,8 @@
 
 A and B differ in every size and option: layers, width, head counts and group size,
 head_dim (A: heads * head_dim equals the width, B: it does not), feed-forward width,
-vocabulary (B: odd), rope_theta, eps, tied or untied head, page size, and B's upper
-layers attend through a sliding window.
+vocabulary (B: odd), rope_theta, eps, tied or untied head, page size.  "Bw" is B with a
+sliding window in its upper layers.
 """
 import os
 import random
@@ -19,9 +19,10 @@ PAGE_A = 16
 TINY_B = dict(
     model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, hidden_size=96,
     num_attention_heads=6, num_key_value_heads=2, head_dim=32, intermediate_size=160, vocab_size=509,
-    rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=4096,
-    use_sliding_window=True, sliding_window=20, max_window_layers=1)
+    rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=4096)
 PAGE_B = 8
+# B with a window of 20 keys in layers 1 and 2 (layer 0 attends to everything)
+TINY_BW = dict(TINY_B, use_sliding_window=True, sliding_window=20, max_window_layers=1)
 
 # C and D have the head sizes of real checkpoints, so that the engine's bfloat16 replay goes through the kernels
 # that serve them (TMA-fed attention at 64 and 128, tcgen05 prompt attention at 128, the tcgen05 products):
@@ -47,7 +48,7 @@ TINY_E = dict(
     use_sliding_window=True, sliding_window=100, max_window_layers=1)
 PAGE_E = 16
 
-CONFIGS = {"A": (TINY_A, PAGE_A), "B": (TINY_B, PAGE_B), "C": (TINY_C, PAGE_C), "D": (TINY_D, PAGE_D),
+CONFIGS = {"A": (TINY_A, PAGE_A), "B": (TINY_B, PAGE_B), "Bw": (TINY_BW, PAGE_B), "C": (TINY_C, PAGE_C), "D": (TINY_D, PAGE_D),
            "E": (TINY_E, PAGE_E)}
 
 
