@@ -64,12 +64,17 @@ class Qwen3Config(ModelConfig):
             p.append("rms_norm_eps must be positive")
         if not (self.rope_theta > 0):
             p.append("rope_theta must be positive")
-        if self.attention_bias:
-            p.append("attention_bias is true: projections with a bias are not supported")
-        if self.rope_scaling is not None:
-            kind = self.rope_scaling.get("rope_type", self.rope_scaling.get("type"))
-            if kind not in (None, "default"):
-                p.append(f"rope_scaling of type '{kind}' is not supported")
+        scaling = self.rope_scaling_parameters()
+        if scaling is not None:
+            kind = scaling.get("rope_type", scaling.get("type"))
+            if kind not in (None, "default", "linear", "yarn"):
+                p.append(f"rope_scaling of type '{kind}' is not supported (default, linear, yarn)")
+            elif kind in ("linear", "yarn"):
+                factor = scaling.get("factor")
+                if isinstance(factor, bool) or not isinstance(factor, (int, float)) or factor < 1:
+                    p.append("rope_scaling needs a factor of at least 1")
+                if kind == "yarn" and not (scaling.get("original_max_position_embeddings") or 0) > 0:
+                    p.append("rope_scaling of type 'yarn' needs original_max_position_embeddings")
         if self.use_sliding_window:
             if self.sliding_window <= 0:
                 p.append("use_sliding_window is true but sliding_window is not a positive number")
@@ -80,6 +85,22 @@ class Qwen3Config(ModelConfig):
                 if bad:
                     p.append(f"unknown layer_types {bad}")
         return p
+
+    def rope_scaling_parameters(self):
+        """The dictionary that scales the rotation, or None: ``rope_scaling``, else ``rope_parameters`` when that
+        names a ``rope_type`` (newer checkpoints keep theta and the scaling together there).  A yarn dictionary
+        without ``original_max_position_embeddings`` takes the configuration's ``max_position_embeddings``."""
+        found = self.rope_scaling
+        if found is None:
+            params = (getattr(self, "_raw", None) or {}).get("rope_parameters")
+            if isinstance(params, dict) and params.get("rope_type", params.get("type")) not in (None, "default"):
+                found = params
+        if found is None:
+            return None
+        found = dict(found)
+        if found.get("rope_type", found.get("type")) == "yarn" and not found.get("original_max_position_embeddings"):
+            found["original_max_position_embeddings"] = self.max_position_embeddings
+        return found
 
     def attention_kinds(self) -> tuple:
         """The mixer of every layer: 'full_attention' or 'sliding_attention'.

@@ -369,3 +369,33 @@ RMX_API int rmx_add_residual(float* h, const void* delta, int n_rows, int width,
     RMX_CHECK_LAUNCH("add_residual");
     return 0;
 }
+
+// x[t, j] = x[t, j] + bias[j] (float add, one rounding): the bias of a projection, added to the product as the
+// reference does (src/weights.rs:198-200).  `ld` is the distance between rows of x.
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, int width, int ld, size_t total) {
+    wait_for_prior_kernels();
+    allow_dependents();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t row = idx / width;
+    const int col = (int)(idx - row * width);
+    T* at = x + row * ld + col;
+    *at = from_float<T>(to_float(*at) + bias[col]);
+}
+
+RMX_API int rmx_add_bias(void* x, const float* bias, int n_rows, int width, int ld, int dtype, void* stream) {
+    if (n_rows == 0 || width == 0) return 0;
+    RMX_REQUIRE(n_rows > 0 && width > 0 && ld >= width && x && bias, "add_bias: bad sizes or a null pointer");
+    const size_t total = (size_t)n_rows * width;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(add_bias_kernel<float>, dim3(blocks), dim3(threads), 0, s, (float*)x, bias, width, ld, total), "add_bias");
+    else if (dtype == RMX_BF16)
+        RMX_CHECK_LAUNCHED(launch_dependent(add_bias_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (__nv_bfloat16*)x, bias, width, ld, total), "add_bias");
+    else
+        RMX_FAIL("add_bias: unknown dtype %d", dtype);
+    return 0;
+}

@@ -75,6 +75,7 @@ class Engine:
         self.spec = build_model_spec(self.config)
         self.workspace = Workspace(self.device)
         ctx = BuildContext(self.device, self.dtype, _ops, self.workspace)
+        self._ctx = ctx
         specs = self.spec.all_param_specs()
         if random_weights:
             tensors = random_tensors(specs, seed, self.dtype, self.device)
@@ -194,13 +195,30 @@ class Engine:
         batch.last_tokens = self.last_tokens
         h = spec.embedding.forward(batch.token_ids, batch)
         pending = None
-        for call, read_only in self._calls:
+        for index, (call, read_only) in enumerate(self._calls):
             cache = self.pools.view(call.cache, batch, read_only) if call.cache in self.pools._where else None
+            self._run_index = index
             h, pending = spec.blocks[call.layer].forward(h, pending, batch, cache)
         if batch.n_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         x = spec.final_norm.forward_rows(h, pending, batch.logit_rows)
         return spec.head.forward(x, batch)
+
+    def step_with_intermediates(self, entries: list, end=()) -> tuple:
+        """``step`` with every named intermediate tensor of every layer run copied out: returns (logits, {name:
+        tensor}) with names ``run<i>.<name>`` for the i-th entry of the schedule, rows in the order of the
+        step's tokens (what the reference's trace program compares with an oracle's dump by name,
+        src/bin/trace.rs:4-24).  The kernels are the ones ``step`` runs."""
+        taken = {}
+
+        def tap(name, tensor):
+            taken[f"run{self._run_index}.{name}"] = tensor.detach().clone()
+        self._ctx.tap = tap
+        try:
+            logits = self.step(entries, end)
+        finally:
+            self._ctx.tap = None
+        return logits, taken
 
     def generate(self, prompts: list, **options):
         """Token ids in, token ids out: see ``engine.generate.generate``.  Returns the list of

@@ -88,6 +88,16 @@ def add_residual(h, delta):
     _launched()
 
 
+def add_bias(x, bias):
+    """x[t, :] += bias in place (float add, one rounding).  ``x`` may be a view of some columns of wider rows."""
+    lib = kernels_library()
+    if x.dim() != 2 or x.stride(1) != 1 or bias.shape != (x.shape[1],) or not x.is_cuda:
+        raise KernelError("add_bias: x must be [rows, width] with unit column stride on a CUDA device, bias [width]")
+    check(lib.rmx_add_bias(c_void_p(x.data_ptr()), _ptr(bias, torch.float32, "bias"), c_int(x.shape[0]), c_int(x.shape[1]),
+                           c_int(x.stride(0)), c_int(dtype_code(x)), _stream()))
+    _launched()
+
+
 def swiglu(gate_up, out, block=0):
     """out = silu(gate) * up.  A row of ``gate_up`` is [gate | up] (block 0) or blocks of ``block``
     gate numbers each followed by its ``block`` up numbers."""

@@ -20,14 +20,14 @@ from .spec import ModelSpec, default_schedule
 
 def build_qwen3(config: Qwen3Config) -> ModelSpec:
     c = config
-    rope = RotaryEmbedding(c.head_dim, c.rope_theta)
+    rope = RotaryEmbedding(c.head_dim, c.rope_theta, scaling=c.rope_scaling_parameters())
     embedding = TokenEmbedding("model.embed_tokens.weight", c.vocab_size, c.hidden_size)
     blocks = []
     for i, kind in enumerate(c.attention_kinds()):
         p = f"model.layers.{i}"
         mixer = AttentionMixer(f"{p}.self_attn", c.hidden_size, c.num_attention_heads, c.num_key_value_heads,
                                c.head_dim, rope, qk_norm_eps=c.rms_norm_eps,
-                               window=c.sliding_window if kind == "sliding_attention" else 0)
+                               window=c.sliding_window if kind == "sliding_attention" else 0, bias=c.attention_bias)
         blocks.append(PreNormBlock(RMSNorm(f"{p}.input_layernorm.weight", c.hidden_size, c.rms_norm_eps), mixer,
                                    RMSNorm(f"{p}.post_attention_layernorm.weight", c.hidden_size, c.rms_norm_eps),
                                    SwiGLUFeedForward(f"{p}.mlp", c.hidden_size, c.intermediate_size)))

@@ -6,6 +6,9 @@ mask [+ window]) v -> output projection (src/dense.rs:139-270).  Query head i
 reads kv head i // (heads / kv_heads); scale = head_dim^-0.5 unless given.  The
 three projections are one matrix product over the concatenated weights
 [q; k; v]; each output row is the same dot product as with separate weights.
+With ``bias`` the projections take ``<prefix>.bias`` tensors, added to the rounded
+product as the reference does (src/weights.rs:96,198-200); the output
+projection's is optional in a checkpoint.
 """
 from __future__ import annotations
 
@@ -18,7 +21,8 @@ class AttentionMixer(Mixer):
     graph_safe = True
 
     def __init__(self, prefix: str, width: int, heads: int, kv_heads: int, head_dim: int, position,
-                 qk_norm_eps: float | None = None, window: int = 0, scale: float | None = None):
+                 qk_norm_eps: float | None = None, window: int = 0, scale: float | None = None,
+                 bias: bool = False):
         if heads % kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
         self.prefix, self.width = prefix, int(width)
@@ -26,8 +30,9 @@ class AttentionMixer(Mixer):
         self.position = position
         self.qk_norm_eps = qk_norm_eps
         self.window = int(window)
-        self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
-        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.scale = (float(scale) if scale is not None else self.head_dim ** -0.5) * float(getattr(position, "score_scale", 1.0))
+        self.bias = bool(bias)
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.b_qkv = self.b_o = None
 
     def children(self):
         return [self.position]
@@ -44,6 +49,11 @@ class AttentionMixer(Mixer):
         if self.qk_norm_eps is not None:
             specs += [ParamSpec(f"{p}.q_norm.weight", (hd,), "norm", "float32"),
                       ParamSpec(f"{p}.k_norm.weight", (hd,), "norm", "float32")]
+        if self.bias:
+            specs += [ParamSpec(f"{p}.q_proj.bias", (self.heads * hd,), "linear", "float32"),
+                      ParamSpec(f"{p}.k_proj.bias", (self.kv_heads * hd,), "linear", "float32"),
+                      ParamSpec(f"{p}.v_proj.bias", (self.kv_heads * hd,), "linear", "float32"),
+                      ParamSpec(f"{p}.o_proj.bias", (self.width,), "linear", "float32", optional=True)]
         return specs
 
     def bind(self, tensors, ctx):
@@ -55,6 +65,10 @@ class AttentionMixer(Mixer):
         if self.qk_norm_eps is not None:
             self.q_norm = tensors[f"{p}.q_norm.weight"].contiguous()
             self.k_norm = tensors[f"{p}.k_norm.weight"].contiguous()
+        if self.bias:
+            self.b_qkv = torch.cat([tensors.pop(f"{p}.q_proj.bias"), tensors.pop(f"{p}.k_proj.bias"),
+                                    tensors.pop(f"{p}.v_proj.bias")]).contiguous()
+            self.b_o = tensors.get(f"{p}.o_proj.bias")
 
     def linear_weights(self):
         return [self.w_qkv, self.w_o]
@@ -68,6 +82,8 @@ class AttentionMixer(Mixer):
         projection = None
         qkv = ws.get("qkv", (n, (nq + 2 * nkv) * hd), dt)
         ops.linear(x, self.w_qkv, qkv, ws, batch.status)
+        if self.b_qkv is not None:
+            ops.add_bias(qkv, self.b_qkv)
         if ops.decode_takes_projection(batch, dt, hd, nq // nkv, cache.page_size, self.position.rotary_dim, angles):
             # decoding: the attention kernel norms, rotates and stores its own token while it waits for its keys
             projection = (qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, angles, not cache.read_only)
@@ -76,9 +92,16 @@ class AttentionMixer(Mixer):
                               self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
                               cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, hd, not cache.read_only,
                               batch.status, angles)
+        tap = self.ctx.tap
+        if tap is not None and projection is None:
+            tap("q_rot", q)
         o = ws.get("attn_out", (n, nq * hd), dt)
         ops.attention(q, cache.k_pool, cache.v_pool, batch, cache.block_table, cache.page_size, o, nq, nkv, hd,
                       cache.window, self.scale, ws, projection=projection)
+        if tap is not None:
+            tap("attn_out", o)
         y = ws.get("mixer_out", (n, self.width), dt)
         ops.linear(o, self.w_o, y, ws, batch.status)
+        if self.b_o is not None:
+            ops.add_bias(y, self.b_o)
         return y

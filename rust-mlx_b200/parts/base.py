@@ -26,13 +26,17 @@ class ParamSpec:
     ``init`` names the recipe of the random-weights mode ("linear", "embedding":
     N(0, 0.02); "norm": 1 + N(0, 0.05); "zeros"; "ones").  ``keep`` says how the tensor is
     held on the device: "compute" follows the run's dtype (bfloat16 or float32),
-    "float32" stays 32-bit whatever the run's dtype, "int32" is an integer table.
+    "float32" stays 32-bit whatever the run's dtype, "int32" is an integer table.  ``optional``: a
+    checkpoint may leave the tensor out (the part then finds no entry of that name in ``bind``), as
+    the reference adds a projection's bias only where a tensor ``<prefix>.bias`` exists
+    (src/weights.rs:96); the random-weights mode always makes it.
     """
 
     name: str
     shape: tuple
     init: str = "linear"
     keep: str = "compute"
+    optional: bool = False
 
 
 @dataclass(frozen=True)
@@ -68,6 +72,11 @@ class BuildContext:
     dtype: torch.dtype
     ops: object
     workspace: object
+    # ``tap(name, tensor)``, or None: while set, parts hand it their named intermediate tensors (buffers of the
+    # workspace that later layers overwrite, so whoever listens copies).  Names a dense block gives: norm1, q_rot,
+    # attn_out, mixer_out, norm2, ffn_act, ffn_out (the reference compares such tensors by name with an oracle's
+    # dump, src/bin/trace.rs:4-24).
+    tap: object = None
 
 
 class Part:
@@ -129,6 +138,7 @@ class PositionEncoding(Part):
 
     rotary_dim: int = 0
     inv_freq: Optional[torch.Tensor] = None
+    score_scale: float = 1.0   # attention scores are multiplied with this on top of the mixer's own scale
 
     def angles(self, batch):
         """Optional: [tokens, rotary_dim] float32, cosines then sines of the step's positions, formed once per

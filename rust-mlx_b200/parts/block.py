@@ -21,8 +21,18 @@ class PreNormBlock(Part):
         return [self.norm1, self.mixer, self.norm2, self.ffn]
 
     def forward(self, h, pending, batch, cache):
+        tap = self.ctx.tap
         h, x = self.norm1.forward(h, pending)
+        if tap is not None:
+            tap("residual", h)      # the stream as this block finds it: everything before it has been added
+            tap("norm1", x)
         a = self.mixer.forward(x, batch, cache)
+        if tap is not None:
+            tap("mixer_out", a)
         h, x = self.norm2.forward(h, a)
+        if tap is not None:
+            tap("norm2", x)
         m = self.ffn.forward(x, batch)
+        if tap is not None:
+            tap("ffn_out", m)
         return h, m

@@ -57,6 +57,8 @@ class SwiGLUFeedForward(FeedForward):
             gu = ws.get("gate_up", (n, 2 * self.inner), dt)
             ops.linear(x, self.w_gate_up, gu, ws, status)
             ops.swiglu(gu, act, self.block)
+        if self.ctx.tap is not None:
+            self.ctx.tap("ffn_act", act)
         y = ws.get("ffn_out", (n, self.width), dt)
         ops.linear(act, self.w_down, y, ws, status)
         return y

@@ -55,7 +55,7 @@ def check_tensors(folder: str, entries: dict, duplicate: list, specs: list, igno
     want = {}
     for s in specs:
         want[s.name] = s
-    missing = [n for n in want if n not in entries]
+    missing = [n for n in want if n not in entries and not want[n].optional]
     unexpected = [n for n in entries if n not in want and not any(fnmatch.fnmatch(n, pat) for pat in ignore)]
     wrong = []
     for name, s in want.items():
@@ -90,7 +90,7 @@ def load_tensors(folder: str, specs: list, compute_dtype: torch.dtype, device, i
     check_tensors(folder, entries, duplicate, specs, ignore)
     out = {}
     for i, s in enumerate(specs):
-        if s.name in out:
+        if s.name in out or (s.optional and s.name not in entries):
             continue
         t = entries[s.name].load()
         out[s.name] = t.to(device=device, dtype=held_dtype(s, t.dtype, compute_dtype))

@@ -84,12 +84,52 @@ def rms_norm(v, weight, eps):
     return v * torch.rsqrt(ms + eps) * weight
 
 
-def linear(x, weight):
-    """y = x . W^T with W stored [out, in] (src/weights.rs:196)."""
-    return x @ weight.t()
+def linear(x, weight, bias=None, rnd=lambda t: t):
+    """y = x . W^T with W stored [out, in] (src/weights.rs:196), plus the bias where the checkpoint has a
+    tensor ``<prefix>.bias``: added to the product, which the library has already rounded to the activations'
+    dtype (src/weights.rs:96,198-200)."""
+    y = rnd(x @ weight.t())
+    return y if bias is None else rnd(y + bias)
 
 
-def rope(x, positions, theta, rotary_dim):
+def rope_frequencies(config, rotary_dim):
+    """(inv_freq as float32 [rotary_dim / 2], factor that q and k are each multiplied with).
+
+    Plain: inv_freq[j] = theta^(-2j / rotary_dim), factor 1 (src/dense.rs:187-195: scale 1).  The reference's dense
+    model has no scaled variant; "linear" and "yarn" restate the published definitions.  linear: inv_freq / factor.
+    yarn: the pair index at which a pair makes b turns within the original context L is
+    d(b) = rotary_dim ln(L / (2 pi b)) / (2 ln theta); pairs below floor(d(beta_fast)) keep their frequency, pairs
+    above ceil(d(beta_slow)) are divided by factor, linear in the index between; q and k are multiplied by
+    0.1 ln(factor) + 1 unless ``attention_factor`` is given."""
+    theta = rope_theta(config)
+    half = rotary_dim // 2
+    inv = theta ** (-2.0 * torch.arange(half, dtype=F) / rotary_dim)
+    scaling = config.get("rope_scaling")
+    if scaling is None and isinstance(config.get("rope_parameters"), dict) and \
+            config["rope_parameters"].get("rope_type", "default") != "default":
+        scaling = config["rope_parameters"]
+    kind = (scaling or {}).get("rope_type", (scaling or {}).get("type"))
+    if kind in (None, "default"):
+        return inv.to(torch.float32), 1.0
+    factor = float(scaling["factor"])
+    if kind == "linear":
+        return (inv / factor).to(torch.float32), 1.0
+    if kind != "yarn":
+        raise ValueError(kind)
+    L = float(scaling.get("original_max_position_embeddings") or config["max_position_embeddings"])
+    d = lambda b: rotary_dim * math.log(L / (2 * math.pi * b)) / (2 * math.log(theta))  # noqa: E731
+    low = max(math.floor(d(scaling.get("beta_fast", 32.0))), 0)
+    high = min(math.ceil(d(scaling.get("beta_slow", 1.0))), rotary_dim - 1)
+    high = high if high != low else low + 0.001
+    out = torch.empty(half, dtype=F)
+    for j in range(half):
+        share = min(max((j - low) / (high - low), 0.0), 1.0)      # of the divided frequency
+        out[j] = share * inv[j] / factor + (1.0 - share) * inv[j]
+    given = scaling.get("attention_factor")
+    return out.to(torch.float32), float(given) if given is not None else 0.1 * math.log(factor) + 1.0
+
+
+def rope(x, positions, theta, rotary_dim, inv_freq=None):
     """Half-split rotation of the first ``rotary_dim`` numbers of each head:
     pairs (j, j + rotary_dim/2), inv_freq[j] = theta^(-2j/rotary_dim),
     out[j] = x[j] cos - x[j+half] sin, out[j+half] = x[j+half] cos + x[j] sin
@@ -100,7 +140,8 @@ def rope(x, positions, theta, rotary_dim):
     x: [T, heads, head_dim]; positions: [T]."""
     half = rotary_dim // 2
     j = torch.arange(half, dtype=F, device=x.device)
-    inv_freq = (theta ** (-2.0 * j / rotary_dim)).to(torch.float32)
+    if inv_freq is None:
+        inv_freq = (theta ** (-2.0 * j / rotary_dim)).to(torch.float32)
     angle = (positions.to(device=x.device, dtype=torch.float32)[:, None] * inv_freq[None, :]).to(F)   # [T, half]
     cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
     a, b = x[..., :half], x[..., half:rotary_dim]
@@ -110,7 +151,7 @@ def rope(x, positions, theta, rotary_dim):
     return out
 
 
-def attention_scores(q, k, v, positions, window):
+def attention_scores(q, k, v, positions, window, score_factor=1.0):
     """softmax(scale * q k^T + mask) v with scale = head_dim^-0.5, causal mask aligned
     to the end, query head i reading kv head i // (heads / kv_heads)
     (src/dense.rs:221-227, 249-256).  q: [T, nq, hd]; k, v: [T, nkv, hd].
@@ -118,7 +159,7 @@ def attention_scores(q, k, v, positions, window):
     T, nq, hd = q.shape
     nkv = k.shape[1]
     group = nq // nkv
-    scale = hd ** -0.5
+    scale = hd ** -0.5 * score_factor
     pos = positions.to(device=q.device, dtype=torch.long)
     allowed = pos[None, :] <= pos[:, None]
     if window > 0:
@@ -133,30 +174,37 @@ def attention_scores(q, k, v, positions, window):
     return out
 
 
-def attention(x, w, prefix, config, positions, window, rnd):
+def attention(x, w, prefix, config, positions, window, rnd, tap=None):
     """q/k/v projections, per-head RMSNorm of q and k before the rotation, rotation of
     all head_dim numbers, attention, output projection (src/dense.rs:139-270)."""
     T = x.shape[0]
     nq, nkv, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
     eps = config["rms_norm_eps"]
-    q = rnd(linear(x, w[prefix + ".q_proj.weight"])).reshape(T, nq, hd)       # dense.rs:147,155
-    k = rnd(linear(x, w[prefix + ".k_proj.weight"])).reshape(T, nkv, hd)      # dense.rs:157-160
-    v = rnd(linear(x, w[prefix + ".v_proj.weight"])).reshape(T, nkv, hd)      # dense.rs:161-165
+    b = lambda name: w.get(prefix + name)                                    # noqa: E731  (weights.rs:96)
+    q = linear(x, w[prefix + ".q_proj.weight"], b(".q_proj.bias"), rnd).reshape(T, nq, hd)   # dense.rs:147,155
+    k = linear(x, w[prefix + ".k_proj.weight"], b(".k_proj.bias"), rnd).reshape(T, nkv, hd)  # dense.rs:157-160
+    v = linear(x, w[prefix + ".v_proj.weight"], b(".v_proj.bias"), rnd).reshape(T, nkv, hd)  # dense.rs:161-165
     q = rms_norm(q, w[prefix + ".q_norm.weight"], eps)                       # dense.rs:169
     k = rms_norm(k, w[prefix + ".k_norm.weight"], eps)                       # dense.rs:175
     theta = rope_theta(config)
-    q = rnd(rope(q, positions, theta, hd))                                   # dense.rs:187-195
-    k = rnd(rope(k, positions, theta, hd))                                   # dense.rs:206-214
-    o = rnd(attention_scores(q, k, v, positions, window))                    # dense.rs:249-256
-    return rnd(linear(o.reshape(T, nq * hd), w[prefix + ".o_proj.weight"]))  # dense.rs:258-269
+    inv_freq, qk_factor = rope_frequencies(config, hd)
+    q = rnd(rope(q, positions, theta, hd, inv_freq))                         # dense.rs:187-195
+    k = rnd(rope(k, positions, theta, hd, inv_freq))                         # dense.rs:206-214
+    o = rnd(attention_scores(q, k, v, positions, window, qk_factor ** 2))    # dense.rs:249-256
+    if tap is not None:
+        tap("q_rot", q.reshape(T, nq * hd))
+        tap("attn_out", o.reshape(T, nq * hd))
+    return linear(o.reshape(T, nq * hd), w[prefix + ".o_proj.weight"], b(".o_proj.bias"), rnd)  # dense.rs:258-269
 
 
-def swiglu_mlp(x, w, prefix, rnd):
+def swiglu_mlp(x, w, prefix, rnd, tap=None):
     """down(silu(gate(x)) * up(x)), silu(z) = z * sigmoid(z) (src/dense.rs:293-298;
     src/compiled.rs:7-12: the product is formed without rounding silu(gate) first)."""
     g = rnd(linear(x, w[prefix + ".gate_proj.weight"]))
     u = rnd(linear(x, w[prefix + ".up_proj.weight"]))
     act = rnd(g * torch.sigmoid(g) * u)
+    if tap is not None:
+        tap("ffn_act", act)
     return rnd(linear(act, w[prefix + ".down_proj.weight"]))
 
 
@@ -171,8 +219,10 @@ def prepare_weights(config, tensors, rounding):
     return out
 
 
-def forward(config, w, ids, rounding=None, positions=None):
-    """Logits [T, vocab] of the whole sequence ``ids`` (src/dense.rs:371-397)."""
+def forward(config, w, ids, rounding=None, positions=None, intermediates=None):
+    """Logits [T, vocab] of the whole sequence ``ids`` (src/dense.rs:371-397).  ``intermediates``: a dictionary
+    that receives every layer's named tensors as ``run<i>.<name>`` (the names the reference's trace program
+    compares, src/bin/trace.rs:4-24)."""
     rnd = make_round(rounding)
     T = len(ids)
     if any(i < 0 or i >= config["vocab_size"] for i in ids):
@@ -184,10 +234,18 @@ def forward(config, w, ids, rounding=None, positions=None):
     h = embedding(w["model.embed_tokens.weight"], ids)                        # dense.rs:379
     for i in range(config["num_hidden_layers"]):
         p = f"model.layers.{i}"
+        tap = None
+        if intermediates is not None:
+            tap = lambda name, t, i=i: intermediates.__setitem__(f"run{i}.{name}", t.clone())  # noqa: E731
+            tap("residual", h)
         x = rnd(rms_norm(h, w[p + ".input_layernorm.weight"], eps))           # dense.rs:382
-        h = h + attention(x, w, p + ".self_attn", config, positions, windows[i], rnd)  # dense.rs:381
-        x = rnd(rms_norm(h, w[p + ".post_attention_layernorm.weight"], eps))  # dense.rs:385-389
-        h = h + swiglu_mlp(x, w, p + ".mlp", rnd)                             # dense.rs:385
+        a = attention(x, w, p + ".self_attn", config, positions, windows[i], rnd, tap)
+        h = h + a                                                             # dense.rs:381
+        x2 = rnd(rms_norm(h, w[p + ".post_attention_layernorm.weight"], eps))  # dense.rs:385-389
+        m = swiglu_mlp(x2, w, p + ".mlp", rnd, tap)
+        h = h + m                                                             # dense.rs:385
+        if tap is not None:
+            tap("norm1", x), tap("mixer_out", a), tap("norm2", x2), tap("ffn_out", m)
     x = rnd(rms_norm(h, w["model.norm.weight"], eps))                         # dense.rs:391
     head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings") else w["lm_head.weight"]
     return linear(x, head)                                                    # dense.rs:392-396
@@ -221,8 +279,8 @@ class PlainModel:
         self.rounding = rounding
         self.w = prepare_weights(self.config, tensors, rounding)
 
-    def logits(self, ids):
-        return forward(self.config, self.w, list(ids), self.rounding)
+    def logits(self, ids, intermediates=None):
+        return forward(self.config, self.w, list(ids), self.rounding, intermediates=intermediates)
 
     def greedy(self, prompt, n):
         return greedy(self.config, self.w, prompt, n, self.rounding)

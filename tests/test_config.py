@@ -1,8 +1,10 @@
 """Configuration and registry (no GPU)."""
 import json
+import math
 import os
 
 import pytest
+import torch
 
 from rust_mlx_b200.config import ConfigError, Qwen3Config
 from rust_mlx_b200.registry import (find_architecture, known_architectures, load_config, register_architecture,
@@ -12,7 +14,8 @@ import tiny
 
 def test_reads_every_key_of_both_tiny_configs():
     a = Qwen3Config.from_dict(tiny.TINY_A)
-    b = Qwen3Config.from_dict(tiny.TINY_B)
+    b = Qwen3Config.from_dict(tiny.TINY_BW)
+    assert Qwen3Config.from_dict(tiny.TINY_B).attention_kinds() == ("full_attention",) * 3
     assert (a.num_hidden_layers, a.hidden_size, a.num_attention_heads, a.num_key_value_heads, a.head_dim) == (2, 64, 4, 2, 16)
     assert (b.intermediate_size, b.vocab_size, b.rope_theta, b.rms_norm_eps) == (160, 509, 1e6, 1e-5)
     assert a.tie_word_embeddings and not b.tie_word_embeddings
@@ -49,8 +52,10 @@ def test_all_problems_are_reported_at_once():
     (dict(num_key_value_heads=3), "multiple"),
     (dict(head_dim=15), "even"),
     (dict(model_type="llama"), "model_type"),
-    (dict(attention_bias=True), "bias"),
-    (dict(rope_scaling={"rope_type": "yarn", "factor": 4}), "rope_scaling"),
+    (dict(rope_scaling={"rope_type": "llama3", "factor": 4}), "rope_scaling"),
+    (dict(rope_scaling={"rope_type": "yarn"}), "factor"),
+    (dict(rope_scaling={"type": "linear", "factor": 0.5}), "factor"),
+    (dict(rope_scaling={"rope_type": "yarn", "factor": 2}, max_position_embeddings=0), "original_max_position_embeddings"),
     (dict(use_sliding_window=True, sliding_window=0), "sliding_window"),
     (dict(use_sliding_window=True, sliding_window=8, layer_types=["full_attention"]), "layer_types"),
     (dict(num_hidden_layers=0), "positive"),
@@ -108,3 +113,25 @@ def test_an_architecture_can_be_added_and_removed():
     finally:
         unregister_architecture("ToyForCausalLM")
     assert "ToyForCausalLM" not in known_architectures()
+
+
+def test_projection_bias_and_scaled_rotation_are_read():
+    from rust_mlx_b200.registry import build_model_spec
+    cfg = Qwen3Config.from_dict(dict(tiny.TINY_A, attention_bias=True,
+                                     rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32}))
+    spec = build_model_spec(cfg)
+    names = {s.name: s for s in spec.all_param_specs()}
+    assert names["model.layers.1.self_attn.k_proj.bias"].shape == (2 * 16,)
+    assert names["model.layers.0.self_attn.o_proj.bias"].optional and not names["model.layers.0.self_attn.q_proj.bias"].optional
+    mixer = spec.blocks[0].mixer
+    plain_table = 10000.0 ** (-2.0 * torch.arange(8, dtype=torch.float64) / 16)
+    assert torch.equal(mixer.position._table[:1], plain_table[:1].float())           # the fastest pair keeps its frequency
+    assert torch.allclose(mixer.position._table[-1:], (plain_table[-1:] / 4).float())   # the slowest is divided by the factor
+    assert abs(mixer.scale - 16 ** -0.5 * (0.1 * math.log(4.0) + 1.0) ** 2) < 1e-12
+    # newer checkpoints keep theta and the scaling together
+    cfg2 = Qwen3Config.from_dict({k: v for k, v in dict(tiny.TINY_A, rope_parameters={
+        "rope_theta": 5e4, "rope_type": "linear", "factor": 2.0}).items() if k != "rope_theta"})
+    assert cfg2.rope_theta == 5e4 and cfg2.rope_scaling_parameters()["factor"] == 2.0
+    linear = build_model_spec(cfg2).blocks[0].mixer.position
+    assert torch.allclose(linear._table.double(), 5e4 ** (-2.0 * torch.arange(8, dtype=torch.float64) / 16) / 2, rtol=1e-6)
+    assert linear.score_scale == 1.0

@@ -32,6 +32,20 @@ def test_embedding(dtype, n, width, vocab):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n, width, ld", [(1, 16, 16), (7, 99, 99), (33, 1000, 1536), (300, 6144, 6144)])
+def test_add_bias(dtype, n, width, ld):
+    """x[t, :] += bias with one rounding, also on some columns of wider rows (the rest untouched)."""
+    dt = DT[dtype]
+    full = rnd((n, ld), dt, 1.0, 3)
+    bias = rnd((width,), torch.float32, 0.5, 4)
+    before = full.clone()
+    ops().add_bias(full[:, :width], bias)
+    want = (before[:, :width].float() + bias).to(dt)
+    assert torch.equal(full[:, :width], want)
+    assert torch.equal(full[:, width:], before[:, width:])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("n, width", [(1, 16), (5, 96), (33, 1000), (64, 4096), (3, 12288 + 8)])
 def test_add_rmsnorm(dtype, n, width):
     dt = DT[dtype]

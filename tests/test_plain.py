@@ -85,7 +85,7 @@ def test_whole_model_is_causal_and_tied_head_reads_the_embedding(tmp_path):
 
 
 def test_window_changes_only_late_positions(tmp_path):
-    folder = tiny.make_folder(tmp_path, tiny.TINY_B, seed=2)
+    folder = tiny.make_folder(tmp_path, tiny.TINY_BW, seed=2)
     m = plain.PlainModel(folder)
     ids = tiny.prompts(509, [30])[0]
     with_window = m.logits(ids)

@@ -47,12 +47,12 @@ def test_wrong_rotation_pairing_is_far_from_oracle():
     m = plain.PlainModel(FIXTURE)
     good = plain.rope
 
-    def interleaved(x, positions, theta, rotary_dim):
+    def interleaved(x, positions, theta, rotary_dim, inv_freq=None):
         half = rotary_dim // 2
         perm = torch.cat([torch.arange(0, rotary_dim, 2), torch.arange(1, rotary_dim, 2)])
         inv = torch.empty_like(perm)
         inv[perm] = torch.arange(rotary_dim)
-        return good(x[..., perm], positions, theta, rotary_dim)[..., inv]
+        return good(x[..., perm], positions, theta, rotary_dim, inv_freq)[..., inv]
 
     plain.rope = interleaved
     try:

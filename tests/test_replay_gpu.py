@@ -7,6 +7,16 @@ of order 1; sums of at most a few hundred float32 products), bfloat16 2e-2 again
 plain implementation restated with bfloat16 roundings (a flipped last bit of a
 bfloat16 activation is 4e-3 of its value).  In float32 the four ways must agree bit
 for bit: every kernel of that path adds in an order that depends on the position only.
+
+The bfloat16 bound of a request is 2e-2, or the distance of the bfloat16 restatement itself
+from the exact (float64) logits of that request where that is more: two bfloat16
+evaluations of the same formulas that round at the same places still differ by flipped
+last bits (sums are added in another order), and cannot be asked to agree better than
+either agrees with the exact values.  (Met with B, full attention in all three layers,
+sharpened: one request's restatement lies 0.0233 from its exact logits and the engine
+0.0222 from the restatement; the named intermediates of that step agree bit for bit
+through the first layer's norm and rotation and then differ by single last bits, 2^-6 at
+values between 2 and 4.  A wrong, stale or missing key moves these logits by 0.5.)
 """
 import os
 
@@ -33,7 +43,18 @@ def setup(workdir, name, dtype):
     reqs = {f"r{i}": p for i, p in enumerate(tiny.prompts(raw["vocab_size"], LENGTHS, seed=7))}
     pm = plain.PlainModel(folder, rounding=None if dtype == "float32" else "bfloat16")
     ref = {rid: pm.logits(t).float() for rid, t in reqs.items()}
+    if dtype == "bfloat16":
+        exact = plain.PlainModel(folder)
+        for rid, t in reqs.items():
+            _bound[(name, dtype, rid)] = max(TOL[dtype], tiny.max_abs(ref[rid], exact.logits(t).float()))
     return raw, page, folder, reqs, ref
+
+
+_bound = {}
+
+
+def bound_of(name, dtype, rid):
+    return _bound.get((name, dtype, rid), TOL[dtype])
 
 
 _cache = {}
@@ -52,7 +73,7 @@ def engine_for(folder, dtype, page, tokens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "Bw", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "Bw", "C", "D", "F", "G"])
 @pytest.mark.parametrize("way", ["whole", "tail_one_by_one", "portions", "mixed"])
 def test_every_way_of_cutting_matches_the_plain_implementation(workdir, name, dtype, way):
     raw, page, folder, reqs, ref = cached_setup(workdir, name, dtype)
@@ -64,11 +85,11 @@ def test_every_way_of_cutting_matches_the_plain_implementation(workdir, name, dt
     assert eng.pools.table.live() == 0 and eng.pools.table.free_pages(0) == eng.pools.num_pages
     for rid in reqs:
         assert got[rid].shape == ref[rid].shape
-        assert tiny.max_abs(got[rid], ref[rid]) < TOL[dtype], (rid, way)
+        assert tiny.max_abs(got[rid], ref[rid]) < bound_of(name, dtype, rid), (rid, way)
     _cache[(name, dtype, way)] = got
 
 
-@pytest.mark.parametrize("name", ["A", "B", "Bw", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "Bw", "C", "D", "E", "F", "G"])
 def test_float32_ways_agree_bit_for_bit(workdir, name):
     raw, page, folder, reqs, ref = cached_setup(workdir, name, "float32")
     results = []
@@ -151,7 +172,7 @@ def test_trace_run_program(workdir, dtype):
     out = os.path.join(str(workdir), f"trace_{dtype}")
     got = replay.run_trace_tool(folder, dtype, steps, out, replay.tokens_needed(steps, 64), raw["vocab_size"])
     for rid in reqs:
-        assert tiny.max_abs(got[rid], ref[rid]) < TOL[dtype], rid
+        assert tiny.max_abs(got[rid], ref[rid]) < bound_of("B", dtype, rid), rid
     # a step in which nothing is wanted writes no file; a request may end in a step without entries
     steps2 = [{"step": 0, "entries": [{"id": "x", "tokens": reqs["r1"][:9], "want": []}], "end": []},
               {"step": 1, "entries": [{"id": "x", "tokens": reqs["r1"][9:], "want": [len(reqs["r1"]) - 10]}], "end": []},
@@ -159,7 +180,7 @@ def test_trace_run_program(workdir, dtype):
     out2 = os.path.join(str(workdir), f"trace2_{dtype}")
     got2 = replay.run_trace_tool(folder, dtype, steps2, out2, 64, raw["vocab_size"])
     assert not os.path.exists(os.path.join(out2, "0.f32"))
-    assert tiny.max_abs(got2["x"][0], ref["r1"][-1]) < TOL[dtype]
+    assert tiny.max_abs(got2["x"][0], ref["r1"][-1]) < bound_of("B", dtype, "r1")
 
 
 def test_out_of_pages_is_an_error_and_changes_nothing(workdir):
@@ -177,3 +198,32 @@ def test_out_of_pages_is_an_error_and_changes_nothing(workdir):
     with pytest.raises(ValueError, match="vocabulary"):
         eng.step([("a", [3], []), ("c", [raw["vocab_size"]], [0])])
     assert eng.length("c") == 0 and eng.length("a") == 17
+
+
+@pytest.mark.parametrize("name, dtype", [("A", "float32"), ("D", "float32"), ("D", "bfloat16")])
+def test_named_intermediates_of_a_step_match_the_plain_implementation(workdir, name, dtype):
+    """``bin/trace_run --dump-intermediates``: every layer run's named tensors of a whole-prompt step against the
+    plain implementation's tensors of the same names (what the reference's trace program does with an oracle's
+    dump, src/bin/trace.rs:4-24), and of a later decoded token against the plain tensors' row of that position."""
+    from safetensors.torch import load_file
+    raw, page, folder, reqs, ref = cached_setup(workdir, name, dtype)
+    toks = reqs["r4"]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:-1], "want": [0]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": toks[-1:], "want": [0]}], "end": ["a"]}]
+    out = os.path.join(str(workdir), f"dump_{name}_{dtype}")
+    replay.run_trace_tool(folder, dtype, steps, out, 64, raw["vocab_size"], extra=["--dump-intermediates", "all", "--page-size", str(page)])
+    want = {}
+    plain.PlainModel(folder, rounding=None if dtype == "float32" else "bfloat16").logits(toks, want)
+    first = load_file(os.path.join(out, "0.intermediates.safetensors"))
+    last = load_file(os.path.join(out, "1.intermediates.safetensors"))
+    names = {f"run{i}.{n}" for i in range(raw["num_hidden_layers"])
+             for n in ("residual", "norm1", "q_rot", "attn_out", "mixer_out", "norm2", "ffn_act", "ffn_out")}
+    assert set(first) == names
+    # (a decoding step with heads of 128 in bfloat16 rotates inside its attention kernel: no q_rot then)
+    assert set(last) | {n for n in names if n.endswith("q_rot")} == names
+    tol = 2e-5 if dtype == "float32" else 4e-2
+    for got, rows in ((first, slice(0, len(toks) - 1)), (last, slice(len(toks) - 1, len(toks)))):
+        for key, t in got.items():
+            w = want[key][rows].float()
+            assert t.shape == w.shape, key
+            assert tiny.max_abs(t, w) < tol * max(1.0, w.abs().max().item()), key

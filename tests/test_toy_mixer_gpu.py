@@ -110,13 +110,28 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         whole = replay.run_engine(eng, replay.whole(reqs))
         for rid in reqs:
             assert tiny.max_abs(whole[rid], ref[rid]) < 2e-5, rid
-        # generation through the scheduler works for it too
-        out = eng.generate([reqs["r0"], reqs["r1"]], max_tokens=5, prefill_chunk=4)
-        ids = list(reqs["r1"])
-        for t in out[1]:
-            logits = plain_toy_logits(folder, ids)[-1]
-            assert logits[t] >= logits.max() - 1e-5
-            ids.append(t)
+        # generation through the scheduler works for it too: the scheduler takes slots from the page table itself,
+        # and a request it admits (or admits again after it stepped back) must not see what the slot's last owner
+        # left there: the slots are made dirty first, and the short prompts would show it
+        def follows_plain(prompts, out):
+            for p, toks in zip(prompts, out):
+                ids = list(p)
+                for t in toks:
+                    logits = plain_toy_logits(folder, ids)[-1]
+                    assert logits[t] >= logits.max() - 1e-5, (len(p), len(ids))
+                    ids.append(t)
+        for grp in eng.pools.state_groups:
+            grp.state.fill_(50.0)
+        ps = [reqs["r3"], reqs["r0"], reqs["r1"]]
+        follows_plain(ps, eng.generate(ps, max_tokens=5, prefill_chunk=4))
+        small = Engine(folder, dtype="float32", max_tokens=80, page_size=8, max_requests=3)   # ten pages: not enough
+        for grp in small.pools.state_groups:
+            grp.state.fill_(-30.0)
+        ps = [reqs["r1"], reqs["r4"], reqs["r2"]]
+        r = small.generate_detailed(ps, max_tokens=12, prefill_chunk=8, ignore_eos=True)
+        assert r.preemptions > 0
+        follows_plain(ps, r.tokens)
+        assert small.pools.table.live() == 0
     finally:
         unregister_architecture("ToyStateForCausalLM")
 

@@ -52,6 +52,68 @@ def test_random_model_folder_is_reproducible_and_keyed_by_name(tmp_path):
     assert torch.equal(tbf["lm_head.weight"], ta["lm_head.weight"].to(torch.bfloat16))
 
 
+def test_random_numbers_are_a_function_of_key_and_index():
+    """The generator against its definition restated with Python integers: element i takes outputs 3i+1..3i+3 of
+    SplitMix64 keyed by ``key``, adds their twelve 16-bit pieces, centres and scales once in float32.  Numbers made
+    in one piece and in pieces (the generator works in chunks) are the same."""
+    import numpy as np
+    from rust_mlx_b200.weights import random_init
+    mask = (1 << 64) - 1
+
+    def mix(z):
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+        return z ^ (z >> 31)
+    key = 0xFEDCBA9876543210
+    scale = np.float32(0.02 / (2.0 * (65536.0 ** 2 - 1.0) ** 0.5))
+    x = random_init.normal(key, 5000, 0.02)
+    for i in (0, 1, 2, 77, 4999):
+        total = 0
+        for k in (1, 2, 3):
+            h = mix((key + (3 * i + k) * 0x9E3779B97F4A7C15) & mask)
+            total += sum((h >> s) & 0xFFFF for s in (0, 16, 32, 48))
+        assert np.float32(x[i].item()) == np.float32(2 * total - 12 * 65535) * scale, i
+    old = random_init._CHUNK
+    random_init._CHUNK = 1024
+    try:
+        assert torch.equal(random_init.normal(key, 5000, 0.02), x)
+    finally:
+        random_init._CHUNK = old
+    big = random_init.normal(3, 200000, 1.0)
+    assert abs(big.mean().item()) < 0.01 and abs(big.std().item() - 1.0) < 0.01
+    assert abs((big ** 4).mean().item() - 2.9) < 0.1           # a sum of twelve uniform numbers: kurtosis 2.9
+
+
+@pytest.mark.gpu
+def test_random_weights_are_the_same_on_the_gpu_as_in_a_folder(tmp_path):
+    """``Engine(config, random_weights=True)`` draws on the GPU what ``write_random_model`` draws on the CPU for the
+    same seed: bit for bit, in both held dtypes, and so the command line's ``--random-weights`` generates what the
+    written folder generates."""
+    import subprocess
+    import sys
+    from rust_mlx_b200.weights import random_tensors
+    cfg = Qwen3Config.from_dict(tiny.TINY_D)
+    specs = build_model_spec(cfg).all_param_specs()
+    for store, held in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+        folder = write_random_model(cfg, str(tmp_path / store), seed=9, store_dtype=store)
+        disk = load_tensors(folder, specs, held, "cuda:0")
+        made = random_tensors(specs, 9, held, "cuda:0")
+        assert set(disk) == set(made)
+        for k in disk:
+            assert disk[k].dtype == made[k].dtype and torch.equal(disk[k], made[k]), k
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ids = str(tmp_path / "p.json")
+    json.dump([5, 9, 300, 41, 7], open(ids, "w"))
+    outs = []
+    for extra in ([], ["--random-weights"]):
+        out = str(tmp_path / f"r{len(extra)}.json")
+        subprocess.run([sys.executable, os.path.join(root, "bin", "infer"), "--model", folder, "--prompt-ids", ids,
+                        "--max-tokens", "8", "--runs", "1", "--warmup-tokens", "1", "--ignore-eos", "--seed", "9",
+                        "--output", out] + extra, check=True, timeout=600)
+        outs.append(json.load(open(out))["runs"][0]["tokens"])
+    assert outs[0] == outs[1] and len(outs[0]) == 8
+
+
 def test_dtypes_held(tmp_path):
     cfg = Qwen3Config.from_dict(tiny.TINY_A)
     folder = write_random_model(cfg, str(tmp_path / "m"), seed=1, store_dtype="bfloat16")

@@ -48,8 +48,18 @@ TINY_E = dict(
     use_sliding_window=True, sliding_window=100, max_window_layers=1)
 PAGE_E = 16
 
+# F: projections with a bias and yarn-scaled rotation (original context 32, so that the ramp lies inside these heads);
+# G: D's head size 128 (the decoding attention finishes the projection itself) with a bias and linearly scaled rotation
+TINY_F = dict(
+    model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=80,
+    num_attention_heads=5, num_key_value_heads=5, head_dim=32, intermediate_size=96, vocab_size=301,
+    rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096,
+    attention_bias=True, rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32})
+PAGE_F = 16
+TINY_G = dict(TINY_D, attention_bias=True, rope_scaling={"type": "linear", "factor": 8.0})
+
 CONFIGS = {"A": (TINY_A, PAGE_A), "B": (TINY_B, PAGE_B), "Bw": (TINY_BW, PAGE_B), "C": (TINY_C, PAGE_C), "D": (TINY_D, PAGE_D),
-           "E": (TINY_E, PAGE_E)}
+           "E": (TINY_E, PAGE_E), "F": (TINY_F, PAGE_F), "G": (TINY_G, PAGE_D)}
 
 
 def make_folder(tmp_path, raw: dict, seed: int = 0, store: str = "float32") -> str:
