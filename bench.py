@@ -235,7 +235,8 @@ def continuous(cfg, raw, a):
     prompts = [torch.randint(0, raw["vocab_size"], (n,), generator=g).tolist() for n in lengths]
     new_tokens = 256
     cache_tokens = sum(-(-(n + new_tokens) // PAGE) * PAGE for n in lengths)
-    engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE, max_requests=64)
+    engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE, max_requests=64,
+                    tuning=a.policy)
     opts = dict(max_tokens=new_tokens, ignore_eos=True, prefill_chunk=512, max_batch_tokens=512 + 64, max_seqs=64)
     engine.generate(prompts[:8], **dict(opts, max_tokens=8))            # warm-up: kernels, graphs of the first sizes
     torch.cuda.synchronize()
@@ -286,8 +287,6 @@ def main():
     from rust_mlx_b200.config import Qwen3Config
     from rust_mlx_b200.engine import Engine
 
-    from rust_mlx_b200.kernels import ops
-    ops.tcgen05_policy = a.policy
     CONTEXT = a.context
     base = SHAPES[a.shape]
     if a.shape != "qwen3-8b" and a.layers == QWEN3_8B["num_hidden_layers"]:
@@ -300,7 +299,7 @@ def main():
     biggest = 1 if (a.no_points or a.prefill_only) else max(64, a.batch)
     cache_tokens = max(biggest, a.batch) * (CONTEXT + 2 * PAGE + a.steps + a.warmup + 64)
     engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE,
-                    max_requests=max(biggest, a.batch) + 2)
+                    max_requests=max(biggest, a.batch) + 2, tuning=a.policy)
     for grp in engine.pools.paged_groups:      # synthetic cache contents for the requests that start at CONTEXT
         grp.k_pool.normal_(0, 1)
         grp.v_pool.normal_(0, 1)

@@ -45,12 +45,18 @@ class Engine:
     ``random_weights=True``) a typed configuration / a folder whose config.json alone
     is read.  ``max_tokens``: how many tokens the cache holds in all (rounded up to
     pages).  ``dtype``: "bfloat16" (serving kernels) or "float32" (every product,
-    norm and softmax in true 32-bit).
+    norm and softmax in true 32-bit).  ``tuning``: which bfloat16 products of few rows take this
+    package's tcgen05 kernel: "auto" times it against the library's product on the model's own
+    weights when the engine starts (shapes whose weights together hold ``tune_min_bytes``), so two
+    starts may choose differently and differ in last bits; "measured" is a fixed rule and
+    ``tuning_table()`` of an earlier engine pins that engine's choices: one checkpoint, one set of
+    bits.  "all" and "none" are for comparisons.
     """
 
     def __init__(self, model, *, dtype: str = "bfloat16", random_weights: bool = False, seed: int = 0,
                  max_tokens: int = 8192, page_size: int = 64, max_requests: int = 256, device: str = "cuda:0",
-                 max_context: int = 0, cuda_graphs: bool = True, verbose: bool = False):
+                 max_context: int = 0, cuda_graphs: bool = True, verbose: bool = False, tuning="auto",
+                 tune_min_bytes: float = 256e6):
         if dtype not in _DTYPES:
             raise EngineError(f"dtype must be one of {sorted(set(_DTYPES))}, got {dtype!r}")
         if not torch.cuda.is_available():
@@ -74,7 +80,8 @@ class Engine:
             self.config = model
         self.spec = build_model_spec(self.config)
         self.workspace = Workspace(self.device)
-        ctx = BuildContext(self.device, self.dtype, _ops, self.workspace)
+        self.ops = _ops.Kernels(tuning)     # this engine's switches and tuning results
+        ctx = BuildContext(self.device, self.dtype, self.ops, self.workspace)
         self._ctx = ctx
         specs = self.spec.all_param_specs()
         if random_weights:
@@ -90,12 +97,14 @@ class Engine:
         self.page_size = page_size
         self.pools = CachePools(self.spec.cache_specs(), max_tokens=max_tokens, page_size=page_size,
                                 max_requests=max_requests, dtype=self.dtype, device=self.device)
-        # which schedule entry writes each cache: the first that names it
+        # which schedule entry writes each cache: the first that names it.  An entry runs with one view for each thing
+        # its block remembers: (cache id, whether this run only reads it)
         seen = set()
         self._calls = []
         for call in self.spec.schedule:
-            self._calls.append((call, call.cache in seen))
-            seen.add(call.cache)
+            ids = call.cache_ids()[:len(self.spec.blocks[call.layer].cache_specs())]
+            self._calls.append((call, tuple((cid, cid in seen) for cid in ids)))
+            seen.update(ids)
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # the token the last sampling chose for the request in each state slot: a decode step launched before the
         # host has read the step before takes its ids from here
@@ -107,18 +116,16 @@ class Engine:
         if stated > 0:
             limit = min(limit, stated)
         self.max_context = min(limit, max_context) if max_context > 0 else limit
-        self.ops = _ops
-        self.max_kv_heads = max([s.kv_heads for s in self.spec.cache_specs().values() if s.kind == "paged"] or [1])
         self._launches_per_graph = {}
         from .graphs import DecodeGraphs
         self.graphs = DecodeGraphs(self) if cuda_graphs and all(p.graph_safe for p in self.spec.all_parts()) else None
         self._req_ids = {}
         self._next_id = 0
-        if self.dtype == torch.bfloat16 and _ops.tcgen05_policy == "auto":
+        if self.dtype == torch.bfloat16 and self.ops.tcgen05_policy == "auto":
             weights = [w for part in self.spec.all_parts() for w in part.linear_weights()]
-            _ops.autotune_linears(weights, self.workspace, log=_log if verbose else None)
+            self.ops.autotune_linears(weights, self.workspace, log=_log if verbose else None, min_bytes=tune_min_bytes)
             fused = [w for part in self.spec.all_parts() for w in part.gate_up_weights()]
-            _ops.autotune_fused_swiglu(fused, self.workspace, log=_log if verbose else None)
+            self.ops.autotune_fused_swiglu(fused, self.workspace, log=_log if verbose else None, min_bytes=tune_min_bytes)
         self.load_seconds = time.time() - t0
         if verbose:
             _log(f"model ready in {self.load_seconds:.1f}s: {len(self.spec.blocks)} layers, {self.dtype_name}, "
@@ -195,9 +202,11 @@ class Engine:
         batch.last_tokens = self.last_tokens
         h = spec.embedding.forward(batch.token_ids, batch)
         pending = None
-        for index, (call, read_only) in enumerate(self._calls):
-            cache = self.pools.view(call.cache, batch, read_only) if call.cache in self.pools._where else None
+        for index, (call, caches) in enumerate(self._calls):
+            views = tuple(self.pools.view(cid, batch, read_only) for cid, read_only in caches)
             self._run_index = index
+            # a block that remembers one thing gets its view, one that remembers several a tuple of them
+            cache = None if not views else (views[0] if len(views) == 1 else views)
             h, pending = spec.blocks[call.layer].forward(h, pending, batch, cache)
         if batch.n_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
@@ -229,6 +238,10 @@ class Engine:
     def generate_detailed(self, prompts: list, **options):
         from .generate import generate
         return generate(self, prompts, **options)
+
+    def tuning_table(self) -> dict:
+        """What this engine's tuning chose; ``Engine(..., tuning=table)`` makes the same choices again."""
+        return self.ops.tuning_table()
 
     def check_status(self) -> None:
         """Kernels report what they could not do (a token without a page) in a status word."""

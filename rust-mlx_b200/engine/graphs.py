@@ -3,7 +3,7 @@
 A decode step (every sequence brings one token and wants its logits) launches a
 few hundred small kernels; issuing them one by one costs more host time than
 the GPU needs to run them.  The step — embedding, every layer, final norm, head
-and sampling — is captured once per (batch size, attention split count) into a
+and sampling — is captured once per (batch size, what the parts say of their launch shapes: ``Part.graph_key``) into a
 CUDA graph whose kernels read the step's ids, positions, block tables and
 sampling numbers from one device buffer of fixed address and layout; each later
 step of that shape copies its numbers into the buffer and launches the graph.
@@ -15,6 +15,7 @@ import gc
 
 import torch
 
+from ..parts.base import DecodeShape, Part
 from .batch import BatchLayout, check_sequences
 
 
@@ -42,6 +43,8 @@ class DecodeGraphs:
         self.graphs = {}
         self.replays = 0
         self.captures = 0
+        # the parts whose launches follow the sequences' lengths: they say so by overriding ``graph_key``
+        self._keyed = [p for p in engine.spec.all_parts() if type(p).graph_key is not Part.graph_key]
 
     def entries(self) -> list:
         e = self.engine
@@ -65,8 +68,8 @@ class DecodeGraphs:
         longest = max(s.start + 1 for s in seqs)
         if longest > e.max_context:
             raise ValueError(f"a sequence of {longest} tokens exceeds the context limit {e.max_context}")
-        splits = e.ops.flash_splits(n, e.max_kv_heads, longest) if hasattr(e.ops, "flash_splits") else 1
-        key = (n, splits)
+        shape = DecodeShape(n, longest)
+        key = (n, tuple(p.graph_key(shape) for p in self._keyed))
         cap = self.graphs.get(key)
         if cap is not None and cap.generation != e.workspace.generation:
             del self.graphs[key]
@@ -105,7 +108,6 @@ class DecodeGraphs:
         cap.dev.copy_(cap.hosts[0], non_blocking=True)
         cap.events[0].record()
         cap.batch = cap.layout.views(cap.dev, e._status, facts)
-        cap.batch.forced_splits = key[1]
         # once eagerly: buffers reach their size, kernels' attributes are set, libraries warm up.
         # It writes this step's keys and values, which the replay below writes again, the same; the tokens it
         # chooses are put back, because a step that runs ahead takes its ids from there.

@@ -175,41 +175,10 @@ def sample(logits, temperature, uniform, out, slots=None, last_tokens=None):
 
 
 # ---------------------------------------------------------------------------
-# Dispatch: which kernel serves a call.  float32 always takes the plain kernels (fixed
-# order of summation, no tensor cores); bfloat16 takes the fast ones where they apply.
-
-def linear(x, w, out, workspace=None, status=None):
-    """out = x . w^T.  w is [out_features, in_features] as stored in the checkpoint."""
-    if x.dtype == torch.float32:
-        gemm_plain(x, w, out)
-    else:
-        linear_bf16(x, w, out, workspace, status)
-
-
-# Which products of few rows (up to 64) take this package's tcgen05 kernel rather than the library's
-# product: "auto" (whichever was faster when the engine timed both on the model's own weights, see
-# ``autotune_linears``; shapes that were not timed follow "measured"), "all" (every product the kernel
-# supports), "measured" (the output head and long reductions, where it won on Qwen3-8B shapes), "none".
-tcgen05_policy = "auto"
-# Launch the tcgen05 product as a programmatic dependent of the kernel before it, so that its weight
-# loads start while that kernel ends.
-dependent_launch = True
-_tuned = {}   # (n, k, padded rows) -> True if the tcgen05 kernel was faster
-_tuned_splits = {}   # (n, k, padded rows) -> the number of K slices that was fastest
-
+# Helpers of the dispatch below that hold no state.
 
 def _mpad(m: int) -> int:
     return 16 if m <= 16 else (32 if m <= 32 else 64)
-
-
-def prefers_tcgen05(m: int, n: int, k: int) -> bool:
-    if tcgen05_policy == "none" or not tcgen05_supported(m, n, k):
-        return False
-    if tcgen05_policy == "all":
-        return True
-    if tcgen05_policy == "auto" and (n, k, _mpad(m)) in _tuned:
-        return _tuned[(n, k, _mpad(m))]
-    return n * k >= (1 << 28) or (k >= 8192 and m <= 32)
 
 
 def _graph_time(fn, calls: int, reps: int = 3) -> float:
@@ -229,85 +198,6 @@ def _graph_time(fn, calls: int, reps: int = 3) -> float:
     stop.record()
     torch.cuda.synchronize()
     return start.elapsed_time(stop) / reps / calls * 1e3
-
-
-def autotune_linears(weights: list, workspace=None, rows=(8, 32, 64), log=None) -> dict:
-    """Time the tcgen05 product against the library's on the model's own bfloat16 weights, per
-    shape and per padded row count, and remember the faster.  Weights of one shape take turns so
-    that none is served from L2 (a lone small weight would be: its timing then says little and
-    the rule of "measured" stands for it)."""
-    groups = {}
-    for w in weights:
-        if w is not None and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_cuda:
-            groups.setdefault((w.shape[0], w.shape[1]), []).append(w)
-    for (n, k), ws in groups.items():
-        if not tcgen05_supported(1, n, k) or len(ws) * n * k * 2 < 256e6:
-            continue
-        for m in rows:
-            key = (n, k, _mpad(m))
-            if key in _tuned:
-                continue
-            a = torch.randn(m, k, device=ws[0].device).to(torch.bfloat16)
-            out = torch.empty(m, n, dtype=torch.bfloat16, device=ws[0].device)
-            calls = max(4, min(len(ws), 12))
-            # the kernel's own choice first: how many slices of K share a tile (the rule's count and its neighbours)
-            rule = min(tcgen05_splits(m, n, k), 8 if m <= 32 else 4)
-            best = None
-            for splits in sorted({max(1, rule - 1), rule, min(rule + 1, 8 if m <= 32 else 4), min(rule + 2, 8 if m <= 32 else 4)}):
-                if splits > max(1, -(-k // 64) // 4):
-                    continue
-                t = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], out, workspace, splits=splits, dependent=True), calls)
-                if best is None or t < best[0]:
-                    best = (t, splits)
-            mine, _tuned_splits[key] = best
-            lib = _graph_time(lambda i: torch.mm(a, ws[i % len(ws)].t(), out=out), calls)
-            _tuned[key] = mine < lib
-            if log is not None:
-                log(f"product [{m} x {k}] . [{n} x {k}]^T: tcgen05 {mine:.1f} us with {best[1]} slices of K, library {lib:.1f} us")
-    return dict(_tuned)
-
-
-def autotune_fused_swiglu(weights: list, workspace=None, rows=(8, 32, 64), log=None) -> dict:
-    """The same for gate/up weights in blocks of 64: the tcgen05 product with the SwiGLU epilogue
-    against the library's product followed by the pointwise kernel."""
-    groups = {}
-    for w in weights:
-        if w is not None and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_cuda and w.shape[0] % 128 == 0:
-            groups.setdefault((w.shape[0], w.shape[1]), []).append(w)
-    for (n, k), ws in groups.items():
-        if not tcgen05_supported(1, n, k) or len(ws) * n * k * 2 < 256e6:
-            continue
-        for m in rows:
-            key = (n, k, _mpad(m), "swiglu")
-            if key in _tuned:
-                continue
-            a = torch.randn(m, k, device=ws[0].device).to(torch.bfloat16)
-            gu = torch.empty(m, n, dtype=torch.bfloat16, device=ws[0].device)
-            act = torch.empty(m, n // 2, dtype=torch.bfloat16, device=ws[0].device)
-            calls = max(4, min(len(ws), 12))
-            mine = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], act, workspace, swiglu=True), calls)
-
-            def lib_pair(i):
-                torch.mm(a, ws[i % len(ws)].t(), out=gu)
-                swiglu(gu, act, 64)
-            lib = _graph_time(lib_pair, calls)
-            # inside a step the fused product also spares a kernel's start and end, which this timing of the pair
-            # alone does not show: it is taken unless the pair is clearly faster
-            _tuned[key] = mine < lib * 1.05
-            if log is not None:
-                log(f"gate/up [{m} x {k}] . [{n} x {k}]^T + SwiGLU: fused tcgen05 {mine:.1f} us, library + pointwise {lib:.1f} us")
-    return dict(_tuned)
-
-
-def linear_bf16(x, w, out, workspace=None, status=None):
-    """bfloat16 operands, float accumulation; the result in bfloat16 or (for logits) float32."""
-    m, k = x.shape
-    if prefers_tcgen05(m, w.shape[0], k) and x.stride(1) == 1 and w.stride(1) == 1:
-        gemm_tcgen05(x, w, out, workspace, status, dependent=dependent_launch)
-    elif out.dtype == torch.bfloat16:
-        torch.mm(x, w.t(), out=out)
-    else:
-        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
 
 
 class _Sequences:
@@ -348,40 +238,6 @@ def _short_and_long(batch, group: int):
     return found
 
 
-def attention(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=None,
-              projection=None):
-    """Picks the attention kernel for the dtype, head size and shape of the step.  A step that mixes decoded
-    tokens with prompt portions runs as two launches, each kind with the kernel made for it.  ``projection``
-    (see ``decode_takes_projection``): the q/k/v rows before norm and rotation, which the decoding kernel then
-    finishes itself; ``q`` is not read."""
-    group = nq // nkv
-    if projection is not None:
-        attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
-                        projection=projection)
-        return
-    if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, group):
-        runs = _short_and_long(batch, group)
-        if runs is not None:
-            for run in runs:
-                _attention_bf16(q, k_pool, v_pool, run, block_table[run.first:run.last], page_size, out, nq, nkv, hd,
-                                window, scale, workspace)
-            return
-    _attention_bf16(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace)
-
-
-def _attention_bf16(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace):
-    group = nq // nkv
-    if (q.dtype == torch.bfloat16 and use_tcgen05_attention and getattr(batch, "max_q_len", 0) * group > 16
-            and tcgen05_attention_supported(hd, group, page_size)):
-        attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=workspace)
-        return
-    if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, nq // nkv):
-        attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace)
-        return
-    attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
-                    window, scale, batch.status)
-
-
 def flash_supported(hd: int, group: int) -> bool:
     return bool(kernels_library().rmx_attention_flash_supports(c_int(hd), c_int(group)))
 
@@ -419,31 +275,23 @@ def flash_splits(n_tiles: int, nkv: int, max_seq_len: int) -> int:
     return splits
 
 
-use_tma = True   # decoding fetches keys and values by TMA where the kernel is built for it
-
-
-fused_decode_rope = True   # a decoding attention norms and rotates its own token while it waits for its first keys
-
-
-def decode_takes_projection(batch, dtype, hd: int, group: int, page_size: int, rotary_dim: int, cos_sin) -> bool:
-    """Whether this step's attention may be handed the q/k/v projection's rows as they come: every sequence brings
-    one token, heads of 128 all rotated, bfloat16, pages the TMA kernel takes."""
-    return (fused_decode_rope and use_tma and dtype == torch.bfloat16 and cos_sin is not None
-            and getattr(batch, "max_q_len", 0) == 1 and batch.n_seqs == batch.positions.shape[0]
-            and bool(kernels_library().rmx_attention_flash_takes_projection(c_int(hd), c_int(group), c_int(page_size), c_int(rotary_dim))))
+def flash_takes_projection(hd: int, group: int, page_size: int, rotary_dim: int) -> bool:
+    """Whether the key-split kernel is built to finish the q/k/v projection of a decoding step at these sizes."""
+    return bool(kernels_library().rmx_attention_flash_takes_projection(c_int(hd), c_int(group), c_int(page_size), c_int(rotary_dim)))
 
 
 def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
-                    n_splits=None, projection=None):
+                    n_splits=None, projection=None, use_tma=True):
     """Tensor-core attention over pages for bfloat16 (prompt portions and decoded tokens alike).  ``projection``:
-    (qkv rows, q_norm, k_norm, eps, cos_sin, write_kv) for a decoding step whose kernel finishes the projection."""
+    (qkv rows, q_norm, k_norm, eps, cos_sin, write_kv) for a decoding step whose kernel finishes the projection.
+    ``use_tma``: keys and values are fetched by TMA where the kernel is built for it."""
     lib = kernels_library()
     group = nq // nkv
     tq = 64 // group
     starts = batch.q_start_host
     n_tiles = sum(-(-(starts[i + 1] - starts[i]) // tq) for i in range(batch.n_seqs))
     if n_splits is None:
-        n_splits = getattr(batch, "forced_splits", None) or flash_splits(n_tiles, nkv, batch.max_seq_len)
+        n_splits = flash_splits(n_tiles, nkv, batch.max_seq_len)
     n = out.shape[0]
     qkv, q_norm, k_norm, eps, cos_sin, write_kv = projection if projection is not None else (None, None, None, 0.0, None, False)
     part_o = part_ml = counters = None
@@ -524,9 +372,7 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
         raise KernelError("gemm_tcgen05: the result is bfloat16 or float32")
     ws = workspace if workspace is not None else _own_workspace()
     if splits is None:
-        splits = _tuned_splits.get((n, k, _mpad(m))) if not swiglu else None
-        if splits is None:
-            splits = tcgen05_splits(m, n, k)
+        splits = tcgen05_splits(m, n, k)
         if cluster:
             splits = min(splits, 8 if m <= 32 else 4)
     partial = counters = None
@@ -543,21 +389,6 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
         c_int((1 if cluster else 0) | (2 if dependent else 0) | (4 if swiglu else 0)), _stream()))
     _launched()
     return status
-
-
-fused_swiglu = True   # the gate/up product of few rows forms silu(gate) * up in its epilogue
-
-
-def prefers_fused_swiglu(m: int, n: int, k: int) -> bool:
-    """The fused product saves a kernel and the round trip of the [m, n] intermediate; it is taken
-    wherever the tcgen05 kernel runs at all, unless timing said the library's product plus the
-    pointwise kernel is faster for this shape."""
-    if not fused_swiglu or tcgen05_policy == "none" or not tcgen05_supported(m, n, k) or n % 128:
-        return False
-    return _tuned.get((n, k, _mpad(m), "swiglu"), True)
-
-
-use_tcgen05_attention = True   # prompt portions at head size 128 run on the tcgen05 tensor cores
 
 
 def tcgen05_attention_supported(hd: int, group: int, page_size: int) -> bool:
@@ -609,9 +440,239 @@ def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq,
     _launched(2 if n_splits > 1 else 1)
 
 
+# Whether this package's kernels are launched as programmatic dependents of the kernel before them (a switch of the
+# loaded library, so of the process: see ``set_dependent_launch``).
+dependent_launch = True
+
+
 def set_dependent_launch(on: bool) -> None:
     """Programmatic dependent launch of this package's kernels (on by default): a kernel's blocks may take their
     places while the kernel before it drains, and the tcgen05 product fetches weights meanwhile."""
     global dependent_launch
     dependent_launch = bool(on)
     kernels_library().rmx_set_dependent_launch(c_int(1 if on else 0))
+
+
+# ---------------------------------------------------------------------------
+# Dispatch: which kernel serves a call.  float32 always takes the plain kernels (fixed order of summation, no
+# tensor cores); bfloat16 takes the fast ones where they apply.  The choices that can be switched or tuned belong
+# to a ``Kernels`` object: every engine has its own and hands it to its parts, so two engines in one process
+# neither share tuning results nor see each other's switches.
+
+class Kernels:
+    """The kernels as one engine sees them: its switches, what its tuning measured, and the dispatch that reads
+    both.  Everything else (the plain faces of the kernels above) is reached through it by name.
+
+    ``policy``: which products of few rows (up to 64) take this package's tcgen05 kernel rather than the library's
+    product: "auto" (whichever was faster when the engine timed both on the model's own weights, see
+    ``autotune_linears``; shapes that were not timed follow "measured"), "measured" (the output head and long
+    reductions, where it won on Qwen3-8B shapes: a fixed rule, the same bits on every start), "all" (every product
+    the kernel supports), "none"; or a table that ``tuning_table`` returned earlier (the choices of that run again).
+    """
+
+    def __init__(self, policy="measured"):
+        self.tuned = {}          # (n, k, padded rows[, "swiglu"]) -> True if the tcgen05 kernel was faster
+        self.tuned_splits = {}   # (n, k, padded rows) -> the number of K slices that was fastest
+        if isinstance(policy, dict):
+            self.load_tuning_table(policy)
+            policy = "auto"
+        if policy not in ("auto", "measured", "all", "none"):
+            raise KernelError(f"unknown kernel policy {policy!r}: auto, measured, all, none or a tuning table")
+        self.tcgen05_policy = policy
+        self.use_tma = True                 # decoding fetches keys and values by TMA where the kernel is built for it
+        self.fused_decode_rope = True       # a decoding attention norms and rotates its own token while it waits for keys
+        self.fused_swiglu = True            # the gate/up product of few rows forms silu(gate) * up in its epilogue
+        self.use_tcgen05_attention = True   # prompt portions at head size 128 run on the tcgen05 tensor cores
+
+    def __getattr__(self, name):
+        # the faces of the kernels that hold no state
+        try:
+            return globals()[name]
+        except KeyError:
+            raise AttributeError(name) from None
+
+    @property
+    def dependent_launch(self) -> bool:
+        return dependent_launch
+
+    # ---- tuning ---------------------------------------------------------------------------------------------
+    def tuning_table(self) -> dict:
+        """What the tuning chose, in a form that JSON takes and ``Kernels(policy=table)`` reads back."""
+        key = lambda k: "x".join(str(p) for p in k)   # noqa: E731
+        return {"policy": self.tcgen05_policy, "tcgen05": {key(k): bool(v) for k, v in sorted(self.tuned.items(), key=str)},
+                "slices": {key(k): int(v) for k, v in sorted(self.tuned_splits.items(), key=str)}}
+
+    def load_tuning_table(self, table: dict) -> None:
+        def key(text):
+            return tuple(int(p) if p.lstrip("-").isdigit() else p for p in text.split("x"))
+        self.tuned = {key(k): bool(v) for k, v in (table.get("tcgen05") or {}).items()}
+        self.tuned_splits = {key(k): int(v) for k, v in (table.get("slices") or {}).items()}
+
+    def prefers_tcgen05(self, m: int, n: int, k: int) -> bool:
+        if self.tcgen05_policy == "none" or not tcgen05_supported(m, n, k):
+            return False
+        if self.tcgen05_policy == "all":
+            return True
+        if self.tcgen05_policy == "auto" and (n, k, _mpad(m)) in self.tuned:
+            return self.tuned[(n, k, _mpad(m))]
+        return n * k >= (1 << 28) or (k >= 8192 and m <= 32)
+
+    def autotune_linears(self, weights: list, workspace=None, rows=(8, 32, 64), log=None, min_bytes: float = 256e6) -> dict:
+        """Time the tcgen05 product against the library's on the model's own bfloat16 weights, per
+        shape and per padded row count, and remember the faster.  Weights of one shape take turns so
+        that none is served from L2 (a lone small weight would be: its timing then says little and
+        the rule of "measured" stands for it; ``min_bytes`` is how much a shape's weights must hold
+        together to be timed)."""
+        groups = {}
+        for w in weights:
+            if w is not None and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_cuda:
+                groups.setdefault((w.shape[0], w.shape[1]), []).append(w)
+        for (n, k), ws in groups.items():
+            if not tcgen05_supported(1, n, k) or len(ws) * n * k * 2 < min_bytes:
+                continue
+            for m in rows:
+                key = (n, k, _mpad(m))
+                if key in self.tuned:
+                    continue
+                a = torch.randn(m, k, device=ws[0].device).to(torch.bfloat16)
+                out = torch.empty(m, n, dtype=torch.bfloat16, device=ws[0].device)
+                calls = max(4, min(len(ws), 12))
+                # the kernel's own choice first: how many slices of K share a tile (the rule's count and its neighbours)
+                most = 8 if m <= 32 else 4
+                rule = min(tcgen05_splits(m, n, k), most)
+                best = None
+                for splits in sorted({max(1, rule - 1), rule, min(rule + 1, most), min(rule + 2, most)}):
+                    if splits > max(1, -(-k // 64) // 4):
+                        continue
+                    t = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], out, workspace, splits=splits, dependent=True), calls)
+                    if best is None or t < best[0]:
+                        best = (t, splits)
+                mine, self.tuned_splits[key] = best
+                lib = _graph_time(lambda i: torch.mm(a, ws[i % len(ws)].t(), out=out), calls)
+                self.tuned[key] = mine < lib
+                if log is not None:
+                    log(f"product [{m} x {k}] . [{n} x {k}]^T: tcgen05 {mine:.1f} us with {best[1]} slices of K, library {lib:.1f} us")
+        return dict(self.tuned)
+
+    def autotune_fused_swiglu(self, weights: list, workspace=None, rows=(8, 32, 64), log=None, min_bytes: float = 256e6) -> dict:
+        """The same for gate/up weights in blocks of 64: the tcgen05 product with the SwiGLU epilogue
+        against the library's product followed by the pointwise kernel."""
+        groups = {}
+        for w in weights:
+            if w is not None and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_cuda and w.shape[0] % 128 == 0:
+                groups.setdefault((w.shape[0], w.shape[1]), []).append(w)
+        for (n, k), ws in groups.items():
+            if not tcgen05_supported(1, n, k) or len(ws) * n * k * 2 < min_bytes:
+                continue
+            for m in rows:
+                key = (n, k, _mpad(m), "swiglu")
+                if key in self.tuned:
+                    continue
+                a = torch.randn(m, k, device=ws[0].device).to(torch.bfloat16)
+                gu = torch.empty(m, n, dtype=torch.bfloat16, device=ws[0].device)
+                act = torch.empty(m, n // 2, dtype=torch.bfloat16, device=ws[0].device)
+                calls = max(4, min(len(ws), 12))
+                mine = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], act, workspace, swiglu=True), calls)
+
+                def lib_pair(i):
+                    torch.mm(a, ws[i % len(ws)].t(), out=gu)
+                    swiglu(gu, act, 64)
+                lib = _graph_time(lib_pair, calls)
+                # inside a step the fused product also spares a kernel's start and end, which this timing of the pair
+                # alone does not show: it is taken unless the pair is clearly faster
+                self.tuned[key] = mine < lib * 1.05
+                if log is not None:
+                    log(f"gate/up [{m} x {k}] . [{n} x {k}]^T + SwiGLU: fused tcgen05 {mine:.1f} us, library + pointwise {lib:.1f} us")
+        return dict(self.tuned)
+
+    def prefers_fused_swiglu(self, m: int, n: int, k: int) -> bool:
+        """The fused product saves a kernel and the round trip of the [m, n] intermediate; it is taken
+        wherever the tcgen05 kernel runs at all, unless timing said the library's product plus the
+        pointwise kernel is faster for this shape."""
+        if not self.fused_swiglu or self.tcgen05_policy == "none" or not tcgen05_supported(m, n, k) or n % 128:
+            return False
+        return self.tuned.get((n, k, _mpad(m), "swiglu"), True)
+
+    # ---- products -------------------------------------------------------------------------------------------
+    def linear(self, x, w, out, workspace=None, status=None):
+        """out = x . w^T.  w is [out_features, in_features] as stored in the checkpoint."""
+        if x.dtype == torch.float32:
+            gemm_plain(x, w, out)
+        else:
+            self.linear_bf16(x, w, out, workspace, status)
+
+    def linear_bf16(self, x, w, out, workspace=None, status=None):
+        """bfloat16 operands, float accumulation; the result in bfloat16 or (for logits) float32."""
+        m, k = x.shape
+        if self.prefers_tcgen05(m, w.shape[0], k) and x.stride(1) == 1 and w.stride(1) == 1:
+            self.gemm_tcgen05(x, w, out, workspace, status, dependent=dependent_launch)
+        elif out.dtype == torch.bfloat16:
+            torch.mm(x, w.t(), out=out)
+        else:
+            torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+
+    def gemm_tcgen05(self, a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False, swiglu=False):
+        """The tcgen05 product with the number of K slices that this engine's tuning found best for the shape."""
+        if splits is None and not swiglu:
+            splits = self.tuned_splits.get((w.shape[0], a.shape[1], _mpad(a.shape[0])))
+            if splits is not None and cluster:
+                splits = min(splits, 8 if a.shape[0] <= 32 else 4)
+        return gemm_tcgen05(a, w, out, workspace, status, splits, cluster, dependent, swiglu)
+
+    # ---- attention ------------------------------------------------------------------------------------------
+    def decode_takes_projection(self, batch, dtype, hd: int, group: int, page_size: int, rotary_dim: int, cos_sin) -> bool:
+        """Whether this step's attention may be handed the q/k/v projection's rows as they come: every sequence brings
+        one token, heads of 128 all rotated, bfloat16, pages the TMA kernel takes."""
+        return (self.fused_decode_rope and self.use_tma and dtype == torch.bfloat16 and cos_sin is not None
+                and getattr(batch, "max_q_len", 0) == 1 and batch.n_seqs == batch.positions.shape[0]
+                and flash_takes_projection(hd, group, page_size, rotary_dim))
+
+    def attention_flash(self, *args, **kwargs):
+        kwargs.setdefault("use_tma", self.use_tma)
+        return attention_flash(*args, **kwargs)
+
+    def attention(self, q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=None,
+                  projection=None):
+        """Picks the attention kernel for the dtype, head size and shape of the step.  A step that mixes decoded
+        tokens with prompt portions runs as two launches, each kind with the kernel made for it.  ``projection``
+        (see ``decode_takes_projection``): the q/k/v rows before norm and rotation, which the decoding kernel then
+        finishes itself; ``q`` is not read."""
+        group = nq // nkv
+        if projection is not None:
+            self.attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
+                                 projection=projection)
+            return
+        if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, group):
+            runs = _short_and_long(batch, group)
+            if runs is not None:
+                for run in runs:
+                    self._attention_bf16(q, k_pool, v_pool, run, block_table[run.first:run.last], page_size, out, nq, nkv, hd,
+                                         window, scale, workspace)
+                return
+        self._attention_bf16(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace)
+
+    def _attention_bf16(self, q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace):
+        group = nq // nkv
+        if (q.dtype == torch.bfloat16 and self.use_tcgen05_attention and getattr(batch, "max_q_len", 0) * group > 16
+                and tcgen05_attention_supported(hd, group, page_size)):
+            attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=workspace)
+            return
+        if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, nq // nkv):
+            self.attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace)
+            return
+        attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
+                        window, scale, batch.status)
+
+    def decode_attention_splits(self, n_seqs: int, nkv: int, hd: int, group: int, max_seq_len: int, dtype) -> int:
+        """How many blocks share the keys of a (sequence, kv head) when ``n_seqs`` sequences decode one token each:
+        the one shape of a decode step's launches that follows the sequences' lengths."""
+        if dtype != torch.bfloat16 or not flash_supported(hd, group):
+            return 1
+        return flash_splits(n_seqs, nkv, max_seq_len)
+
+
+# Calls without an engine (tests of single kernels, parts bound by hand) take this one: the fixed rule, no tuning.
+default = Kernels("measured")
+linear, linear_bf16, attention = default.linear, default.linear_bf16, default.attention
+prefers_tcgen05, prefers_fused_swiglu = default.prefers_tcgen05, default.prefers_fused_swiglu
+decode_takes_projection = default.decode_takes_projection

@@ -37,13 +37,12 @@ class ModelSpec(Part):
         return out
 
     def cache_specs(self) -> dict:
-        """cache id -> CacheSpec of the run that writes it (the first that names it)."""
+        """cache id -> CacheSpec of the run that writes it (the first that names it).  The block says what it
+        remembers (``cache_specs()``); the schedule entry names one id for each."""
         out = {}
         for call in self.schedule:
-            if call.cache not in out:
-                spec = self.blocks[call.layer].mixer.cache_spec()
-                if spec is not None:
-                    out[call.cache] = spec
+            for cid, spec in zip(call.cache_ids(), self.blocks[call.layer].cache_specs()):
+                out.setdefault(cid, spec)
         return out
 
     def check_schedule(self) -> None:
@@ -51,14 +50,21 @@ class ModelSpec(Part):
         for call in self.schedule:
             if not 0 <= call.layer < len(self.blocks):
                 raise ValueError(f"schedule names layer {call.layer}, the model has {len(self.blocks)}")
-            spec = self.blocks[call.layer].mixer.cache_spec()
-            if call.cache in writer:
-                first = self.blocks[writer[call.cache]].mixer.cache_spec()
-                if spec is None or first is None or spec.group_key() != first.group_key():
-                    raise ValueError(f"layer {call.layer} cannot read cache {call.cache}: its needs differ "
-                                     f"from those of layer {writer[call.cache]} which writes it")
-            else:
-                writer[call.cache] = call.layer
+            specs, ids = self.blocks[call.layer].cache_specs(), call.cache_ids()
+            # (a block that remembers nothing may still be given an id: it is not used)
+            if specs and len(ids) != len(specs):
+                raise ValueError(f"layer {call.layer} remembers {len(specs)} things, its schedule entry names "
+                                 f"{len(ids)} caches")
+            if len(set(ids)) != len(ids):
+                raise ValueError(f"the schedule entry of layer {call.layer} names a cache twice")
+            for cid, spec in zip(ids, specs):
+                if cid in writer:
+                    first = writer[cid][1]
+                    if spec.group_key() != first.group_key():
+                        raise ValueError(f"layer {call.layer} cannot read cache {cid}: its needs differ "
+                                         f"from those of layer {writer[cid][0]} which writes it")
+                else:
+                    writer[cid] = (call.layer, spec)
 
 
 def default_schedule(n_layers: int) -> list:

@@ -1,5 +1,5 @@
-from .base import (BuildContext, CacheSpec, FeedForward, LayerCall, Mixer, Norm, ParamSpec, Part,
+from .base import (BuildContext, CacheSpec, DecodeShape, FeedForward, LayerCall, Mixer, Norm, ParamSpec, Part,
                    PositionEncoding)
 
-__all__ = ["BuildContext", "CacheSpec", "FeedForward", "LayerCall", "Mixer", "Norm", "ParamSpec", "Part",
+__all__ = ["BuildContext", "CacheSpec", "DecodeShape", "FeedForward", "LayerCall", "Mixer", "Norm", "ParamSpec", "Part",
            "PositionEncoding"]

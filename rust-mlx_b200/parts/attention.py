@@ -40,6 +40,11 @@ class AttentionMixer(Mixer):
     def cache_spec(self):
         return CacheSpec("paged", kv_heads=self.kv_heads, head_dim=self.head_dim, window=self.window)
 
+    def graph_key(self, shape):
+        # the one launch shape of a decode step that follows the lengths: into how many blocks the keys are split
+        return (self.ctx.ops.decode_attention_splits(shape.n_seqs, self.kv_heads, self.head_dim, self.heads // self.kv_heads,
+                                                     shape.max_seq_len, self.ctx.dtype),)
+
     def param_specs(self):
         p, hd = self.prefix, self.head_dim
         specs = [ParamSpec(f"{p}.q_proj.weight", (self.heads * hd, self.width)),

@@ -79,6 +79,15 @@ class BuildContext:
     tap: object = None
 
 
+@dataclass(frozen=True)
+class DecodeShape:
+    """What is known of a decode step (every sequence brings one token) before it is laid out: how many
+    sequences (spare places of a padded graph included) and the longest sequence's length after the step."""
+
+    n_seqs: int
+    max_seq_len: int
+
+
 class Part:
     """Base of mixers, feed-forwards, norms, position encodings, embeddings and heads.
 
@@ -89,6 +98,18 @@ class Part:
     says so; one part that is not keeps the whole model on plain launches."""
 
     graph_safe = False
+
+    def graph_key(self, shape: DecodeShape) -> tuple:
+        """What, besides the number of sequences, decides which kernels with which launch shapes this part's
+        ``forward`` issues for a decode step of ``shape`` (an attention mixer: into how many blocks it splits the
+        keys, which follows the longest sequence).  A captured step is replayed only for steps with equal keys
+        of all parts.  Most parts launch the same whatever the lengths: the empty tuple."""
+        return ()
+
+    def cache_specs(self) -> list:
+        """What this part and the parts under it remember per request: one ``CacheSpec`` for each cache that a
+        schedule entry has to name for it, in a fixed order (a block of one attention mixer: one)."""
+        return []
 
     def param_specs(self) -> list:
         return []
@@ -157,6 +178,10 @@ class Mixer(Part):
     def cache_spec(self) -> Optional[CacheSpec]:
         return None
 
+    def cache_specs(self) -> list:
+        spec = self.cache_spec()
+        return [] if spec is None else [spec]
+
     def forward(self, x: torch.Tensor, batch, cache):
         raise NotImplementedError
 
@@ -174,7 +199,13 @@ class LayerCall:
 
     The first entry that names a cache writes it; a later entry with the same cache
     reads what the first wrote and writes nothing.  A block may appear in several
-    entries (it then runs more than once with the same weights)."""
+    entries (it then runs more than once with the same weights).  ``cache`` is one id,
+    or a tuple of ids for a block that remembers several things (one id for each entry
+    of the block's ``cache_specs()``, in that order; the block's ``forward`` then gets a
+    tuple of views)."""
 
     layer: int
-    cache: int
+    cache: object
+
+    def cache_ids(self) -> tuple:
+        return tuple(self.cache) if isinstance(self.cache, (tuple, list)) else (self.cache,)

@@ -20,6 +20,9 @@ class PreNormBlock(Part):
     def children(self):
         return [self.norm1, self.mixer, self.norm2, self.ffn]
 
+    def cache_specs(self):
+        return self.mixer.cache_specs()
+
     def forward(self, h, pending, batch, cache):
         tap = self.ctx.tap
         h, x = self.norm1.forward(h, pending)

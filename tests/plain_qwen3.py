@@ -142,7 +142,7 @@ def rope(x, positions, theta, rotary_dim, inv_freq=None):
     j = torch.arange(half, dtype=F, device=x.device)
     if inv_freq is None:
         inv_freq = (theta ** (-2.0 * j / rotary_dim)).to(torch.float32)
-    angle = (positions.to(device=x.device, dtype=torch.float32)[:, None] * inv_freq[None, :]).to(F)   # [T, half]
+    angle = (positions.to(device=x.device, dtype=torch.float32)[:, None] * inv_freq.to(x.device)[None, :]).to(F)   # [T, half]
     cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
     a, b = x[..., :half], x[..., half:rotary_dim]
     out = x.clone()

@@ -21,24 +21,34 @@ SHAPE_8B = dict(
 LENGTHS = [150, 33, 70, 9]
 
 
-def engine_and_weights(dtype, tokens):
+def engine_and_weights(dtype, tokens, **options):
     from rust_mlx_b200.config import Qwen3Config
     from rust_mlx_b200.engine import Engine
     from rust_mlx_b200.registry import build_model_spec
     from rust_mlx_b200.weights.random_init import random_tensors
     cfg = Qwen3Config.from_dict(SHAPE_8B)
-    eng = Engine(cfg, dtype=dtype, random_weights=True, seed=5, max_tokens=tokens, page_size=64, max_requests=4)
+    eng = Engine(cfg, dtype=dtype, random_weights=True, seed=5, max_tokens=tokens, page_size=64, max_requests=4, **options)
     # the same tensors again, by name, for the plain implementation (drawn from (seed, name), so they are equal)
     held = torch.bfloat16 if dtype == "bfloat16" else torch.float32
     tensors = random_tensors(build_model_spec(cfg).all_param_specs(), 5, held, "cuda:0")
     return eng, tensors
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_layer_sizes_of_qwen3_8b(dtype):
+@pytest.mark.parametrize("dtype, tuned", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+def test_layer_sizes_of_qwen3_8b(dtype, tuned):
+    """``tuned``: the engine times its tcgen05 product against the library's on these two layers' weights when it
+    starts (as it does at full depth, where a shape's weights hold far more than the threshold lowered here) and
+    runs with what it chose: q/k/v and output projections on the tcgen05 kernel with the tuned number of K
+    slices, the choice changing with the padded row count.  The same bound holds, and an engine given the first
+    one's table makes the same choices and gives the same bits."""
     reqs = {f"r{i}": p for i, p in enumerate(tiny.prompts(SHAPE_8B["vocab_size"], LENGTHS, seed=3))}
     steps_by_way = {w: getattr(replay, w)(reqs) for w in ("whole", "tail_one_by_one", "portions", "mixed")}
-    eng, tensors = engine_and_weights(dtype, 1024)
+    eng, tensors = engine_and_weights(dtype, 1024, **(dict(tuning="auto", tune_min_bytes=1e6) if tuned else dict(tuning="measured")))
+    if tuned:
+        table = eng.tuning_table()
+        assert len(table["tcgen05"]) >= 12 and len(table["slices"]) >= 9 and any(table["tcgen05"].values()), table
+    else:
+        assert not eng.tuning_table()["tcgen05"]
     rounding = "bfloat16" if dtype == "bfloat16" else None
     w = {k: v.to(torch.float64) for k, v in tensors.items()}
     # sharpen attention as the tiny tests do (scores of random weights are all near zero otherwise)
@@ -62,3 +72,17 @@ def test_layer_sizes_of_qwen3_8b(dtype):
         for way in ("tail_one_by_one", "portions", "mixed"):
             for rid in reqs:
                 assert torch.equal(results[way][rid], results["whole"][rid]), (way, rid)
+    if tuned:
+        import json
+        del eng
+        again, _ = engine_and_weights(dtype, 1024, tuning=json.loads(json.dumps(table)))
+        for block in again.spec.blocks:
+            block.mixer.q_norm.mul_(2.0)
+            block.mixer.k_norm.mul_(2.0)
+        assert again.tuning_table() == table
+        got = replay.run_engine(again, steps_by_way["tail_one_by_one"])
+        for rid in reqs:
+            assert torch.equal(got[rid], results["tail_one_by_one"][rid]), rid
+        # another engine in the same process knows nothing of it
+        from rust_mlx_b200.kernels import ops
+        assert not ops.default.tuned and not ops.Kernels("auto").tuned

@@ -15,7 +15,7 @@ def context(dtype=torch.float32):
     from rust_mlx_b200.engine.workspace import Workspace
     from rust_mlx_b200.kernels import ops
     from rust_mlx_b200.parts import BuildContext
-    return BuildContext(DEV, dtype, ops, Workspace(DEV))
+    return BuildContext(DEV, dtype, ops.default, Workspace(DEV))
 
 
 def bind(part, seed=0, dtype=torch.float32):

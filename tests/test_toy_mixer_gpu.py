@@ -238,3 +238,94 @@ def test_toy_routed_feed_forward_and_unrotated_layers(tmp_path):
                 assert tiny.max_abs(got[rid], ref[rid]) < 5e-5, (way, rid)
     finally:
         unregister_architecture("ToyRoutedForCausalLM")
+
+
+def test_toy_block_that_remembers_two_things(tmp_path):
+    """A block defined here with two stateful sub-layers (attention over pages and a running average in a state
+    slot, side by side): it says so in ``cache_specs()``, its schedule entry names one cache id for each, and its
+    ``forward`` gets a tuple of views.  Built, stepped (whole, in portions, mixed) and generated from without a
+    change to the framework's files."""
+    import replay
+    from rust_mlx_b200.config import Qwen3Config
+    from rust_mlx_b200.engine import Engine
+    from rust_mlx_b200.models.qwen3 import build_qwen3
+    from rust_mlx_b200.parts import LayerCall, Part
+    from rust_mlx_b200.registry import register_architecture, unregister_architecture
+    from rust_mlx_b200.weights import write_random_model
+    Toy = make_toy()
+
+    class TwoMemoryBlock(Part):
+        def __init__(self, inner, toy):
+            self.inner, self.toy = inner, toy          # a pre-norm block of the framework and the second sub-layer
+
+        def children(self):
+            return [self.inner, self.toy]
+
+        def cache_specs(self):
+            return self.inner.cache_specs() + self.toy.cache_specs()
+
+        def forward(self, h, pending, batch, cache):
+            pages, slots = cache
+            b = self.inner
+            h, x = b.norm1.forward(h, pending)
+            a = b.mixer.forward(x, batch, pages) + self.toy.forward(x, batch, slots)
+            h, x = b.norm2.forward(h, a)
+            return h, b.ffn.forward(x, batch)
+
+    def build(config):
+        spec = build_qwen3(config)
+        for i in (0, 2):
+            spec.blocks[i] = TwoMemoryBlock(spec.blocks[i], Toy(f"model.layers.{i}.toy", config.hidden_size, 0.6))
+        spec.schedule = [LayerCall(0, (0, 10)), LayerCall(1, 1), LayerCall(2, (2, 12))]
+        spec.check_schedule()
+        return spec
+
+    def plain_logits(folder, ids):
+        config, tensors = plain.read_folder(folder)
+        w = plain.prepare_weights(config, tensors, None)
+        eps, T = config["rms_norm_eps"], len(ids)
+        h = plain.embedding(w["model.embed_tokens.weight"], ids)
+        for i in range(3):
+            p = f"model.layers.{i}"
+            x = plain.rms_norm(h, w[p + ".input_layernorm.weight"], eps)
+            h = h + plain.attention(x, w, p + ".self_attn", config, torch.arange(T), 0, lambda t: t)
+            if i in (0, 2):
+                s, rows = torch.zeros(config["hidden_size"], dtype=torch.float64), []
+                for t in range(T):
+                    s = 0.6 * s + x[t]
+                    rows.append(s @ w[p + ".toy.mix.weight"].t())
+                h = h + torch.stack(rows)
+            h = h + plain.swiglu_mlp(plain.rms_norm(h, w[p + ".post_attention_layernorm.weight"], eps), w, p + ".mlp", lambda t: t)
+        return plain.linear(plain.rms_norm(h, w["model.norm.weight"], eps), w["lm_head.weight"])
+
+    register_architecture("ToyTwoMemoriesForCausalLM", Qwen3Config, build)
+    try:
+        raw = dict(tiny.TINY_B, architectures=["ToyTwoMemoriesForCausalLM"])
+        folder = str(tmp_path / "two")
+        write_random_model(Qwen3Config.from_dict(raw), folder, seed=5, store_dtype="float32")
+        reqs = {f"r{i}": p for i, p in enumerate(tiny.prompts(509, [12, 31, 5, 20], seed=8))}
+        ref = {rid: plain_logits(folder, ids).float() for rid, ids in reqs.items()}
+        for way in ("whole", "portions", "mixed"):
+            steps = getattr(replay, way)(reqs, **({"live": 3} if way == "mixed" else {}))
+            eng = Engine(folder, dtype="float32", max_tokens=replay.tokens_needed(steps, 8), page_size=8, max_requests=3)
+            assert sorted(g.spec.kind for g in eng.pools.groups) == ["paged", "state"]
+            assert len(eng.pools.paged_groups[0].cache_ids) == 3 and len(eng.pools.state_groups[0].cache_ids) == 2
+            got = replay.run_engine(eng, steps)
+            for rid in reqs:
+                assert tiny.max_abs(got[rid], ref[rid]) < 2e-5, (way, rid)
+        for grp in eng.pools.state_groups:
+            grp.state.fill_(9.0)
+        out = eng.generate([reqs["r2"], reqs["r0"]], max_tokens=4, prefill_chunk=5)
+        for p, toks in zip([reqs["r2"], reqs["r0"]], out):
+            ids = list(p)
+            for t in toks:
+                logits = plain_logits(folder, ids)[-1]
+                assert logits[t] >= logits.max() - 1e-5
+                ids.append(t)
+        # a schedule entry that names the wrong number of caches is refused when the model is built
+        with pytest.raises(ValueError, match="remembers 2"):
+            spec = build(Qwen3Config.from_dict(raw))
+            spec.schedule[0] = LayerCall(0, 0)
+            spec.check_schedule()
+    finally:
+        unregister_architecture("ToyTwoMemoriesForCausalLM")
