@@ -37,10 +37,10 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
-// Polls until the phase with the given parity has completed; false if it gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Polls until the phase with the given parity has completed; false if it gave up after `limit` polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit) {
     const uint32_t addr = smem_addr(bar);
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -103,6 +103,8 @@ struct GemmParams {
     unsigned int* counters;  // [n_tiles], zero between launches (splits > 1)
     int* status;
     int M, N, K, ldc, splits, k_blocks, out_float;
+    uint32_t spin_limit;     // polls after which a wait on a barrier gives up (SPIN_LIMIT; a test passes a small number)
+    int no_loads;            // test only: the producer issues no copies, so that every wait for a tile runs out
     int dependent;           // launched as a programmatic dependent: wait for the grid before before reading A
     int epilogue;            // 0: C = product.  1: the tile's rows are 64 gate rows then their 64 up rows;
                              //    C[M, N / 2] = silu(gate) * up, formed in float and rounded once.
@@ -167,7 +169,8 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
     tcgen05_fence_after();
     const uint32_t tmem_acc = tmem_base_smem;
 
-    if (warp == 0 && lane == 0) {
+    const uint32_t spin_limit = p.spin_limit;
+    if (warp == 0 && lane == 0 && !p.no_loads) {
         // ---- producer: stream W and A tiles through the ring.  The weights do not depend on the kernel
         // before this one, so the first stages' W tiles are on their way before the wait for that kernel.
         const int ahead = n_kb < STAGES ? n_kb : STAGES;
@@ -180,7 +183,7 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
             tma_load_2d(tiles + i * STAGE_BYTES + W_BYTES, &map_a, &full_bar[i], (kb_begin + i) * TILE_K, 0);
         for (int i = ahead; i < n_kb; ++i) {
             const int s = i % STAGES, round = i / STAGES;
-            if (!mbar_wait(&empty_bar[s], (round - 1) & 1)) { atomicExch(&s_failed, 1); break; }
+            if (!mbar_wait(&empty_bar[s], (round - 1) & 1, spin_limit)) { atomicExch(&s_failed, 1); break; }
             unsigned char* dst = tiles + s * STAGE_BYTES;
             mbar_expect_tx(&full_bar[s], STAGE_BYTES);
             const int k0 = (kb_begin + i) * TILE_K;
@@ -192,7 +195,7 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
         const uint32_t idesc = umma_idesc(MPAD);
         for (int i = 0; i < n_kb; ++i) {
             const int s = i % STAGES, round = i / STAGES;
-            if (!mbar_wait(&full_bar[s], round & 1)) { atomicExch(&s_failed, 1); break; }
+            if (!mbar_wait(&full_bar[s], round & 1, spin_limit)) { atomicExch(&s_failed, 1); break; }
             tcgen05_fence_after();
             const uint32_t w_addr = smem_addr(tiles + s * STAGE_BYTES), a_addr = w_addr + W_BYTES;
 #pragma unroll
@@ -205,7 +208,7 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
     __syncwarp();
 
     // ---- epilogue: every thread owns one weight row of the tile
-    bool ok = n_kb == 0 || mbar_wait(&acc_bar, 0);
+    bool ok = n_kb == 0 || mbar_wait(&acc_bar, 0, spin_limit);
     if (!ok) atomicExch(&s_failed, 1);
     tcgen05_fence_after();
     const int n = tile * TILE_N + warp * 32 + lane;
@@ -442,7 +445,7 @@ RMX_API long long rmx_gemm_tcgen05_scratch_floats(int M, int N, int splits) {
 namespace {
 int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
                      int out_float, int splits, float* partial, unsigned int* counters, int* status,
-                     int flags, cudaStream_t s) {
+                     int flags, cudaStream_t s, uint32_t spin_limit = SPIN_LIMIT, int no_loads = 0) {
     if (M == 0 || N == 0) return 0;
     RMX_REQUIRE(rmx_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05: M=%d N=%d K=%d is outside 1..64 rows, K %% 8 == 0", M, N, K);
     RMX_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0,
@@ -465,7 +468,7 @@ int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K,
     GemmParams p;
     p.c = C; p.partial = partial; p.counters = counters; p.status = status;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
-    p.dependent = 0; p.epilogue = epilogue;
+    p.dependent = 0; p.epilogue = epilogue; p.spin_limit = spin_limit; p.no_loads = no_loads;
     // stages sized so that two blocks fit an SM: more blocks in flight smooth the last wave
     if (mpad == 16) return launch<16, 6>(mw, ma, p, n_tiles, s, cluster, dependent);
     if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s, cluster, dependent);
@@ -479,6 +482,19 @@ RMX_API int rmx_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N
                              int out_float, int splits, float* partial, unsigned int* counters, int* status,
                              int flags, void* stream) {
     return gemm_tcgen05_run(A, W, C, M, N, K, lda, ldw, ldc, out_float, splits, partial, counters, status, flags, (cudaStream_t)stream);
+}
+
+// For tests of the give-up path: the same kernel with the same arguments, except that its producer issues no
+// copies and every wait gives up after `spin_limit` polls.  No tile ever arrives, so the thread that issues the
+// MMAs gives up at its first wait; the block records status 3, writes no output, frees its tensor memory, joins
+// its cluster's barriers (or counts itself at the tile's counter, which is zero again afterwards) and returns.
+// Nothing is left in flight: there was no copy and no MMA.
+RMX_API int rmx_gemm_tcgen05_wait_probe(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw,
+                                        int ldc, int out_float, int splits, float* partial, unsigned int* counters,
+                                        int* status, int flags, int spin_limit, void* stream) {
+    RMX_REQUIRE(spin_limit >= 1 && spin_limit <= (1 << 20), "gemm_tcgen05_wait_probe: a limit of 1 to 2^20 polls, got %d", spin_limit);
+    return gemm_tcgen05_run(A, W, C, M, N, K, lda, ldw, ldc, out_float, splits, partial, counters, status, flags & ~2,
+                            (cudaStream_t)stream, (uint32_t)spin_limit, 1);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -564,7 +580,7 @@ RMX_API int rmx_gemm_tcgen05_static(const void* A, const void* W, void* C, int M
     GemmParams p;
     p.c = C; p.partial = scratch.partial; p.counters = scratch.counters; p.status = scratch.status;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
-    p.dependent = 0; p.epilogue = 0;
+    p.dependent = 0; p.epilogue = 0; p.spin_limit = SPIN_LIMIT; p.no_loads = 0;
     if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s);
     if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s);
     return launch<64, 4>(mw, ma, p, n_tiles, s);

@@ -391,6 +391,26 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
     return status
 
 
+def gemm_tcgen05_wait_probe(a, w, out, status, splits=1, cluster=True, swiglu=False, spin_limit=1000, workspace=None):
+    """For tests: the tcgen05 product's kernel launched so that its waits run out (no tile is ever copied, every
+    wait gives up after ``spin_limit`` polls).  It must return, leave status 3 in ``status`` and ``out`` untouched."""
+    lib = kernels_library()
+    m, k = a.shape
+    n = w.shape[0]
+    ws = workspace if workspace is not None else _own_workspace()
+    partial = counters = None
+    if splits > 1:
+        partial = ws.get("gemm_partial", (lib.rmx_gemm_tcgen05_scratch_floats(c_int(m), c_int(n), c_int(splits)),), torch.float32)
+        counters = ws.get_zeroed("gemm_counters", (max(4096, -(-n // 128)),), torch.int32)
+    check(lib.rmx_gemm_tcgen05_wait_probe(
+        _ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(out, name="out"), c_int(m), c_int(n), c_int(k),
+        c_int(a.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0),
+        c_int(splits), _ptr(partial), _ptr(counters), _ptr(status, torch.int32, "status"),
+        c_int((1 if cluster else 0) | (4 if swiglu else 0)), c_int(spin_limit), _stream()))
+    _launched()
+    return counters
+
+
 def tcgen05_attention_supported(hd: int, group: int, page_size: int) -> bool:
     return bool(kernels_library().rmx_attention_tcgen05_supports(c_int(hd), c_int(group), c_int(page_size)))
 

@@ -826,3 +826,52 @@ def test_decoding_attention_that_finishes_the_projection_itself(nq, nkv, page, n
     assert torch.equal(out1, out2)
     # (bit patterns: slots that no request holds are NaN in both)
     assert torch.equal(k1.view(torch.int16), k2.view(torch.int16)) and torch.equal(v1.view(torch.int16), v2.view(torch.int16))
+
+
+@pytest.mark.parametrize("m, n, k, splits, cluster", [(8, 4096, 4096, 4, True), (8, 1000, 2048, 3, False), (40, 640, 512, 1, True),
+                                                      (16, 4096, 12288, 6, True)])
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_kernel_usable(m, n, k, splits, cluster):
+    """The give-up path of the tcgen05 product: its kernel is launched so that no tile ever arrives and every wait
+    on a barrier gives up after 1,000 polls.  It must return (not hang, not trap), report status 3, write nothing,
+    free its tensor memory and leave the tiles' split-K counters at zero; the next ordinary product on the same
+    stream, with the same scratch, is right."""
+    a = rnd((m, k), torch.bfloat16, 1.0, 1)
+    w = rnd((n, k), torch.bfloat16, k ** -0.5, 2)
+    out = torch.full((m, n), 7.0, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    counters = ops().gemm_tcgen05_wait_probe(a, w, out, status, splits=splits, cluster=cluster, spin_limit=1000)
+    torch.cuda.synchronize()
+    assert status.item() == 3
+    assert bool((out == 7.0).all())
+    if counters is not None:
+        assert int(counters.abs().sum().item()) == 0
+    status.zero_()
+    for _ in range(3):          # tensor memory was given back: blocks of later launches still get theirs
+        ops().gemm_tcgen05(a, w, out, status=status, splits=splits, cluster=cluster)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    want = a.double() @ w.double().t()
+    assert (out.double() - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+
+
+def test_the_engine_raises_when_a_kernel_reports_a_wait_that_ran_out(tmp_path):
+    """The status word reaches the host: a step after which the word holds 3 raises, commits no lengths, and the
+    engine steps on."""
+    import tiny
+    from rust_mlx_b200.engine import Engine, EngineError
+    raw, page = tiny.CONFIGS["D"]
+    folder = tiny.make_folder(tmp_path, raw, seed=2)
+    eng = Engine(folder, dtype="bfloat16", max_tokens=256, page_size=page, max_requests=2)
+    ids = tiny.prompts(raw["vocab_size"], [20], seed=1)[0]
+    first = eng.step([("a", ids[:10], [9])]).cpu()
+    a = rnd((8, 512), torch.bfloat16, 1.0, 1)
+    w = rnd((256, 512), torch.bfloat16, 0.05, 2)
+    ops().gemm_tcgen05_wait_probe(a, w, torch.empty(8, 256, dtype=torch.bfloat16, device=DEV), eng._status, splits=2)
+    with pytest.raises(EngineError, match="gave up waiting"):
+        eng.step([("a", ids[10:], [9])])
+    assert eng.length("a") == 10                      # the step was not committed
+    again = eng.step([("a", ids[10:], [9])])           # ... and runs when asked again
+    eng.release("a")
+    whole = eng.step([("b", ids, [9, 19])], ["b"]).cpu()
+    assert torch.equal(whole[0], first[0])
+    assert (whole[1] - again[0].cpu()).abs().max().item() < 2e-2
