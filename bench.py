@@ -2,15 +2,23 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
 
-The default run has the layer sizes of the Qwen3-8B shape (BASELINE.json configs[2]) with
-random weights in bfloat16: decode at batch 8 from a context of 2,048 tokens per request.
-It prints ONE JSON line.  ``value`` is decoded tokens per second, timed on the device with
-CUDA events over exactly K steps (each step: upload of the step's ids and tables from
-pinned memory, the model, greedy sampling).  ``e2e`` is the same through the Python entry
-point (``Engine.generate``): host token ids in, host token ids out, one host
-synchronisation per step.  ``prefill`` is one 2,048-token prompt in one step; ``roofline``
-is the decode step's bytes (every weight once plus the live requests' cache) over its time.
-Weights (15 GB) are far larger than L2, so no flush is needed between steps.
+The default run has the layer sizes of Qwen3-8B with random weights in bfloat16: decode at
+batch 8 from a context of 2,048 tokens per request.  It prints ONE JSON line.  ``value`` is
+decoded tokens per second, timed on the device with CUDA events over exactly K steps (each
+step: upload of the step's ids and tables from pinned memory, the model, greedy sampling).
+``e2e`` is the same through the Python entry point (``Engine.generate``): host token ids in,
+host token ids out, one host synchronisation per step; the ids it generated are then compared
+with those of its warm-up run and of a run without graphs and in lockstep (``checked``), as
+the reference's benchmarks compare every timed run's ids with the first run's
+(src/bin/batch-bench.rs:147-151).  ``prefill`` is one 2,048-token prompt in one step;
+``roofline`` is the decode step's bytes (every weight once plus the live requests' cache)
+over its time.  Weights (15 GB) are far larger than L2, so no flush is needed between steps.
+
+``--per-kernel`` instead times the phases of one decode step one by one (CUDA events between
+the kernels, inside a captured graph, so without host gaps and without overlap between
+neighbouring kernels) and prints bytes, time and fraction of the memory peak of each: a
+synchronised diagnostic, not shares of the natural run time (the reference's
+src/bin/profile.rs:22-36 does the same per phase).
 """
 import argparse
 import json
@@ -28,7 +36,7 @@ QWEN3_8B = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidd
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
                 max_position_embeddings=4096)
-# the other layer sizes BASELINE.json names (configs[3] and configs[4]); the default run is configs[2]
+# the Qwen3-4B and Qwen3-32B layer sizes beside the default
 SHAPES = {
     "qwen3-8b": QWEN3_8B,
     "qwen3-4b": dict(QWEN3_8B, hidden_size=2560, intermediate_size=9728, tie_word_embeddings=True),
@@ -114,7 +122,6 @@ class DecodeRun:
 
     def __init__(self, engine, batch, context):
         import torch
-        from rust_mlx_b200.sampling import Sampler
         self.e, self.batch, self.context, self.torch = engine, batch, context, torch
         self.rids = list(range(10_000, 10_000 + batch))
         self.len = context
@@ -122,7 +129,6 @@ class DecodeRun:
             engine.pools.open(r)
             engine.pools.table.reserve(r, context)
             engine.pools.table.commit(r, context)
-        self.sampler = Sampler(engine.device)
         g = torch.Generator().manual_seed(batch)
         self.ids = torch.randint(0, engine.vocab_size, (4096, batch), generator=g).tolist()
         self.out = torch.empty(batch, dtype=torch.int32, device=engine.device)
@@ -140,7 +146,7 @@ class DecodeRun:
         else:
             batch = build_batch(seqs, e.pools, e.device, e._status, e.vocab_size)
             logits = e.forward(batch)
-            self.sampler.sample(logits, [0.0] * self.batch, 0, self.rids, [0] * self.batch, out=self.out)
+            e.ops.sample(logits, None, None, self.out)
         self.len += 1
         self.n += 1
         for r in self.rids:
@@ -206,11 +212,23 @@ def time_e2e(engine, batch, new_tokens):
     import torch
     g = torch.Generator().manual_seed(7)
     prompts = torch.randint(0, engine.vocab_size, (batch, CONTEXT), generator=g).tolist()
+    opts = dict(ignore_eos=True, prefill_chunk=2048, max_batch_tokens=batch * CONTEXT)
     # warm-up with the same shapes: the decode step of this batch size is captured into its graph here
-    engine.generate(prompts, max_tokens=3, ignore_eos=True, prefill_chunk=2048, max_batch_tokens=batch * CONTEXT)
-    r = engine.generate_detailed(prompts, max_tokens=new_tokens, ignore_eos=True, prefill_chunk=2048,
-                                 max_batch_tokens=batch * CONTEXT)
+    warm = engine.generate(prompts, max_tokens=3, **opts)
+    r = engine.generate_detailed(prompts, max_tokens=new_tokens, **opts)
     decoded = r.generated_tokens - batch
+    # what was generated: the timed run's ids begin with the warm-up run's, and a run of plain launches in
+    # lockstep (no graphs, no step launched ahead) generates the same ids
+    graphs, engine.graphs = engine.graphs, None
+    try:
+        plain = engine.generate(prompts, max_tokens=new_tokens, run_ahead=False, **opts)
+    finally:
+        engine.graphs = graphs
+    checked = all(len(t) == new_tokens for t in r.tokens) and all(t[:3] == w for t, w in zip(r.tokens, warm)) and plain == r.tokens
+    if not checked:
+        first = next(((i, j) for i, (x, y) in enumerate(zip(r.tokens, plain)) for j, (u, v) in enumerate(zip(x, y)) if u != v), None)
+        print(f"bench.py: the timed run's ids differ from the check runs' (first difference at request, token {first})",
+              file=sys.stderr)
     # bytes per decode step: ids, positions, sequence indices, starts, lengths, slots, rows, block tables up; tokens + status down
     # a captured decode step uploads one buffer of fixed layout: ids, positions, sequence indices, starts, lengths,
     # slots, rows, temperatures, uniforms and block tables of the context limit
@@ -219,7 +237,85 @@ def time_e2e(engine, batch, new_tokens):
     b = bucket(batch)
     h2d = 4 * BatchLayout(b, b, b, [engine.max_context // PAGE for _ in engine.pools.paged_groups]).total
     d2h = 4 * (b + 1)
-    return decoded / r.decode_seconds, h2d, d2h
+    return decoded / r.decode_seconds, h2d, d2h, checked
+
+
+def per_kernel(engine, raw, a, pk):
+    """One decode step of ``a.batch`` requests at CONTEXT tokens, captured with an event after every phase of every
+    layer; replayed ``a.steps`` times.  Prints a table (standard error) and one JSON line."""
+    import torch
+    from rust_mlx_b200.engine.batch import SequenceInput, build_batch
+    run = DecodeRun(engine, a.batch, CONTEXT)
+    try:
+        e = engine
+        for r in run.rids:
+            e.pools.table.reserve(r, run.len + 1)
+        seqs = [SequenceInput(r, run.len, [run.ids[0][i]], [0]) for i, r in enumerate(run.rids)]
+        batch = build_batch(seqs, e.pools, e.device, e._status, e.vocab_size)
+        out = torch.empty(a.batch, dtype=torch.int32, device=e.device)
+        marks = []          # (phase that ended here, event)
+
+        def tap(name, tensor):
+            ev = torch.cuda.Event(enable_timing=True, external=True)
+            ev.record()
+            marks.append((name, ev))
+
+        def step():
+            marks.clear()
+            tap("start", None)
+            logits = e.forward(batch)
+            e.ops.sample(logits, None, None, out)
+            tap("head", None)
+        e.forward(batch)                      # buffers reach their size
+        torch.cuda.synchronize()
+        e._ctx.tap = tap
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+        finally:
+            e._ctx.tap = None
+        # what ends at a mark, by the mark's name: the kernels between it and the mark before
+        phase = {"residual": None, "norm1": "add + norm", "qkv": "q/k/v product", "q_rot": "norm + rotation + cache write",
+                 "attn_out": "attention", "mixer_out": "output product", "norm2": "add + norm", "ffn_act": "gate/up product + SwiGLU",
+                 "ffn_out": "down product", "head": "final norm + head + sampling"}
+        total = {}
+        for _ in range(max(a.warmup, 3)):
+            graph.replay()
+        for _ in range(a.steps):
+            graph.replay()
+            torch.cuda.synchronize()
+            last = marks[0][1]
+            for name, ev in marks[1:]:
+                if phase.get(name) is None:
+                    continue            # (the stream before a block's norm: the same place as its norm1 mark)
+                total.setdefault(phase[name], []).append(last.elapsed_time(ev) * 1e3)
+                last = ev
+        h, inter, v = raw["hidden_size"], raw["intermediate_size"], raw["vocab_size"]
+        nq, nkv, hd, layers = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"], a.layers
+        per_layer_bytes = {"q/k/v product": (nq + 2 * nkv) * hd * h * 2, "output product": nq * hd * h * 2,
+                           "gate/up product + SwiGLU": 2 * inter * h * 2, "down product": inter * h * 2,
+                           "attention": a.batch * (CONTEXT + 1) * 2 * nkv * hd * 2,
+                           "add + norm": a.batch * h * (4 + 4 + 2 + 2), "norm + rotation + cache write": a.batch * (nq + 2 * nkv) * hd * 4,
+                           "final norm + head + sampling": v * h * 2 + a.batch * v * 8}
+        rows, step_us = [], 0.0
+        for name, times in total.items():
+            calls = len(times) // a.steps
+            us = sum(times) / a.steps / calls
+            gbs = per_layer_bytes[name] / us / 1e3
+            step_us += us * calls
+            rows.append({"phase": name, "calls_per_step": calls, "us": round(us, 2), "bytes": per_layer_bytes[name],
+                         "gb_per_s": round(gbs, 1), "frac": round(gbs / pk["hbm_gbs"], 3)})
+        print(f"{'phase':34s} {'calls':>5s} {'us each':>9s} {'MB each':>9s} {'GB/s':>8s} {'of peak':>8s}", file=sys.stderr)
+        for r_ in rows:
+            print(f"{r_['phase']:34s} {r_['calls_per_step']:5d} {r_['us']:9.2f} {r_['bytes'] / 1e6:9.2f} {r_['gb_per_s']:8.1f} {r_['frac']:8.3f}",
+                  file=sys.stderr)
+        print(json.dumps({"per_kernel": rows, "step_us_serialised": round(step_us, 1), "batch": a.batch, "context": CONTEXT,
+                          "layers": layers, "shape": a.shape, "peak_gb_per_s": pk["hbm_gbs"], "of": pk["source"],
+                          "note": "events between kernels inside one captured graph: no host gaps, no overlap of neighbours"}))
+        return 0
+    finally:
+        run.close()
 
 
 def continuous(cfg, raw, a):
@@ -258,13 +354,16 @@ def main():
     global CONTEXT, MAX_CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, prefill and e2e")
     ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prefill only (for profiling it)")
+    ap.add_argument("--per-kernel", action="store_true",
+                    help="instead: time the phases of one decode step one by one and print each one's bytes, time and "
+                         "fraction of the memory peak")
     ap.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES), help="layer sizes (default: the Qwen3-8B shape)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when decoding starts")
     ap.add_argument("--continuous", action="store_true",
@@ -296,7 +395,7 @@ def main():
     cfg = Qwen3Config.from_dict(raw)
     if a.continuous:
         return continuous(cfg, raw, a)
-    biggest = 1 if (a.no_points or a.prefill_only) else max(64, a.batch)
+    biggest = 1 if (a.no_points or a.prefill_only or a.per_kernel) else max(64, a.batch)
     cache_tokens = max(biggest, a.batch) * (CONTEXT + 2 * PAGE + a.steps + a.warmup + 64)
     engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE,
                     max_requests=max(biggest, a.batch) + 2, tuning=a.policy)
@@ -304,6 +403,8 @@ def main():
         grp.k_pool.normal_(0, 1)
         grp.v_pool.normal_(0, 1)
     pk = peaks()
+    if a.per_kernel:
+        return per_kernel(engine, raw, a, pk)
     if a.prefill_only:
         pf_ms = time_prefill(engine, PREFILL_TOKENS)
         flops = prefill_flops(raw, a.layers, PREFILL_TOKENS)
@@ -343,8 +444,9 @@ def main():
         flops = prefill_flops(raw, a.layers, PREFILL_TOKENS)
         line["prefill"] = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
                            "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"]}
-        e2e, h2d, d2h = time_e2e(engine, a.batch, max(128, a.steps))
+        e2e, h2d, d2h, checked = time_e2e(engine, a.batch, max(128, a.steps))
         line["e2e"] = {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        line["checked"] = checked
     print(json.dumps(line))
     return 0
 

@@ -89,6 +89,9 @@ class AttentionMixer(Mixer):
         ops.linear(x, self.w_qkv, qkv, ws, batch.status)
         if self.b_qkv is not None:
             ops.add_bias(qkv, self.b_qkv)
+        tap = self.ctx.tap
+        if tap is not None:
+            tap("qkv", qkv)
         if ops.decode_takes_projection(batch, dt, hd, nq // nkv, cache.page_size, self.position.rotary_dim, angles):
             # decoding: the attention kernel norms, rotates and stores its own token while it waits for its keys
             projection = (qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, angles, not cache.read_only)
@@ -97,7 +100,6 @@ class AttentionMixer(Mixer):
                               self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table,
                               cache.page_size, cache.k_pool, cache.v_pool, q, nq, nkv, hd, not cache.read_only,
                               batch.status, angles)
-        tap = self.ctx.tap
         if tap is not None and projection is None:
             tap("q_rot", q)
         o = ws.get("attn_out", (n, nq * hd), dt)

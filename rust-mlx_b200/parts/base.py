@@ -73,7 +73,7 @@ class BuildContext:
     ops: object
     workspace: object
     # ``tap(name, tensor)``, or None: while set, parts hand it their named intermediate tensors (buffers of the
-    # workspace that later layers overwrite, so whoever listens copies).  Names a dense block gives: norm1, q_rot,
+    # workspace that later layers overwrite, so whoever listens copies).  Names a dense block gives: residual, norm1, qkv, q_rot,
     # attn_out, mixer_out, norm2, ffn_act, ffn_out (the reference compares such tensors by name with an oracle's
     # dump, src/bin/trace.rs:4-24).
     tap: object = None

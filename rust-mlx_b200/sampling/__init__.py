@@ -1,4 +1,5 @@
+"""Choosing tokens: the kernel is ``ops.sample`` (greedy and temperature rows in one launch); the uniform numbers of
+temperature sampling come from ``rng.uniform``, keyed by (seed, request, step)."""
 from .rng import uniform
-from .sampler import Sampler
 
-__all__ = ["Sampler", "uniform"]
+__all__ = ["uniform"]

@@ -184,6 +184,8 @@ def attention(x, w, prefix, config, positions, window, rnd, tap=None):
     q = linear(x, w[prefix + ".q_proj.weight"], b(".q_proj.bias"), rnd).reshape(T, nq, hd)   # dense.rs:147,155
     k = linear(x, w[prefix + ".k_proj.weight"], b(".k_proj.bias"), rnd).reshape(T, nkv, hd)  # dense.rs:157-160
     v = linear(x, w[prefix + ".v_proj.weight"], b(".v_proj.bias"), rnd).reshape(T, nkv, hd)  # dense.rs:161-165
+    if tap is not None:
+        tap("qkv", torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1))
     q = rms_norm(q, w[prefix + ".q_norm.weight"], eps)                       # dense.rs:169
     k = rms_norm(k, w[prefix + ".k_norm.weight"], eps)                       # dense.rs:175
     theta = rope_theta(config)

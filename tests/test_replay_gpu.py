@@ -217,7 +217,7 @@ def test_named_intermediates_of_a_step_match_the_plain_implementation(workdir, n
     first = load_file(os.path.join(out, "0.intermediates.safetensors"))
     last = load_file(os.path.join(out, "1.intermediates.safetensors"))
     names = {f"run{i}.{n}" for i in range(raw["num_hidden_layers"])
-             for n in ("residual", "norm1", "q_rot", "attn_out", "mixer_out", "norm2", "ffn_act", "ffn_out")}
+             for n in ("residual", "norm1", "qkv", "q_rot", "attn_out", "mixer_out", "norm2", "ffn_act", "ffn_out")}
     assert set(first) == names
     # (a decoding step with heads of 128 in bfloat16 rotates inside its attention kernel: no q_rot then)
     assert set(last) | {n for n in names if n.endswith("q_rot")} == names
