@@ -12,7 +12,7 @@ tokens of the timed runs as they are generated (the reference prints their text,
 and, like the reference, leaves the report out of standard output (222).  Text
 prompts and chat templates need a tokenizer and are not offered: prompts are
 token ids.  Added: ``--dtype``, ``--temperature``, ``--seed``, ``--random-weights``,
-``--page-size``, ``--cache-tokens``, ``--max-batch-tokens``; ``--prompt-ids`` may
+``--page-size``, ``--cache-tokens``, ``--max-batch-tokens``, ``--tuning``; ``--prompt-ids`` may
 also hold an array of arrays, which are then generated as one batch.
 """
 from __future__ import annotations
@@ -41,6 +41,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--cache-tokens", type=int, default=0, help="tokens the cache holds (default: what the prompts need)")
     ap.add_argument("--max-batch-tokens", type=int, default=0, help="token budget of a step (default: the prefill chunk)")
+    ap.add_argument("--tuning", default="auto",
+                    help="which products of few rows take the tcgen05 kernel: auto (timed at start), measured (a fixed "
+                         "rule), all, none, or the JSON report of an earlier run whose choices are made again")
     return ap
 
 
@@ -65,8 +68,12 @@ def main(argv=None) -> int:
     page = a.page_size
     need = sum(-(-(len(p) + a.max_tokens) // page) * page for p in prompts)
     t0 = time.time()
+    tuning = a.tuning
+    if tuning not in ("auto", "measured", "all", "none"):
+        with open(tuning) as fh:
+            tuning = json.load(fh)["runtime"]["tuning"]
     engine = Engine(a.model, dtype=a.dtype, random_weights=a.random_weights, seed=a.seed, page_size=page,
-                    max_tokens=a.cache_tokens or need, max_requests=max(len(prompts), 1), verbose=True)
+                    max_tokens=a.cache_tokens or need, max_requests=max(len(prompts), 1), verbose=True, tuning=tuning)
     load_seconds = time.time() - t0
     print(f"weights ready: {load_seconds:.3f}s, {torch.cuda.memory_allocated() / 2**30:.2f} GiB active",
           file=sys.stderr)
@@ -95,14 +102,16 @@ def main(argv=None) -> int:
                 "prefill_tokens_per_second": r.prompt_tokens / r.prefill_seconds if r.prefill_seconds > 0 else None,
                 "decode_tokens_per_second": tps, "inter_token_seconds": r.step_seconds, "steps": r.steps,
                 "preemptions": r.preemptions, "peak_memory_bytes": torch.cuda.max_memory_allocated()})
+    from .environment import capture
     report = {
-        "environment": {"device": torch.cuda.get_device_name(), "torch": torch.__version__,
-                        "cuda": torch.version.cuda},
+        "environment": capture(),
         "model": a.model,
         "runtime": {"backend": "cuda sm_100a", "dtype": a.dtype, "temperature": a.temperature, "seed": a.seed,
                     "batch_size": len(prompts), "kv_cache": "fresh per run", "ignore_eos": a.ignore_eos,
                     "prefill_chunk": a.prefill_chunk, "warmup_tokens": a.warmup_tokens, "page_size": page,
-                    "random_weights": a.random_weights},
+                    "random_weights": a.random_weights,
+                    # which products took which kernel: pass this table as ``tuning`` to get the same bits again
+                    "tuning": engine.tuning_table()},
         "prompt_ids": ids, "load_seconds": load_seconds, "runs": records}
     text = json.dumps(report, indent=1)
     if a.output:

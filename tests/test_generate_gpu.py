@@ -349,6 +349,10 @@ def test_python_entry_point_and_command_line(workdir):
     report = json.load(open(out))
     assert [r["tokens"] for r in report["runs"]] == [want, want]
     assert report["prompt_ids"] == p and report["runs"][0]["generated_tokens"] == 5
+    env = report["environment"]          # hardware, software, revision (with its dirty flag), what the GPU was doing
+    assert "B200" in env["hardware"]["gpu"] and env["software"]["torch"] and "dirty" in env["revision"]
+    assert "sm_mhz" in env["workload"] or env["workload"].get("clocks") == "unavailable"
+    assert report["runtime"]["tuning"]["policy"] == "auto"
     assert subprocess.run(cmd[:-2] + ["--runs", "0"], capture_output=True).returncode != 0
     # --stream: the timed runs' ids on standard output as they come, and no report there
     streamed = subprocess.run(cmd[:-2] + ["--stream"], capture_output=True, text=True, timeout=300, check=True).stdout
