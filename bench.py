@@ -263,6 +263,7 @@ def per_kernel(engine, raw, a, pk):
         def step():
             marks.clear()
             tap("start", None)
+            tap("nothing", None)          # two events with no kernel between them: what an event itself costs
             logits = e.forward(batch)
             e.ops.sample(logits, None, None, out)
             tap("head", None)
@@ -278,7 +279,7 @@ def per_kernel(engine, raw, a, pk):
         # what ends at a mark, by the mark's name: the kernels between it and the mark before
         phase = {"residual": None, "norm1": "add + norm", "qkv": "q/k/v product", "q_rot": "norm + rotation + cache write",
                  "attn_out": "attention", "mixer_out": "output product", "norm2": "add + norm", "ffn_act": "gate/up product + SwiGLU",
-                 "ffn_out": "down product", "head": "final norm + head + sampling"}
+                 "ffn_out": "down product", "head": "final norm + head + sampling", "nothing": "(an event alone)"}
         total = {}
         for _ in range(max(a.warmup, 3)):
             graph.replay()
@@ -299,9 +300,10 @@ def per_kernel(engine, raw, a, pk):
                            "add + norm": a.batch * h * (4 + 4 + 2 + 2), "norm + rotation + cache write": a.batch * (nq + 2 * nkv) * hd * 4,
                            "final norm + head + sampling": v * h * 2 + a.batch * v * 8}
         rows, step_us = [], 0.0
+        event_us = sum(total.pop("(an event alone)")) / a.steps      # subtracted from every phase below
         for name, times in total.items():
             calls = len(times) // a.steps
-            us = sum(times) / a.steps / calls
+            us = max(sum(times) / a.steps / calls - event_us, 0.01)
             gbs = per_layer_bytes[name] / us / 1e3
             step_us += us * calls
             rows.append({"phase": name, "calls_per_step": calls, "us": round(us, 2), "bytes": per_layer_bytes[name],
@@ -310,7 +312,8 @@ def per_kernel(engine, raw, a, pk):
         for r_ in rows:
             print(f"{r_['phase']:34s} {r_['calls_per_step']:5d} {r_['us']:9.2f} {r_['bytes'] / 1e6:9.2f} {r_['gb_per_s']:8.1f} {r_['frac']:8.3f}",
                   file=sys.stderr)
-        print(json.dumps({"per_kernel": rows, "step_us_serialised": round(step_us, 1), "batch": a.batch, "context": CONTEXT,
+        print(f"(an event alone: {event_us:.2f} us, subtracted from every phase)", file=sys.stderr)
+        print(json.dumps({"per_kernel": rows, "step_us_serialised": round(step_us, 1), "event_us": round(event_us, 2), "batch": a.batch, "context": CONTEXT,
                           "layers": layers, "shape": a.shape, "peak_gb_per_s": pk["hbm_gbs"], "of": pk["source"],
                           "note": "events between kernels inside one captured graph: no host gaps, no overlap of neighbours"}))
         return 0
