@@ -1006,11 +1006,10 @@ int launch_flash_as(const FlashParams& p, int n_tiles, cudaStream_t s) {
     constexpr size_t tiles = (size_t)(QROWS + 2 * STAGES * BN) * (HD + 8) * sizeof(__nv_bfloat16);
     constexpr size_t merge = (size_t)QROWS * (HD + 8) * sizeof(__nv_bfloat16) + (size_t)NWARPS * 16 * (HD + 2) * sizeof(float);
     constexpr size_t smem = tiles > merge ? tiles : merge;
-    static bool raised = false;  // per instantiation: the attribute is set once
-    if (smem > 48 * 1024 && !raised) {
+    static bool raised[64] = {};  // per instantiation and device: the attribute is set once
+    if (smem > 48 * 1024 && rmx_first_on_device(raised)) {
         cudaError_t e = cudaFuncSetAttribute(attention_flash_kernel<HD, KEYSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RMX_FAIL("attention_flash: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
-        raised = true;
     }
     dim3 grid(n_tiles, p.nkv, p.n_splits);
     attention_flash_kernel<HD, KEYSPLIT><<<grid, THREADS, smem, s>>>(p);
@@ -1080,11 +1079,10 @@ int launch_tma_as(const FlashParams& p, int n_tiles, long long pool_rows, cudaSt
     // stages, Q rows and, for decoding, the cluster's receive buffers (16 rows of HD floats and 8 x 16 pairs)
     constexpr size_t smem = 1024 + (size_t)STAGES * 2 * 64 * HD * 2 + (size_t)QROWS * (HD + 8) * 2 +
                             (KEYSPLIT ? (size_t)16 * HD * 4 + 8 * 16 + 8 * 16 * 8 : 0);
-    static bool raised = false;
-    if (!raised) {
+    static bool raised[64] = {};
+    if (rmx_first_on_device(raised)) {
         cudaError_t e = cudaFuncSetAttribute(attention_tma_kernel<HD, KEYSPLIT, FINISH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RMX_FAIL("attention_tma: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
-        raised = true;
     }
     dim3 grid(n_tiles, p.nkv, p.n_splits);
     if (p.cluster) {

@@ -746,11 +746,10 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
     if (pool_map(&mk, k_pool, pool_rows, p.box_rows) != 0) return -1;
     if (pool_map(&mv, v_pool, pool_rows, p.box_rows) != 0) return -1;
     constexpr size_t smem = 1024 + 2 * Q_BYTES + (size_t)STAGES * 2 * KV_BYTES + 2 * P_BYTES;
-    static bool raised = false;
-    if (!raised) {
+    static bool raised[64] = {};
+    if (rmx_first_on_device(raised)) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RMX_FAIL("attention_tcgen05: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
-        raised = true;
     }
     // blocks are handed to the SMs in the order x, then y: all kv heads of the tile that sees the most keys first
     attention_tcgen05_kernel<<<dim3(nkv, n_tiles, n_splits), THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);

@@ -88,6 +88,15 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     cfg.numAttrs = rmx_dependent_launch_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
 }
+// A kernel function's attributes (its limit of dynamic shared memory) are kept per device.  True the first time it
+// is asked for `seen` with the current device, so that each entry point raises its kernel's limit once on every device.
+inline bool rmx_first_on_device(bool (&seen)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (seen[dev]) return false;
+    seen[dev] = true;
+    return true;
+}
 #define RMX_CHECK_LAUNCHED(err, name)                                                     \
     do {                                                                                  \
         cudaError_t e__ = (err);                                                          \

@@ -322,12 +322,9 @@ int launch_as(const CUtensorMap& mw, const CUtensorMap& ma, const GemmParams& p,
     constexpr size_t smem = (size_t)STAGES * (TILE_N * TILE_K * 2 + MPAD * TILE_K * 2) + 1024;
     // a function's attributes are kept per device: raise the limit once on each
     static bool raised[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) RMX_FAIL("gemm_tcgen05: no current device");
-    if (!raised[dev]) {
+    if (rmx_first_on_device(raised)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_swapab_kernel<MPAD, STAGES, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RMX_FAIL("gemm_tcgen05: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-        raised[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_tiles, p.splits);
