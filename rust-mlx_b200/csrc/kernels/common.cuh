@@ -59,7 +59,12 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return total;
 }
 
-// Programmatic dependent launch: a kernel that is launched as a dependent of the one before it may start
+// Programmatic dependent launch.  Every kernel here lets its dependents go first thing (before its own wait): the
+// kernel after it then takes its place and does what needs no input (a product fetches its first weight tiles) while
+// this kernel still waits for the one before, so that the prologues of up to three kernels run ahead of the data.
+// A dependent's wait returns only when this kernel has completed, which it cannot before its own wait has returned,
+// so waiting for the kernel before covers the ones before that too.
+// A kernel that is launched as a dependent of the one before it may start
 // (and do what does not need that kernel's results, such as fetching weights) once every block of that
 // kernel has called this or has ended.  It has no effect when the next kernel is launched the usual way.
 __device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }

@@ -38,8 +38,8 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
                                  float* __restrict__ h, int width, int vocab, const int* __restrict__ from_last,
                                  const int* __restrict__ seq_index, const int* __restrict__ slots,
                                  const int* __restrict__ last_tokens) {
+    allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
-    allow_dependents();
     const int t = blockIdx.x;
     const int id = (from_last && from_last[t]) ? last_tokens[slots[seq_index[t]]] : ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -87,8 +87,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
                                    T* __restrict__ x, int width, int write_h) {
     __shared__ float scratch[32];
     extern __shared__ __align__(16) float vals[];
-    wait_for_prior_kernels();
+    // what follows (a product) may take its place and fetch its weights now: it waits for this kernel, and so for the
+    // one before it, before it touches what they write
     allow_dependents();
+    wait_for_prior_kernels();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* hrow = h + (size_t)src * width;
@@ -144,8 +146,10 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restri
         const int i = (c * blockDim.x + threadIdx.x) * 4;
         g[c] = i < width ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    wait_for_prior_kernels();
+    // what follows (a product) may take its place and fetch its weights now: it waits for this kernel, and so for the
+    // one before it, before it touches what they write
     allow_dependents();
+    wait_for_prior_kernels();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* hrow = h + (size_t)src * width;
@@ -262,8 +266,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 // four outputs per thread; inter is a multiple of 4
 template <typename T>
 __global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total4) {
+    allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
-    allow_dependents();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total4) return;
     const int per_row = inter >> 2;
@@ -284,8 +288,8 @@ __device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdiv
 
 __global__ void swiglu_kernel8(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter,
                                int block) {
+    allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
-    allow_dependents();
     const int per_row = inter >> 3;
     const __nv_bfloat16* src = gate_up + (size_t)blockIdx.x * 2 * inter;
     __nv_bfloat16* dst = out + (size_t)blockIdx.x * inter;
@@ -374,8 +378,8 @@ RMX_API int rmx_add_residual(float* h, const void* delta, int n_rows, int width,
 // reference does (src/weights.rs:198-200).  `ld` is the distance between rows of x.
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, int width, int ld, size_t total) {
+    allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
-    allow_dependents();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t row = idx / width;

@@ -30,8 +30,8 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_kernel(
     T* __restrict__ k_pool, T* __restrict__ v_pool, T* __restrict__ q_out, int n_tokens, int nq, int nkv, int hd,
     int row_stride, int write_kv, int* __restrict__ status, const float* __restrict__ cos_sin) {
     extern __shared__ float smem[];
+    allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
-    allow_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -98,8 +98,8 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_kernel(
 // cos_sin[t][j] = cos(pos_t * inv_freq[j]), cos_sin[t][half + j] = sin(...): once per step.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float* __restrict__ cos_sin, int n_tokens, int half) {
+    allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
-    allow_dependents();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_tokens * half) return;
     const int t = idx / half, j = idx - t * half;
@@ -121,8 +121,8 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_128_kernel(
     __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ q_out, int n_tokens, int nq, int nkv, int row_stride,
     int write_kv, int* __restrict__ status) {
     constexpr int hd = 128;
+    allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
-    allow_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     const int total = n_tokens * heads_total;   // the launcher keeps this below 2^31
@@ -183,8 +183,8 @@ __global__ void __launch_bounds__(WARPS * 32, 8) qk_rope_cache_128_wide_kernel(
     __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ q_out, int n_tokens, int nq, int nkv, int row_stride,
     int write_kv, int* __restrict__ status) {
     constexpr int hd = 128, PASSES = HEADS_PER_WARP / 2;
+    allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
-    allow_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     const int groups = (heads_total + HEADS_PER_WARP - 1) / HEADS_PER_WARP;

@@ -18,8 +18,8 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     __shared__ float s_val[THREADS];
     __shared__ int s_idx[THREADS];
     __shared__ int s_choice;
+    allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
-    allow_dependents();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * ld;
 
