@@ -450,13 +450,17 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
                 fence_after();
             }
             float s[BN];
-#pragma unroll
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(lane_addr + (i & 1) * BN + c, v);
+            {
+                // both halves of the tile's scores are asked for before either is waited for
+                uint32_t v0[32], v1[32];
+                tmem_ld32(lane_addr + (i & 1) * BN, v0);
+                tmem_ld32(lane_addr + (i & 1) * BN + 32, v1);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) s[c + j] = __uint_as_float(v[j]);
+                for (int j = 0; j < 32; ++j) {
+                    s[j] = __uint_as_float(v0[j]);
+                    s[32 + j] = __uint_as_float(v1[j]);
+                }
             }
             if ((i & 1) || i + 1 == n_kt) {   // the pair's scores are in registers: the next pair's may overwrite them
                 fence_before();

@@ -557,11 +557,12 @@ class Kernels:
                 a = torch.randn(m, k, device=ws[0].device).to(torch.bfloat16)
                 out = torch.empty(m, n, dtype=torch.bfloat16, device=ws[0].device)
                 calls = max(4, min(len(ws), 12))
-                # the kernel's own choice first: how many slices of K share a tile (the rule's count and its neighbours)
+                # the kernel's own choice first: how many slices of K share a tile (from one less than the rule's count up to
+                # what a cluster takes: more slices mean fewer k-blocks for each block to stream, and a longer reduction)
                 most = 8 if m <= 32 else 4
                 rule = min(tcgen05_splits(m, n, k), most)
                 best = None
-                for splits in sorted({max(1, rule - 1), rule, min(rule + 1, most), min(rule + 2, most)}):
+                for splits in range(max(1, rule - 1), most + 1):
                     if splits > max(1, -(-k // 64) // 4):
                         continue
                     t = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], out, workspace, splits=splits, dependent=True), calls)
