@@ -593,7 +593,14 @@ class Kernels:
                 gu = torch.empty(m, n, dtype=torch.bfloat16, device=ws[0].device)
                 act = torch.empty(m, n // 2, dtype=torch.bfloat16, device=ws[0].device)
                 calls = max(4, min(len(ws), 12))
-                mine = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], act, workspace, swiglu=True), calls)
+                best = None
+                for splits in range(1, 4):    # (a weight with this many tiles seldom gains from slices of K; it is asked, not assumed)
+                    if splits > max(1, -(-k // 64) // 4):
+                        continue
+                    t = _graph_time(lambda i: gemm_tcgen05(a, ws[i % len(ws)], act, workspace, swiglu=True, splits=splits, dependent=True), calls)
+                    if best is None or t < best[0]:
+                        best = (t, splits)
+                mine, self.tuned_splits[key] = best
 
                 def lib_pair(i):
                     torch.mm(a, ws[i % len(ws)].t(), out=gu)
@@ -603,7 +610,7 @@ class Kernels:
                 # alone does not show: it is taken unless the pair is clearly faster
                 self.tuned[key] = mine < lib * 1.05
                 if log is not None:
-                    log(f"gate/up [{m} x {k}] . [{n} x {k}]^T + SwiGLU: fused tcgen05 {mine:.1f} us, library + pointwise {lib:.1f} us")
+                    log(f"gate/up [{m} x {k}] . [{n} x {k}]^T + SwiGLU: fused tcgen05 {mine:.1f} us with {best[1]} slices of K, library + pointwise {lib:.1f} us")
         return dict(self.tuned)
 
     def prefers_fused_swiglu(self, m: int, n: int, k: int) -> bool:
@@ -634,8 +641,9 @@ class Kernels:
 
     def gemm_tcgen05(self, a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False, swiglu=False):
         """The tcgen05 product with the number of K slices that this engine's tuning found best for the shape."""
-        if splits is None and not swiglu:
-            splits = self.tuned_splits.get((w.shape[0], a.shape[1], _mpad(a.shape[0])))
+        if splits is None:
+            key = (w.shape[0], a.shape[1], _mpad(a.shape[0])) + (("swiglu",) if swiglu else ())
+            splits = self.tuned_splits.get(key)
             if splits is not None and cluster:
                 splits = min(splits, 8 if a.shape[0] <= 32 else 4)
         return gemm_tcgen05(a, w, out, workspace, status, splits, cluster, dependent, swiglu)
