@@ -181,7 +181,9 @@ def time_decode(engine, batch, steps, warmup, clocks=None):
         run.close()
 
 
-def time_prefill(engine, tokens, reps=3):
+def time_prefill(engine, tokens, reps=3, start_at=0):
+    """One portion of ``tokens`` prompt tokens in one step, the request holding ``start_at`` tokens already (0: a whole
+    prompt from its start; otherwise a later portion of a long prompt, its earlier keys being the synthetic cache)."""
     import torch
     from rust_mlx_b200.engine.batch import SequenceInput, build_batch
     g = torch.Generator().manual_seed(1)
@@ -190,8 +192,11 @@ def time_prefill(engine, tokens, reps=3):
     for rep in range(reps + 1):
         rid = 20_000 + rep
         engine.pools.open(rid)
-        engine.pools.table.reserve(rid, tokens)
-        batch = build_batch([SequenceInput(rid, 0, ids, [tokens - 1])], engine.pools, engine.device, engine._status,
+        if start_at:
+            engine.pools.table.reserve(rid, start_at)
+            engine.pools.table.commit(rid, start_at)
+        engine.pools.table.reserve(rid, start_at + tokens)
+        batch = build_batch([SequenceInput(rid, start_at, ids, [tokens - 1])], engine.pools, engine.device, engine._status,
                             engine.vocab_size)
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -364,6 +369,9 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, prefill and e2e")
     ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prefill only (for profiling it)")
+    ap.add_argument("--portion-at", type=int, default=0, metavar="CONTEXT",
+                    help="instead: time one 512-token portion of a prompt whose first CONTEXT tokens are in the cache (chunked "
+                         "prefill of a long prompt); prints its own JSON line")
     ap.add_argument("--per-kernel", action="store_true",
                     help="instead: time the phases of one decode step one by one and print each one's bytes, time and "
                          "fraction of the memory peak")
@@ -398,7 +406,9 @@ def main():
     cfg = Qwen3Config.from_dict(raw)
     if a.continuous:
         return continuous(cfg, raw, a)
-    biggest = 1 if (a.no_points or a.prefill_only or a.per_kernel) else max(64, a.batch)
+    if a.portion_at:
+        CONTEXT = a.portion_at
+    biggest = 1 if (a.no_points or a.prefill_only or a.per_kernel or a.portion_at) else max(64, a.batch)
     cache_tokens = max(biggest, a.batch) * (CONTEXT + 2 * PAGE + a.steps + a.warmup + 64)
     engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE,
                     max_requests=max(biggest, a.batch) + 2, tuning=a.policy)
@@ -408,6 +418,18 @@ def main():
     pk = peaks()
     if a.per_kernel:
         return per_kernel(engine, raw, a, pk)
+    if a.portion_at:
+        portion = 512
+        ms = time_prefill(engine, portion, start_at=a.portion_at)
+        _, per_layer, head = model_bytes(raw, a.layers)
+        gemm = 2.0 * portion * a.layers * per_layer + 2.0 * head
+        # every query of the portion against the cache's keys and, causally, the portion's own (half of them on average)
+        attn = 4.0 * portion * (a.portion_at + portion / 2) * raw["head_dim"] * raw["num_attention_heads"] * a.layers
+        print(json.dumps({"metric": f"prompt portion of {portion} tokens at context {a.portion_at} ({a.shape} shape, bf16)",
+                          "value": round(portion / (ms * 1e-3), 1), "unit": "tok/s", "ms": round(ms, 3), "layers": a.layers,
+                          "tflop": round((gemm + attn) / 1e12, 2), "attention_share_of_flop": round(attn / (gemm + attn), 3),
+                          "frac": round((gemm + attn) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"]}))
+        return 0
     if a.prefill_only:
         pf_ms = time_prefill(engine, PREFILL_TOKENS)
         flops = prefill_flops(raw, a.layers, PREFILL_TOKENS)
