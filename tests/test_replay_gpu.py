@@ -227,3 +227,45 @@ def test_named_intermediates_of_a_step_match_the_plain_implementation(workdir, n
             w = want[key][rows].float()
             assert t.shape == w.shape, key
             assert tiny.max_abs(t, w) < tol * max(1.0, w.abs().max().item()), key
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_context_in_portions_and_then_token_by_token(workdir, dtype):
+    """4,400 tokens on configuration D (heads of 128): the prompt in portions of 512 (each portion's attention sees
+    thousands of earlier keys, so a tile's keys are shared among several blocks and their shares added), then 24
+    tokens one by one (the decoding attention splits 70 key tiles among a cluster), beside a second, short request
+    that decodes in the same steps.  Against the plain implementation evaluated once over the whole sequence in
+    float64 on the GPU (sharpened weights, as everywhere in this file: a few keys carry most of a row's weight)."""
+    raw, page = tiny.CONFIGS["D"]
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=8, store="float32"))
+    n, tail = 4400, 24
+    long_ids = tiny.prompts(raw["vocab_size"], [n], seed=11)[0]
+    short_ids = tiny.prompts(raw["vocab_size"], [40 + tail], seed=12)[0]
+    config, tensors = plain.read_folder(folder)
+    rounding = None if dtype == "float32" else "bfloat16"
+    w = {k: v.to("cuda:0") for k, v in plain.prepare_weights(config, tensors, rounding).items()}
+    exact = {k: v.to("cuda:0") for k, v in plain.prepare_weights(config, tensors, None).items()}
+    want = plain.forward(config, w, long_ids, rounding).float().cpu()
+    want_exact = plain.forward(config, exact, long_ids, None).float().cpu()
+    want_short = plain.forward(config, w, short_ids, rounding).float().cpu()
+    eng = engine_for(folder, dtype, page, -(-n // page) * page + 2 * page)
+    got, got_short = [], []
+    at = 0
+    while at < n - tail:
+        c = min(512, n - tail - at)
+        rows = eng.step([("long", long_ids[at:at + c], [c - 1])])
+        got.append((at + c - 1, rows[0].cpu()))
+        at += c
+    eng.step([("short", short_ids[:40], [])])
+    for i in range(tail):
+        rows = eng.step([("long", long_ids[at + i:at + i + 1], [0]), ("short", short_ids[40 + i:41 + i], [0])])
+        got.append((at + i, rows[0].cpu()))
+        got_short.append((40 + i, rows[1].cpu()))
+    eng.release("long")
+    eng.release("short")
+    assert eng.pools.table.live() == 0
+    tol = 1e-4 if dtype == "float32" else max(TOL[dtype], tiny.max_abs(want, want_exact))
+    for pos, row in got:
+        assert tiny.max_abs(row, want[pos]) < tol, (pos, tol)
+    for pos, row in got_short:
+        assert tiny.max_abs(row, want_short[pos]) < (1e-4 if dtype == "float32" else TOL[dtype]), pos
