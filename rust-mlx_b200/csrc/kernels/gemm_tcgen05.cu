@@ -165,7 +165,54 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
     if (failed && tid == 0) atomicExch(p.status, 3);
     // (a block that failed still joins the cluster's barriers, or the tile's counter, below)
 
-    if constexpr (CLUSTER) {
+    if constexpr (CLUSTER && MPAD >= 32) {
+        // More than 16 rows: the slices share the summing.  Row t belongs to block t mod splits of the cluster; every
+        // block hands each of its rows to the row's owner (its own rows to itself) through distributed shared memory,
+        // and every owner adds the slices of its rows in slice order and writes them.  A block's work then does not
+        // grow with the number of slices (one block adding everything reads splits x rows numbers a thread), and the
+        // room it needs is a fraction of the stages, so that up to eight slices can share a tile at any row count.
+        // (The loop over a block's rows is not unrolled on purpose: this code runs once a block, and what it costs is
+        // fetching its instructions.  With up to 16 rows the first block adds everything: it is faster there, and the
+        // other blocks leave their SMs sooner.)
+        const uint32_t rank = cluster_ctarank();
+        const int S = p.splits, cap = (MPAD + S - 1) / S;    // cap: rows a block can own
+        float* recv = reinterpret_cast<float*>(tiles);       // [S slices][cap rows][128]
+        float* ex = recv + (size_t)S * cap * TILE_N;          // [64]: SwiGLU's exchange between the halves of the block
+        cluster_sync();
+        {
+            uint32_t owner = 0;
+            float* at = recv + (size_t)rank * cap * TILE_N + tid;   // row t is its owner's j-th: `at` moves on with j
+#pragma unroll
+            for (int t = 0; t < MPAD; ++t) {
+                if (t < p.M) st_cluster(at, owner, acc[t]);
+                if (++owner == (uint32_t)S) { owner = 0; at += TILE_N; }
+            }
+        }
+        cluster_sync();
+        if (failed) return;
+        const size_t slice = (size_t)cap * TILE_N;
+        for (int j = 0, t = (int)rank; t < p.M; ++j, t += S) {
+            const float* src = recv + (size_t)j * TILE_N + tid;
+            float sum = 0.f;
+            for (int z = 0; z < S; ++z) sum += src[z * slice];
+            if (p.epilogue == 1) {
+                // the upper half of the block (up rows) hands its sums to the lower half (gate rows)
+                if (tid >= 64) ex[tid - 64] = sum;
+                __syncthreads();
+                const int col = tile * 64 + tid;
+                if (tid < 64 && col < p.N / 2) {
+                    const float v = sum / (1.f + expf(-sum)) * ex[tid];
+                    if (p.out_float) reinterpret_cast<float*>(p.c)[(size_t)t * p.ldc + col] = v;
+                    else reinterpret_cast<__nv_bfloat16*>(p.c)[(size_t)t * p.ldc + col] = __float2bfloat16_rn(v);
+                }
+                __syncthreads();
+            } else if (n < p.N) {
+                if (p.out_float) reinterpret_cast<float*>(p.c)[(size_t)t * p.ldc + n] = sum;
+                else reinterpret_cast<__nv_bfloat16*>(p.c)[(size_t)t * p.ldc + n] = __float2bfloat16_rn(sum);
+            }
+        }
+        return;
+    } else if constexpr (CLUSTER) {
         // every block's MMAs are done (its shared-memory stages are free); the slices hand their sums to the
         // first block of the cluster, which adds them in slice order
         float* slots = reinterpret_cast<float*>(tiles);   // [splits - 1][MPAD][128] in the first block
@@ -386,7 +433,11 @@ int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K,
     const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     // flags: 1 = reduce split-K inside a cluster when it can be (no scratch needed); 2 = programmatic dependent launch
     const int stages = mpad == 64 ? 4 : (mpad == 16 ? 6 : 5);
-    const bool fits = (size_t)(splits - 1) * mpad * TILE_N * 4 <= (size_t)stages * (TILE_N * TILE_K * 2 + mpad * TILE_K * 2);
+    // what the cluster's reduction needs of a block's stages: up to 16 rows, the other slices' sums of all rows in the
+    // first block; above, every slice's sums of the rows a block owns (and a line for SwiGLU)
+    const size_t reduce_bytes = mpad <= 16 ? (size_t)(splits - 1) * mpad * TILE_N * 4
+                                           : ((size_t)splits * ((mpad + splits - 1) / splits) * TILE_N + 64) * 4;
+    const bool fits = reduce_bytes <= (size_t)stages * (TILE_N * TILE_K * 2 + mpad * TILE_K * 2);
     const bool cluster = (flags & 1) && splits >= 2 && splits <= 8 && fits;
     const bool dependent = (flags & 2) != 0;
     const int epilogue = (flags & 4) ? 1 : 0;   // flags: 4 = SwiGLU over blocks of 64 gate rows and 64 up rows

@@ -374,7 +374,7 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
     if splits is None:
         splits = tcgen05_splits(m, n, k)
         if cluster:
-            splits = min(splits, 8 if m <= 32 else 4)
+            splits = min(splits, 8)
     partial = counters = None
     if splits > 1:
         need = lib.rmx_gemm_tcgen05_scratch_floats(c_int(m), c_int(n), c_int(splits))
@@ -559,7 +559,7 @@ class Kernels:
                 calls = max(4, min(len(ws), 12))
                 # the kernel's own choice first: how many slices of K share a tile (from one less than the rule's count up to
                 # what a cluster takes: more slices mean fewer k-blocks for each block to stream, and a longer reduction)
-                most = 8 if m <= 32 else 4
+                most = 8
                 rule = min(tcgen05_splits(m, n, k), most)
                 best = None
                 for splits in range(max(1, rule - 1), most + 1):
@@ -645,7 +645,7 @@ class Kernels:
             key = (w.shape[0], a.shape[1], _mpad(a.shape[0])) + (("swiglu",) if swiglu else ())
             splits = self.tuned_splits.get(key)
             if splits is not None and cluster:
-                splits = min(splits, 8 if a.shape[0] <= 32 else 4)
+                splits = min(splits, 8)
         return gemm_tcgen05(a, w, out, workspace, status, splits, cluster, dependent, swiglu)
 
     # ---- attention ------------------------------------------------------------------------------------------
