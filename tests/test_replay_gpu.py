@@ -269,3 +269,27 @@ def test_a_long_context_in_portions_and_then_token_by_token(workdir, dtype):
         assert tiny.max_abs(row, want[pos]) < tol, (pos, tol)
     for pos, row in got_short:
         assert tiny.max_abs(row, want_short[pos]) < (1e-4 if dtype == "float32" else TOL[dtype]), pos
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("head_dim, heads, kv_heads, hidden", [(48, 5, 5, 72), (80, 6, 2, 104), (112, 7, 1, 88), (144, 3, 3, 120),
+                                                               (256, 4, 2, 136)])
+def test_head_sizes_in_steps_of_16_and_odd_head_counts(workdir, head_dim, heads, kv_heads, hidden, dtype):
+    """Head sizes that no tensor-core attention kernel is built for (48, 80, 112, 144, 256), head counts and groups
+    that are no power of two, widths that are multiples of 8 only: the engine takes them (the attention on FMA
+    units where nothing faster exists) and agrees with the plain implementation, mixed and with the tail token by
+    token; nothing is computed wrongly for lack of a kernel."""
+    raw = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=hidden,
+               num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, intermediate_size=152,
+               vocab_size=211, rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096)
+    folder = tiny.sharpen(tiny.make_folder(workdir, raw, seed=head_dim, store="float32"))
+    reqs = {f"r{i}": p for i, p in enumerate(tiny.prompts(raw["vocab_size"], [37, 5, 70, 18], seed=head_dim))}
+    pm = plain.PlainModel(folder, rounding=None if dtype == "float32" else "bfloat16")
+    exact = plain.PlainModel(folder)
+    for way in ("mixed", "tail_one_by_one"):
+        steps = getattr(replay, way)(reqs)
+        got = replay.run_engine(engine_for(folder, dtype, 16, replay.tokens_needed(steps, 16)), steps)
+        for rid, toks in reqs.items():
+            want = pm.logits(toks).float()
+            tol = 2e-5 if dtype == "float32" else max(TOL[dtype], tiny.max_abs(want, exact.logits(toks).float()))
+            assert tiny.max_abs(got[rid], want) < tol, (way, rid)
