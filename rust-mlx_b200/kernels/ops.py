@@ -503,6 +503,7 @@ class Kernels:
         self.fused_decode_rope = True       # a decoding attention norms and rotates its own token while it waits for keys
         self.fused_swiglu = True            # the gate/up product of few rows forms silu(gate) * up in its epilogue
         self.use_tcgen05_attention = True   # prompt portions at head size 128 run on the tcgen05 tensor cores
+        self._splits_memo = {}
 
     def __getattr__(self, name):
         # the faces of the kernels that hold no state
@@ -695,9 +696,15 @@ class Kernels:
     def decode_attention_splits(self, n_seqs: int, nkv: int, hd: int, group: int, max_seq_len: int, dtype) -> int:
         """How many blocks share the keys of a (sequence, kv head) when ``n_seqs`` sequences decode one token each:
         the one shape of a decode step's launches that follows the sequences' lengths."""
-        if dtype != torch.bfloat16 or not flash_supported(hd, group):
-            return 1
-        return flash_splits(n_seqs, nkv, max_seq_len)
+        # (asked once a layer and step: remembered by what the answer depends on, the length only through its key tiles)
+        key = (n_seqs, nkv, hd, group, -(-max_seq_len // 64), dtype)
+        found = self._splits_memo.get(key)
+        if found is None:
+            if len(self._splits_memo) > 4096:
+                self._splits_memo.clear()
+            found = 1 if dtype != torch.bfloat16 or not flash_supported(hd, group) else flash_splits(n_seqs, nkv, max_seq_len)
+            self._splits_memo[key] = found
+        return found
 
 
 # Calls without an engine (tests of single kernels, parts bound by hand) take this one: the fixed rule, no tuning.
