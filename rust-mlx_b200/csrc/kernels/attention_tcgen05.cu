@@ -5,44 +5,57 @@
 // every key and value tile.  Keys are visited in tiles of 64 aligned to absolute positions.
 //
 // A block takes two neighbouring tiles, which share every key and value tile it fetches (or one, for steps so
-// small that SMs would be left without work).
+// small that SMs would be left without work).  Key tiles go in pairs: one step of every role is 128 keys.
 //
-//   warp 0   producer: Q once and then K/V tiles by TMA (tensor-map boxes, 128-byte swizzle) into a ring
-//   warps 1 and 10  issue the MMAs (warp 10 the scores, warp 1 O += P V, so that neither waits for what the
-//            other waits for): S = Q K^T into tensor memory, for two neighbouring key tiles at once (an MMA of 128
-//            rows by 64 columns takes as long as one of 128 columns, so the scores of a pair of key tiles cost
-//            what one tile's would; the pair's key tiles lie in neighbouring slots of the ring, which makes them
-//            one operand of 128 rows); the next pair's scores are formed as soon as the softmax warps have read
-//            this pair's into registers; later O += P V, tile by tile
-//   warps 2-5 and 6-9  softmax of the first and the second query tile: every thread owns one row (one lane
-//            of tensor memory): it reads its 64 scores, masks where the tile touches the diagonal or the
-//            window's edge, keeps the running maximum and sum in float, writes its probabilities as bfloat16
-//            into shared memory for the second MMA, and rescales its row of O when the maximum moved
+//   warp 0   producer: Q once, then pairs of key tiles and of value tiles by TMA (tensor-map boxes, 128-byte
+//            swizzle) into two rings, the keys a pair ahead of the values
+//   warp 1   issues S = Q K^T: the scores of a pair of key tiles are one group of MMAs of 128 columns (an MMA of
+//            128 rows by 64 columns takes as long as one of 128 columns; the pair's key tiles lie in neighbouring
+//            slots of the ring, which makes them one operand of 128 rows).  There is one score buffer in tensor
+//            memory; the two query tiles take it in turns: as soon as a tile's softmax warps have their scores
+//            in registers, the other tile's next scores are formed in it
+//   warp 2   issues O += P V with P read from tensor memory.  (Two issuing warps: the tensor cores take an MMA
+//            only when an earlier one has left their queue, so a warp that issues is held for as long as they
+//            run; while one is held or waits for a barrier, the other issues.  Both run their loop with every
+//            lane and elect one to issue, so that the operand descriptors stay in uniform registers.)
+//   warp 3   spare
+//   warps 4-7 and 8-11  softmax of the first and the second query tile: every thread owns one row (one lane of
+//            tensor memory) and holds its 128 scores of a pair in registers.  The reference m that exponentials
+//            are taken against moves only when a score exceeds it by more than 2^8, so a pair is first tried in one
+//            pass against the reference as it stands (exponent, largest exponent seen, sum, probabilities as
+//            bfloat16 into tensor memory), and done the long way (maximum, new reference, O rescaled, exponentials)
+//            only where that pass meets a larger score, a row has no reference yet, or the pair needs a mask (the
+//            diagonal, the window's edge)
 //
-// S and O live in tensor memory (per query tile 128 columns of scores, a pair of key tiles, and 128 of O).  Tiles
-// late in a sequence see more keys: blocks start in the order of their tiles' lengths, all kv heads of the longest
-// tile first, so that the longest blocks do not run last.  V is used as it lies in the cache, [key][d], through an
-// MN-major operand descriptor.  Every wait on a barrier is bounded: a block that gives up records status 3,
-// frees its tensor memory and ends.
+// Registers: the roles' warpgroup gives most of its registers to the softmax warpgroups (setmaxnreg).
+// Tensor memory (all 512 columns): scores 128, O of each query tile 128, P of each query tile 64 (128 keys as
+// bfloat16).  Tiles late in a sequence see more keys: blocks start in the order of their tiles' lengths, all kv
+// heads of the longest tile first, so that the longest blocks do not run last.  V is used as it lies in the cache,
+// [key][d], through an MN-major operand descriptor.  Every wait on a barrier is bounded: a block that gives up
+// records status 3, frees its tensor memory and ends.
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "common.cuh"
 
 namespace {
 constexpr int HD = 128, BM = 128, BN = 64;
-constexpr int STAGES = 4;                   // slots of the key/value ring, one key tile (and its value tile) each; pairs 0|1 and 2|3
-constexpr int THREADS = 352;   // producer, O += P V issuer, 4 softmax warps for each of the block's two query tiles, score issuer
+constexpr int K_PAIRS = 3, V_PAIRS = 2;     // rings of pairs of key tiles and of value tiles (the keys are asked for earlier: the scores run a pair ahead)
+constexpr int K_SLOTS = 2 * K_PAIRS, V_SLOTS = 2 * V_PAIRS;
+constexpr int THREADS = 384;   // a warpgroup of roles (producer, two MMA issuers, a spare warp) and one of softmax warps for each query tile
+constexpr int ROLE_REGS = 56, SOFTMAX_REGS = 224;   // registers a thread after the warpgroups have traded them (128 x 56 + 256 x 224 <= 65536)
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int Q_BYTES = BM * HD * 2;        // 32 KB: two boxes of [128 rows][64 columns]
 constexpr int KV_BYTES = BN * HD * 2;       // 16 KB per key tile, the same per value tile
-constexpr int P_BYTES = BM * BN * 2;        // 16 KB
-constexpr int TILE_COLS = 256;              // per query tile: S of a pair of key tiles in columns 0..63 and 64..127, O in 128..255
+// Tensor memory: the scores of a pair of key tiles in columns 0..127, one buffer that the two query tiles take in
+// turns (a tile's softmax warps read their scores into registers and hand it on); O of tile t in 128 (1 + t) ..;
+// P of tile t, bfloat16, 128 keys in 64 columns, from 384 + 64 t.
 constexpr int TMEM_COLS = 512;              // two query tiles: all of an SM's tensor memory
-constexpr int O_COL = 128;
+constexpr int S_COL = 0, O_COL = 128, O_COLS = 128, P_COL = 384, P_COLS = 64;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -100,6 +113,24 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, 
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
         ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "r"((uint32_t)accumulate) : "memory");
 }
+// The same with the A operand in tensor memory (rows are lanes; 16 bfloat16 of the reduction are 8 columns).
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t id, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(id), "r"((uint32_t)accumulate) : "memory");
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -123,6 +154,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
           "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
           "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
@@ -180,40 +218,42 @@ struct Params {
 // One block: two neighbouring query tiles (A and B, 128 rows each) of one sequence against one kv head.  Both use
 // every key and value tile the block fetches, and while the softmax warps of one tile work the tensor cores
 // serve the other.
-__global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                    const __grid_constant__ CUtensorMap map_k,
                                                                    const __grid_constant__ CUtensorMap map_v,
                                                                    const Params p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_smem = base;                               // [2 tiles][2 boxes][128 rows][128 B]
-    // keys: [2 halves of d][STAGES slots][64 rows][128 B], so that the same half of two neighbouring slots is one
-    // run of 128 rows; values: [STAGES slots][2 halves of d][64 rows][128 B]
+    // keys: [2 halves of d][K_SLOTS slots][64 rows][128 B], so that the same half of two neighbouring slots is one
+    // run of 128 rows; values: [V_SLOTS slots][2 halves of d][64 rows][128 B]
     unsigned char* kv_smem = q_smem + 2 * Q_BYTES;
     unsigned char* k_smem = kv_smem;
-    unsigned char* v_smem = kv_smem + STAGES * KV_BYTES;
-    unsigned char* p_smem = kv_smem + STAGES * 2 * KV_BYTES;    // [2 tiles][128 rows][128 B]
-    // keys come and go by pairs of slots (a pair's scores are one group of MMAs), values slot by slot
-    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[STAGES], v_empty[STAGES], s_full[2], s_read[2], p_full[2], o_done[2];
+    unsigned char* v_smem = kv_smem + K_SLOTS * KV_BYTES;
+    // keys and values come and go by pairs of slots (a pair of key tiles is one step of every role)
+    __shared__ __align__(8) uint64_t q_full, k_full[K_PAIRS], k_empty[K_PAIRS], v_full[V_PAIRS], v_empty[V_PAIRS], s_full[2], s_read[2], p_full[2], pv_done[2];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int s_failed, s_tile[3], s_warp_total[THREADS / 32];
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // (the same in every lane, and known to be)
     const int kvh = blockIdx.x;   // the kv head runs fastest, so that blocks start in the order of their tiles
     if (tid == 0) {
         s_failed = 0;
         mbar_init(&q_full, 1);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&v_full[s], 1);
-            mbar_init(&v_empty[s], 1);
+        for (int i = 0; i < K_PAIRS; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+        }
+        for (int i = 0; i < V_PAIRS; ++i) {
+            mbar_init(&v_full[i], 1);
+            mbar_init(&v_empty[i], 1);
         }
         for (int t = 0; t < 2; ++t) {
-            mbar_init(&k_full[t], 1);
-            mbar_init(&k_empty[t], 1);
             mbar_init(&s_full[t], 1);
-            mbar_init(&s_read[t], 4);      // one arrival per softmax warp of the tile
-            mbar_init(&p_full[t], 128);
-            mbar_init(&o_done[t], 1);
+            mbar_init(&p_full[t], 4);      // one arrival per softmax warp of the tile
+            mbar_init(&s_read[t], 4);
+            mbar_init(&pv_done[t], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_q) : "memory");
@@ -264,7 +304,7 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
     }
     // the key and value stages start as zeros: a part of a tile that is never fetched (beyond the sequence's end, a
     // page the request does not hold) must hold finite numbers, because a probability of zero still multiplies it
-    for (int idx = tid; idx < STAGES * 2 * KV_BYTES / 16; idx += THREADS)
+    for (int idx = tid; idx < (K_SLOTS + V_SLOTS) * KV_BYTES / 16; idx += THREADS)
         reinterpret_cast<uint4*>(kv_smem)[idx] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     fence_before();
@@ -289,14 +329,18 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
         }
     }
     const bool two = n_tok > p.tq;   // the second tile has rows
+    const int n_pairs = (n_kt + 1) / 2;
+    // (the softmax warps hold a row's 128 scores in registers: the warpgroup of roles hands them most of its own,
+    // every warp of a warpgroup as the first thing in its branch)
 
     if (warp == 0 && seq >= 0) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(ROLE_REGS));
         // ---- producer.  A copy brings one box (a page's keys or values of one tile, or 64 of them if pages are
-        // larger) of one half of d; the copies of a group (a pair of key tiles, or one value tile: at most 32) are
-        // issued by as many lanes at once, because a thread that issues them one after another takes longer than the
-        // tensor cores take for the tile.  The warp holds the part of the block table that the copies are about to
-        // need in registers (three runs of 32 entries, the last one still on its way), so that no copy waits for a
-        // load of its page's number from global memory.
+        // larger) of one half of d; the copies of a pair of tiles (at most 32) are issued by as many lanes at once,
+        // because a thread that issues them one after another takes longer than the tensor cores take for the
+        // pair.  The warp holds the part of the block table that the copies are about to need in registers (three
+        // runs of 32 entries, the last one still on its way), so that no copy waits for a load of its page's number
+        // from global memory.
         constexpr uint32_t FULL = 0xffffffffu;
         if (lane == 0) {
             mbar_expect_tx(&q_full, two ? 2 * Q_BYTES : Q_BYTES);
@@ -315,13 +359,13 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
             int done = lane == 0 ? (int)mbar_wait(bar, parity) : 1;
             return __shfl_sync(FULL, done, 0) != 0;
         };
-        // this lane's copy within a group: which tile of the group, which box of the tile, which half of d
+        // this lane's copy within a pair: which tile of the pair, which box of the tile, which half of d
         const int boxes = BN / p.box_rows, per_tile = 2 * boxes;
         const int my_tile = lane / per_tile, my_box = (lane % per_tile) >> 1, my_half = lane & 1;
         const uint32_t copy_bytes = p.box_rows * 64 * 2u;
         // the copies of tiles first .. first + n - 1 (keys when `keys`, else values) into their slots, counted by `bar`
         auto fetch = [&](int first, int n, bool keys, uint64_t* bar) {
-            // move the table's registers on so that the group's last entry lies in them (no group reaches back more
+            // move the table's registers on so that the pair's last entry lies in them (no pair reaches back more
             // than 32 entries behind the furthest entry asked for so far)
             const int e_last = min((kt_lo + first + n) * BN - 1, pos_last) >> p.page_shift;
             while (e_last >= win + 64) {
@@ -342,96 +386,120 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
             if (lane == 0) mbar_expect_tx(bar, copies * copy_bytes);
             __syncwarp();
             if (mine) {
-                const int st = i % STAGES;
+                const int st = i % (keys ? K_SLOTS : V_SLOTS);
                 const int row = (page * p.nkv + kvh) * p.page_size + (kp & (p.page_size - 1));
-                unsigned char* dst = keys ? k_smem + st * (KV_BYTES / 2) + my_half * (STAGES * KV_BYTES / 2)
+                unsigned char* dst = keys ? k_smem + st * (KV_BYTES / 2) + my_half * (K_SLOTS * KV_BYTES / 2)
                                           : v_smem + st * KV_BYTES + my_half * (KV_BYTES / 2);
                 tma_2d(dst + my_box * p.box_rows * 128, keys ? &map_k : &map_v, bar, my_half * 64, row);
             }
             __syncwarp();
         };
         bool ok = true;
-        for (int i = 0; i < n_kt && ok; ++i) {
-            if ((i & 1) == 0) {   // the keys of the pair of tiles i, i + 1: their slots are free once the scores of the pair before last are formed
-                const int j = i >> 1;
-                if (j >= 2 && !wait(&k_empty[j & 1], ((j >> 1) - 1) & 1)) { ok = false; break; }
-                fetch(i, min(2, n_kt - i), true, &k_full[j & 1]);
-            }
-            const int st = i % STAGES, round = i / STAGES;
-            if (round > 0 && !wait(&v_empty[st], (round - 1) & 1)) { ok = false; break; }
-            fetch(i, 1, false, &v_full[st]);
+        // A pair's key slots are free once the scores of the pair K_PAIRS before are formed, its value slots once the
+        // probabilities of the pair V_PAIRS before have been multiplied with them.  The keys are asked for a pair
+        // ahead of the values (the scores of a pair are formed while the softmax of the pair before still runs).
+        auto keys_of = [&](int j) {
+            if (j >= K_PAIRS && !wait(&k_empty[j % K_PAIRS], (j / K_PAIRS - 1) & 1)) return false;
+            fetch(2 * j, min(2, n_kt - 2 * j), true, &k_full[j % K_PAIRS]);
+            return true;
+        };
+        if (n_pairs > 0) ok = keys_of(0);
+        for (int j = 0; j < n_pairs && ok; ++j) {
+            if (j + 1 < n_pairs && !keys_of(j + 1)) { ok = false; break; }
+            if (j >= V_PAIRS && !wait(&v_empty[j % V_PAIRS], (j / V_PAIRS - 1) & 1)) { ok = false; break; }
+            fetch(2 * j, min(2, n_kt - 2 * j), false, &v_full[j % V_PAIRS]);
         }
         if (!ok && lane == 0) atomicExch(&s_failed, 1);
-    } else if (warp == 10 && lane == 0 && seq >= 0) {
-        // ---- issuer of the score MMAs.  One thread issues them all, so what it executes per MMA counts: the operand
-        // descriptors are formed before the loop (those of Q do not change; those of K differ by the pair's address,
-        // which is added to the descriptor's low bits), and the loops are unrolled.
-        const uint32_t id_s = idesc(2 * BN, false);
-        const int n_t = two ? 2 : 1;
-        uint64_t q_desc[2][HD / 16];
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
-#pragma unroll
-            for (int kk = 0; kk < HD / 16; ++kk)
-                q_desc[t][kk] = desc_kmajor(smem_u32(q_smem + t * Q_BYTES) + (kk >> 2) * (Q_BYTES / 2) + (kk & 3) * 32);
-        const uint64_t k_desc0 = desc_kmajor(smem_u32(k_smem));
-        const int n_pairs = (n_kt + 1) / 2;
-        bool ok = mbar_wait(&q_full, 0);
-        for (int j = 0; j < n_pairs && ok; ++j) {
-            // S = Q K^T of the key tiles 2 j and 2 j + 1 (slots 2 (j & 1) and the next: 128 rows of keys) for each query
-            // tile into its 128 score columns: the reduction runs over d, 8 steps of 16; d 0..63 lie in the first half
-            // of the key region, 64..127 in the second.  (If the pair's second tile does not exist, its columns are
-            // never read.)  The columns are free once the softmax warps have read the pair before into registers.
-            if (!mbar_wait(&k_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
-            fence_after();
-            const uint64_t k_desc = k_desc0 + (uint64_t)(((j & 1) * 2 * (KV_BYTES / 2)) >> 4);
-            for (int t = 0; t < n_t && ok; ++t) {
-                if (j > 0 && !mbar_wait(&s_read[t], (j - 1) & 1)) { ok = false; break; }
-                fence_after();
-                const uint32_t d_addr = tmem + t * TILE_COLS;
-#pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk)
-                    umma(d_addr, t == 0 ? q_desc[0][kk] : q_desc[1][kk],
-                         k_desc + (uint64_t)(((kk >> 2) * (STAGES * KV_BYTES / 2) + (kk & 3) * 32) >> 4), id_s, kk > 0);
-                umma_commit(&s_full[t]);
-            }
-            umma_commit(&k_empty[j & 1]);   // the pair's key slots are free once these MMAs have finished
-        }
-        if (!ok) atomicExch(&s_failed, 1);
-    } else if (warp == 1 && lane == 0 && seq >= 0) {
-        // ---- issuer of O += P V: the reduction runs over a tile's 64 keys, 4 steps of 16; V is [key][d], MN-major:
-        // blocks of 64 d are 8 KB apart, groups of 8 keys 1 KB
-        const uint32_t id_o = idesc(HD, true);
-        const int n_t = two ? 2 : 1;
-        uint64_t p_desc[2][BN / 16];
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
-#pragma unroll
-            for (int kk = 0; kk < BN / 16; ++kk) p_desc[t][kk] = desc_kmajor(smem_u32(p_smem + t * P_BYTES) + kk * 32);
-        const uint64_t v_desc0 = desc_mnmajor(smem_u32(v_smem), KV_BYTES / 2, 1024);
+    } else if ((warp == 1 || warp == 2) && seq >= 0) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(ROLE_REGS));
+        // ---- issuers of the MMAs: warp 1 the scores, warp 2 O += P V.  While one waits (for a barrier, or because
+        // the tensor cores' queue is full: an MMA is taken only when an earlier one has left it) the other issues.
+        // The whole warp runs the loop with everything it computes the same in every lane (so that operand
+        // descriptors can live in the warp's uniform registers), and one elected lane issues.
+        constexpr uint32_t FULL = 0xffffffffu;
+        const uint32_t tm = __shfl_sync(FULL, tmem, 0);
+        const int n_pairs_u = __shfl_sync(FULL, n_pairs, 0), n_kt_u = __shfl_sync(FULL, n_kt, 0);
+        const int n_t = __shfl_sync(FULL, two ? 2 : 1, 0);
+        const uint32_t q_addr = __shfl_sync(FULL, smem_u32(q_smem), 0);
+        const int jobs = n_pairs_u * n_t;   // a job is (pair of key tiles, query tile), pair by pair, tile by tile
+        auto wait = [&](uint64_t* bar, uint32_t parity) {
+            int done = lane == 0 ? (int)mbar_wait(bar, parity) : 1;
+            return __shfl_sync(FULL, done, 0) != 0;
+        };
         bool ok = true;
-        for (int i = 0; i < n_kt && ok; ++i) {
-            const int st = i % STAGES;
-            if (!mbar_wait(&v_full[st], (i / STAGES) & 1)) { ok = false; break; }
-            const uint64_t v_desc = v_desc0 + (uint64_t)((st * KV_BYTES) >> 4);
-            for (int t = 0; t < n_t && ok; ++t) {
-                if (!mbar_wait(&p_full[t], i & 1)) { ok = false; break; }
+        if (warp == 1) {
+            // S = Q K^T of the pair j of key tiles (two neighbouring slots: 128 rows of keys) for query tile t into
+            // the score columns: the reduction runs over d, 8 steps of 16; d 0..63 lie in the first half of the key
+            // region, 64..127 in the second.  (If the pair's second tile does not exist, its columns are never
+            // used.)  The score columns pass from job to job: job k's scores may be formed once the warps of job
+            // k - 1 have theirs in registers.
+            const uint32_t id_s = idesc(2 * BN, false);
+            const uint64_t q_desc0 = desc_kmajor(q_addr);
+            const uint64_t k_desc0 = desc_kmajor(q_addr + 2 * Q_BYTES);
+            ok = wait(&q_full, 0);
+            int t = 0, j = 0;
+            for (int k = 0; k < jobs && ok; ++k) {
+                if (t == 0 && !wait(&k_full[j % K_PAIRS], (j / K_PAIRS) & 1)) { ok = false; break; }
+                if (k > 0) {
+                    const int pt = t == 0 ? n_t - 1 : t - 1, pj = t == 0 ? j - 1 : j;
+                    if (!wait(&s_read[pt], pj & 1)) { ok = false; break; }
+                }
                 fence_after();
-                const uint32_t d_addr = tmem + t * TILE_COLS + O_COL;
+                const uint64_t q_desc = q_desc0 + (uint64_t)((t * Q_BYTES) >> 4);
+                const uint64_t k_desc = k_desc0 + (uint64_t)(((j % K_PAIRS) * 2 * (KV_BYTES / 2)) >> 4);
+                const uint32_t d_addr = tm + S_COL;
+                if (elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk)
-                    umma(d_addr, t == 0 ? p_desc[0][kk] : p_desc[1][kk], v_desc + (uint64_t)((kk * 2048) >> 4), id_o, i > 0 || kk > 0);
-                umma_commit(&o_done[t]);
+                    for (int kk = 0; kk < HD / 16; ++kk)
+                        umma(d_addr, q_desc + (uint64_t)(((kk >> 2) * (Q_BYTES / 2) + (kk & 3) * 32) >> 4),
+                             k_desc + (uint64_t)(((kk >> 2) * (K_SLOTS * KV_BYTES / 2) + (kk & 3) * 32) >> 4), id_s, kk > 0);
+                    umma_commit(&s_full[t]);
+                    if (t == n_t - 1) umma_commit(&k_empty[j % K_PAIRS]);   // the pair's keys are free after the last tile's scores
+                }
+                __syncwarp();
+                if (++t == n_t) { t = 0; ++j; }
             }
-            umma_commit(&v_empty[st]);   // both query tiles are done with this slot's values once these MMAs have finished
+        } else {
+            // O += P V of the pair's tiles: the probabilities come from tensor memory (16 keys are 8 columns), the
+            // reduction runs over a tile's 64 keys in 4 steps of 16; V is [key][d], MN-major: blocks of 64 d are 8 KB
+            // apart, groups of 8 keys 1 KB
+            const uint32_t id_o = idesc(HD, true);
+            const uint64_t v_desc0 = desc_mnmajor(q_addr + 2 * Q_BYTES + K_SLOTS * KV_BYTES, KV_BYTES / 2, 1024);
+            int t = 0, j = 0;
+            for (int k = 0; k < jobs && ok; ++k) {
+                if (t == 0 && !wait(&v_full[j % V_PAIRS], (j / V_PAIRS) & 1)) { ok = false; break; }
+                if (!wait(&p_full[t], j & 1)) { ok = false; break; }
+                fence_after();
+                const int tiles = min(2, n_kt_u - 2 * j);
+                const uint32_t d_addr = tm + O_COL + t * O_COLS, a_addr = tm + P_COL + t * P_COLS;
+                const uint64_t v_desc = v_desc0 + (uint64_t)((((2 * j) % V_SLOTS) * KV_BYTES) >> 4);
+                if (elect_one()) {
+#pragma unroll
+                    for (int kk = 0; kk < BN / 16; ++kk)
+                        umma_ts(d_addr, a_addr + kk * 8, v_desc + (uint64_t)((kk * 2048) >> 4), id_o, j > 0 || kk > 0);
+                    if (tiles == 2) {
+#pragma unroll
+                        for (int kk = 0; kk < BN / 16; ++kk)
+                            umma_ts(d_addr, a_addr + (BN / 16 + kk) * 8, v_desc + (uint64_t)((KV_BYTES + kk * 2048) >> 4), id_o, true);
+                    }
+                    umma_commit(&pv_done[t]);
+                    if (t == n_t - 1) umma_commit(&v_empty[j % V_PAIRS]);   // every query tile is done with the pair's values
+                }
+                __syncwarp();
+                if (++t == n_t) { t = 0; ++j; }
+            }
         }
-        if (!ok) atomicExch(&s_failed, 1);
-    } else if (warp >= 2 && warp < 10 && seq >= 0 && (warp < 6 || two)) {
+        if (!ok && lane == 0) atomicExch(&s_failed, 1);
+    } else if (warp < 4 && seq >= 0) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(ROLE_REGS));   // the spare warps of the roles' warpgroup
+    } else if (warp >= 4 && seq >= 0 && (warp < 8 || two)) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(SOFTMAX_REGS));
         // ---- softmax of query tile t: thread owns row r of the tile = lane r of tensor memory
-        const int t = warp < 6 ? 0 : 1;
+        const int t = warp < 8 ? 0 : 1;
         const int quad = warp & 3;
         const int r = quad * 32 + lane;
-        const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16) + t * TILE_COLS;
+        const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
+        const uint32_t s_addr = lane_base + S_COL, o_addr = lane_base + O_COL + t * O_COLS, p_addr = lane_base + P_COL + t * P_COLS;
         const int tile_tok0 = tok0 + t * p.tq;
         const int tile_tokens = min(p.tq, n_tok - t * p.tq);
         const int rows_valid = tile_tokens * p.group;
@@ -439,116 +507,154 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
         const int tok = row_ok ? r / p.group : 0;
         const int row_pos = pos0 + t * p.tq + tok;
         const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
-        unsigned char* p_tile = p_smem + t * P_BYTES;
+        const uint64_t scale2 = pair(p.scale_log2, p.scale_log2);
         float m = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int i = 0; i < n_kt; ++i) {
-            const int kt = kt_lo + i;
-            if ((i & 1) == 0) {   // the scores of the pair of key tiles i, i + 1
-                ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], (i >> 1) & 1));
+        for (int j = 0; j < n_pairs; ++j) {
+            const int tiles = min(2, n_kt - 2 * j);
+            const int k0 = (kt_lo + 2 * j) * BN;   // the pair's first key
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1));
+            if (!ok) break;
+            fence_after();
+            // the row's scores of the whole pair: the second tile's are on their way while the first's maximum is taken
+            uint32_t v[4][32];
+#define SCORE(i) __uint_as_float(v[(i) >> 5][(i) & 31])
+            tmem_ld32(s_addr, v[0]);
+            tmem_ld32(s_addr + 32, v[1]);
+            tmem_ld_wait();
+            tmem_ld32(s_addr + 64, v[2]);   // (of a pair's missing second tile: never used)
+            tmem_ld32(s_addr + 96, v[3]);
+            tmem_ld_wait();
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_read[t]);   // the scores are in registers: their columns may go to the next job
+            if (j > 0) {
+                // the MMAs of the pair before have read its probabilities and added into O: both may be written now
+                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (j - 1) & 1));
                 if (!ok) break;
                 fence_after();
             }
-            float s[BN];
-            {
-                // both halves of the tile's scores are asked for before either is waited for
-                uint32_t v0[32], v1[32];
-                tmem_ld32(lane_addr + (i & 1) * BN, v0);
-                tmem_ld32(lane_addr + (i & 1) * BN + 32, v1);
-                tmem_ld_wait();
+            // Exponents against the reference `ref` and the row's sum, two numbers at a time (fma and add on pairs of
+            // floats); the probabilities go into tensor memory as bfloat16, 32 keys in 16 columns.  With `track` the
+            // largest exponent is kept as well.
+            auto emit = [&](float ref, auto track, float& largest) {
+                const uint64_t ref2 = pair(-ref, -ref);
+                uint64_t sum_a = pair(0.f, 0.f), sum_b = pair(0.f, 0.f);
+                float x0 = -INFINITY, x1 = -INFINITY, x2 = -INFINITY, x3 = -INFINITY;
+                uint32_t pk[2][16];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    s[j] = __uint_as_float(v0[j]);
-                    s[32 + j] = __uint_as_float(v1[j]);
+                for (int c = 0; c < 4; ++c) {
+                    if (c < 2 || tiles == 2) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            float e0, e1, e2, e3;
+                            unpair(fma_pair(pair(SCORE(32 * c + i), SCORE(32 * c + i + 1)), scale2, ref2), e0, e1);
+                            unpair(fma_pair(pair(SCORE(32 * c + i + 2), SCORE(32 * c + i + 3)), scale2, ref2), e2, e3);
+                            if constexpr (decltype(track)::value) {
+                                if (i & 4) {
+                                    x2 = max3(x2, e0, e1);
+                                    x3 = max3(x3, e2, e3);
+                                } else {
+                                    x0 = max3(x0, e0, e1);
+                                    x1 = max3(x1, e2, e3);
+                                }
+                            }
+                            const float a0 = ex2(e0), a1 = ex2(e1), a2 = ex2(e2), a3 = ex2(e3);
+                            sum_a = add_pair(sum_a, pair(a0, a1));
+                            sum_b = add_pair(sum_b, pair(a2, a3));
+                            pk[c & 1][i / 2] = pack_bf16(a0, a1);
+                            pk[c & 1][i / 2 + 1] = pack_bf16(a2, a3);
+                            // (a chunk is stored while the next one's exponentials are on their way: a store right
+                            // after its own chunk would hold them back until the chunk's last exponential is there)
+                            if (c > 0 && i == 16) tmem_st16(p_addr + 16 * (c - 1), pk[(c - 1) & 1]);
+                        }
+                    }
                 }
-            }
-            if ((i & 1) || i + 1 == n_kt) {   // the pair's scores are in registers: the next pair's may overwrite them
-                fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&s_read[t]);
-            }
-            // a tile that every row of this warp sees whole (below the diagonal, inside the window) needs no mask:
-            // the maximum is taken over the raw scores and the scale goes into the exponent's multiply-add
-            const bool whole = __all_sync(0xffffffffu, row_ok && kt * BN + BN - 1 <= row_pos && kt * BN >= row_lo);
-            float mx = -INFINITY;
-            if (whole) {
-#pragma unroll
-                for (int j = 0; j < BN; j += 2) mx = max3(mx, s[j], s[j + 1]);
-                mx *= p.scale_log2;
-            } else {
-#pragma unroll
-                for (int j = 0; j < BN; ++j) {
-                    const int kp = kt * BN + j;
-                    const bool seen = row_ok && kp <= row_pos && kp >= row_lo;
-                    s[j] = seen ? s[j] : -INFINITY;
-                    mx = fmaxf(mx, s[j]);
-                }
-                mx = mx == -INFINITY ? mx : mx * p.scale_log2;
-            }
+                tmem_st16(p_addr + 16 * (tiles == 2 ? 3 : 1), pk[1]);
+                float sum_even, sum_odd;
+                unpair(add_pair(sum_a, sum_b), sum_even, sum_odd);
+                largest = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
+                return sum_even + sum_odd;
+            };
             // m is the reference the exponentials are taken against, not the true maximum: it moves only when a
             // score exceeds it by more than 8 (probabilities then stay below 2^8, far from overflow), so that O, which
-            // sits in tensor memory, has to be rescaled only rarely
-            const float m_new = (m == -INFINITY || mx > m + 8.f) ? fmaxf(m, mx) : m;
-            const float corr = m_new == -INFINITY ? 1.f : ex2(m - m_new);
-            const float neg_ref = m_new == -INFINITY ? 0.f : -m_new;
-            m = m_new;
-            // exponents and the row's sum two numbers at a time (fma and add on pairs of floats)
-            const uint64_t scale2 = pair(p.scale_log2, p.scale_log2), ref2 = pair(neg_ref, neg_ref);
-            uint64_t sum2 = pair(0.f, 0.f);
-            uint32_t pk[BN / 2];
-#pragma unroll
-            for (int j = 0; j < BN; j += 2) {
-                float e0, e1;
-                unpair(fma_pair(pair(s[j], s[j + 1]), scale2, ref2), e0, e1);
-                const float a = ex2(e0), b = ex2(e1);
-                sum2 = add_pair(sum2, pair(a, b));
-                pk[j / 2] = pack_bf16(a, b);
+            // sits in tensor memory, has to be rescaled only rarely.  A pair that every row of this warp sees whole
+            // (below the diagonal, inside the window) is therefore tried against the reference as it stands, in one
+            // pass that also keeps the largest exponent; only if that shows a score more than 8 above the reference
+            // (or a row has no reference yet) is the pair done the long way: maximum first, then the exponentials.
+            const bool whole = __all_sync(0xffffffffu, row_ok && k0 + tiles * BN - 1 <= row_pos && k0 >= row_lo);
+            bool long_way = !__all_sync(0xffffffffu, whole && m != -INFINITY);
+            if (!long_way) {
+                float largest;
+                const float sum = emit(m, std::true_type(), largest);
+                long_way = __any_sync(0xffffffffu, largest > 8.f);
+                if (!long_way) l += sum;
             }
-            float sum_even, sum_odd;
-            unpair(sum2, sum_even, sum_odd);
-            l = l * corr + (sum_even + sum_odd);
-            if (i > 0) {
-                // the MMA that used the last probabilities and added into O has finished
-                ok = __all_sync(0xffffffffu, mbar_wait(&o_done[t], (i - 1) & 1));
-                if (!ok) break;
-                fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.f)) {   // the maximum of some row of this warp moved: rescale O
+            if (long_way) {
+                float mx = -INFINITY;
+                if (whole) {   // no mask: the maximum is taken over the raw scores
+                    float c0 = -INFINITY, c1 = -INFINITY, c2 = -INFINITY, c3 = -INFINITY;   // four chains, so that none waits for the last
+#pragma unroll
+                    for (int i = 0; i < 2 * BN; i += 8) {
+                        if (i < BN || tiles == 2) {
+                            c0 = max3(c0, SCORE(i), SCORE(i + 1));
+                            c1 = max3(c1, SCORE(i + 2), SCORE(i + 3));
+                            c2 = max3(c2, SCORE(i + 4), SCORE(i + 5));
+                            c3 = max3(c3, SCORE(i + 6), SCORE(i + 7));
+                        }
+                    }
+                    mx = fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)) * p.scale_log2;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 2 * BN; ++i) {
+                        const int kp = k0 + i;
+                        const bool seen = row_ok && i < tiles * BN && kp <= row_pos && kp >= row_lo;
+                        v[i >> 5][i & 31] = seen ? v[i >> 5][i & 31] : 0xff800000u;   // -inf
+                        mx = fmaxf(mx, SCORE(i));
+                    }
+                    mx = mx == -INFINITY ? mx : mx * p.scale_log2;
+                }
+                const float m_new = (m == -INFINITY || mx > m + 8.f) ? fmaxf(m, mx) : m;
+                const float corr = m_new == -INFINITY ? 1.f : ex2(m - m_new);
+                m = m_new;
+                if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+                    // the reference of some row of this warp moved: rescale O
 #pragma unroll
                     for (int c = 0; c < HD; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(lane_addr + O_COL + c, v);
+                        uint32_t o[32];
+                        tmem_ld32(o_addr + c, o);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
-                        tmem_st32(lane_addr + O_COL + c, v);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                        tmem_st32(o_addr + c, o);
                     }
-                    tmem_st_wait();
                 }
+                float unused;
+                l = l * corr + emit(m_new == -INFINITY ? 0.f : m_new, std::false_type(), unused);
             }
-            // probabilities of this row: 64 bfloat16 = one 128-byte row with its 16-byte chunks swizzled
-            unsigned char* prow = p_tile + r * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+#undef SCORE
             // positions past the sequence's end lie in a fetched page but were never written: their values must
             // not reach the sum, not even multiplied by zero.  Only the tile that holds the end has such keys; the
             // first query tile's warps clear them (both tiles' MMAs wait for these warps' arrival or come after it).
-            if (t == 0 && kt * BN + BN - 1 > pos_last) {
+            if (t == 0 && k0 + tiles * BN - 1 > pos_last) {
                 // (the values must have arrived, or they would land on top of the zeros)
-                ok = __all_sync(0xffffffffu, mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1));
+                ok = __all_sync(0xffffffffu, mbar_wait(&v_full[j % V_PAIRS], (j / V_PAIRS) & 1));
                 if (!ok) break;
-                unsigned char* vd = v_smem + (i % STAGES) * KV_BYTES;
-                const int first_bad = pos_last + 1 - kt * BN;
+                const int kt_end = pos_last / BN - kt_lo;   // the tile that holds the end, counted from this block's first
+                unsigned char* vd = v_smem + (kt_end % V_SLOTS) * KV_BYTES;
+                const int first_bad = pos_last + 1 - (kt_lo + kt_end) * BN;
                 for (int idx = quad * 32 + lane; idx < (BN - first_bad) * 16; idx += 128) {
                     const int row = first_bad + idx / 16, c = idx % 16;   // 16 chunks of 16 bytes per row: two boxes of 8
                     *reinterpret_cast<uint4*>(vd + (c >> 3) * (KV_BYTES / 2) + row * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
                 }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tmem_st_wait();
             fence_before();
-            mbar_arrive(&p_full[t]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[t]);
         }
-        if (ok && n_kt > 0) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[t], (n_kt - 1) & 1));
+        if (ok && n_kt > 0) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (n_pairs - 1) & 1));
         if (ok) {
             fence_after();
             const int g = r - tok * p.group;
@@ -560,7 +666,7 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
 #pragma unroll
                     for (int c = 0; c < HD; c += 32) {
                         uint32_t v[32];
-                        tmem_ld32(lane_addr + O_COL + c, v);
+                        tmem_ld32(o_addr + c, v);
                         tmem_ld_wait();
                         if (row_ok) {
 #pragma unroll
@@ -577,7 +683,7 @@ __global__ void __launch_bounds__(THREADS) attention_tcgen05_kernel(const __grid
 #pragma unroll
                 for (int c = 0; c < HD; c += 32) {
                     uint32_t v[32];
-                    tmem_ld32(lane_addr + O_COL + c, v);
+                    tmem_ld32(o_addr + c, v);
                     tmem_ld_wait();
                     if (row_ok) {
 #pragma unroll
@@ -749,7 +855,7 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
     if (q_map(&mq, q, n_tokens, nq, group, p.tq) != 0) return -1;
     if (pool_map(&mk, k_pool, pool_rows, p.box_rows) != 0) return -1;
     if (pool_map(&mv, v_pool, pool_rows, p.box_rows) != 0) return -1;
-    constexpr size_t smem = 1024 + 2 * Q_BYTES + (size_t)STAGES * 2 * KV_BYTES + 2 * P_BYTES;
+    constexpr size_t smem = 1024 + 2 * Q_BYTES + (size_t)(K_SLOTS + V_SLOTS) * KV_BYTES;
     static bool raised[64] = {};
     if (rmx_first_on_device(raised)) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
