@@ -23,9 +23,14 @@
 //            tensor memory) and holds its 128 scores of a pair in registers.  The reference m that exponentials
 //            are taken against moves only when a score exceeds it by more than 2^8, so a pair is first tried in one
 //            pass against the reference as it stands (exponent, largest exponent seen, sum, probabilities as
-//            bfloat16 into tensor memory), and done the long way (maximum, new reference, O rescaled, exponentials)
-//            only where that pass meets a larger score, a row has no reference yet, or the pair needs a mask (the
-//            diagonal, the window's edge)
+//            bfloat16 into tensor memory), and done the long way (maximum, new reference, O rescaled, the same pass
+//            again) only where that pass meets a larger score or a row has no reference yet.  A pair that needs a
+//            mask (the diagonal, the window's edge) is masked in tensor memory first and then treated like any other
+//
+// Code size: the kernel's code is fetched anew at every launch (the kernels between two launches push it out of
+// the instruction caches), and straight-line code is fetched at a few instructions a microsecond: 30 KB of
+// unrolled paths that a block runs once or twice cost 100 us a launch when they were there.  So there is one
+// instance of the pass over a pair's scores, and everything that runs once a block or rarely is a rolled loop.
 //
 // Registers: the roles' warpgroup gives most of its registers to the softmax warpgroups (setmaxnreg).
 // Tensor memory (all 512 columns): scores 128, O of each query tile 128, P of each query tile 64 (128 keys as
@@ -36,7 +41,6 @@
 #include <cuda.h>
 
 #include <mutex>
-#include <type_traits>
 #include <unordered_map>
 
 #include "common.cuh"
@@ -516,7 +520,27 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1));
             if (!ok) break;
             fence_after();
-            // the row's scores of the whole pair: the second tile's are on their way while the first's maximum is taken
+            // A pair that some row of this warp does not see whole (the diagonal, the window's edge, rows past the
+            // tile's end, a missing second key tile) is masked first, in a rolled loop that takes the scores through
+            // registers back into tensor memory with -inf where the row must not look: such pairs are few, and the
+            // code for all that follows is the same for every pair (code that a block runs once costs more to
+            // fetch than to run).
+            const bool whole = __all_sync(0xffffffffu, row_ok && k0 + tiles * BN - 1 <= row_pos && k0 >= row_lo);
+            if (!whole) {
+                // key k0 + i is seen if lo <= i <= hi
+                const int lo = row_lo - k0, hi = row_ok ? min(row_pos - k0, tiles * BN - 1) : -1 << 20;
+#pragma unroll 1
+                for (int c = 0; c < 2 * BN; c += 32) {
+                    uint32_t w[32];
+                    tmem_ld32(s_addr + c, w);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) w[i] = (c + i >= lo && c + i <= hi) ? w[i] : 0xff800000u;   // -inf
+                    tmem_st32(s_addr + c, w);
+                }
+                tmem_st_wait();
+            }
+            // the row's scores of the pair, all in registers
             uint32_t v[4][32];
 #define SCORE(i) __uint_as_float(v[(i) >> 5][(i) & 31])
             tmem_ld32(s_addr, v[0]);
@@ -537,7 +561,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             // Exponents against the reference `ref` and the row's sum, two numbers at a time (fma and add on pairs of
             // floats); the probabilities go into tensor memory as bfloat16, 32 keys in 16 columns.  With `track` the
             // largest exponent is kept as well.
-            auto emit = [&](float ref, auto track, float& largest) {
+            auto emit = [&](float ref, float& largest) {
                 const uint64_t ref2 = pair(-ref, -ref);
                 uint64_t sum_a = pair(0.f, 0.f), sum_b = pair(0.f, 0.f);
                 float x0 = -INFINITY, x1 = -INFINITY, x2 = -INFINITY, x3 = -INFINITY;
@@ -550,14 +574,12 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
                             float e0, e1, e2, e3;
                             unpair(fma_pair(pair(SCORE(32 * c + i), SCORE(32 * c + i + 1)), scale2, ref2), e0, e1);
                             unpair(fma_pair(pair(SCORE(32 * c + i + 2), SCORE(32 * c + i + 3)), scale2, ref2), e2, e3);
-                            if constexpr (decltype(track)::value) {
-                                if (i & 4) {
-                                    x2 = max3(x2, e0, e1);
-                                    x3 = max3(x3, e2, e3);
-                                } else {
-                                    x0 = max3(x0, e0, e1);
-                                    x1 = max3(x1, e2, e3);
-                                }
+                            if (i & 4) {
+                                x2 = max3(x2, e0, e1);
+                                x3 = max3(x3, e2, e3);
+                            } else {
+                                x0 = max3(x0, e0, e1);
+                                x1 = max3(x1, e2, e3);
                             }
                             const float a0 = ex2(e0), a1 = ex2(e1), a2 = ex2(e2), a3 = ex2(e3);
                             sum_a = add_pair(sum_a, pair(a0, a1));
@@ -578,21 +600,15 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             };
             // m is the reference the exponentials are taken against, not the true maximum: it moves only when a
             // score exceeds it by more than 8 (probabilities then stay below 2^8, far from overflow), so that O, which
-            // sits in tensor memory, has to be rescaled only rarely.  A pair that every row of this warp sees whole
-            // (below the diagonal, inside the window) is therefore tried against the reference as it stands, in one
-            // pass that also keeps the largest exponent; only if that shows a score more than 8 above the reference
-            // (or a row has no reference yet) is the pair done the long way: maximum first, then the exponentials.
-            const bool whole = __all_sync(0xffffffffu, row_ok && k0 + tiles * BN - 1 <= row_pos && k0 >= row_lo);
-            bool long_way = !__all_sync(0xffffffffu, whole && m != -INFINITY);
-            if (!long_way) {
-                float largest;
-                const float sum = emit(m, std::true_type(), largest);
-                long_way = __any_sync(0xffffffffu, largest > 8.f);
-                if (!long_way) l += sum;
-            }
-            if (long_way) {
-                float mx = -INFINITY;
-                if (whole) {   // no mask: the maximum is taken over the raw scores
+            // sits in tensor memory, has to be rescaled only rarely.  A pair is therefore tried against the reference
+            // as it stands, in one pass that also keeps the largest exponent; only if that shows a score more than 8
+            // above the reference (or a row has no reference yet) is the pair done the long way: maximum, new
+            // reference, O rescaled, and the same pass once more.
+            bool long_way = !__all_sync(0xffffffffu, m != -INFINITY);
+            float ref = m, corr = 1.f, sum;
+#pragma unroll 1
+            for (;;) {
+                if (long_way) {
                     float c0 = -INFINITY, c1 = -INFINITY, c2 = -INFINITY, c3 = -INFINITY;   // four chains, so that none waits for the last
 #pragma unroll
                     for (int i = 0; i < 2 * BN; i += 8) {
@@ -603,35 +619,31 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
                             c3 = max3(c3, SCORE(i + 6), SCORE(i + 7));
                         }
                     }
-                    mx = fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)) * p.scale_log2;
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 2 * BN; ++i) {
-                        const int kp = k0 + i;
-                        const bool seen = row_ok && i < tiles * BN && kp <= row_pos && kp >= row_lo;
-                        v[i >> 5][i & 31] = seen ? v[i >> 5][i & 31] : 0xff800000u;   // -inf
-                        mx = fmaxf(mx, SCORE(i));
-                    }
+                    float mx = fmaxf(fmaxf(c0, c1), fmaxf(c2, c3));
                     mx = mx == -INFINITY ? mx : mx * p.scale_log2;
-                }
-                const float m_new = (m == -INFINITY || mx > m + 8.f) ? fmaxf(m, mx) : m;
-                const float corr = m_new == -INFINITY ? 1.f : ex2(m - m_new);
-                m = m_new;
-                if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-                    // the reference of some row of this warp moved: rescale O
+                    const float m_new = (m == -INFINITY || mx > m + 8.f) ? fmaxf(m, mx) : m;
+                    corr = m_new == -INFINITY ? 1.f : ex2(m - m_new);
+                    ref = m_new == -INFINITY ? 0.f : m_new;
+                    m = m_new;
+                    if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+                        // the reference of some row of this warp moved: rescale O
+#pragma unroll 1
+                        for (int c = 0; c < HD; c += 32) {
+                            uint32_t o[32];
+                            tmem_ld32(o_addr + c, o);
+                            tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < HD; c += 32) {
-                        uint32_t o[32];
-                        tmem_ld32(o_addr + c, o);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                        tmem_st32(o_addr + c, o);
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                            tmem_st32(o_addr + c, o);
+                        }
                     }
                 }
-                float unused;
-                l = l * corr + emit(m_new == -INFINITY ? 0.f : m_new, std::false_type(), unused);
+                float largest;
+                sum = emit(ref, largest);
+                if (long_way || !__any_sync(0xffffffffu, largest > 8.f)) break;
+                long_way = true;
             }
+            l = l * corr + sum;
 #undef SCORE
             // positions past the sequence's end lie in a fetched page but were never written: their values must
             // not reach the sum, not even multiplied by zero.  Only the tile that holds the end has such keys; the
@@ -663,8 +675,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
                 // this run's share of the row (a run without keys leaves maximum -inf and sum 0, and no numbers)
                 float* dst = p.part_o + ((size_t)blockIdx.z * p.n_rows + row) * HD;
                 if (n_kt > 0) {
-#pragma unroll
-                    for (int c = 0; c < HD; c += 32) {
+#pragma unroll 1
+                    for (int c = 0; c < HD; c += 32) {   // (rolled, like every loop that runs once a block: code that is fetched once costs more than it saves)
                         uint32_t v[32];
                         tmem_ld32(o_addr + c, v);
                         tmem_ld_wait();
@@ -680,7 +692,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             } else if (n_kt > 0) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 __nv_bfloat16* dst = p.out + row * HD;
-#pragma unroll
+#pragma unroll 1
                 for (int c = 0; c < HD; c += 32) {
                     uint32_t v[32];
                     tmem_ld32(o_addr + c, v);

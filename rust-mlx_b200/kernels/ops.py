@@ -416,18 +416,24 @@ def tcgen05_attention_supported(hd: int, group: int, page_size: int) -> bool:
 
 
 def tcgen05_attention_shape(counts: list, nkv: int, group: int, max_seq_len: int) -> tuple:
-    """(query tiles a block, runs of keys) for prompt portions of ``counts`` tokens: two neighbouring tiles of 128
-    rows a block (they share the key tiles it fetches); where that leaves SMs without work, the tiles' keys in as
-    many runs as fill them (each of at least 12 key tiles of 64, at most 8 runs: measured, shorter runs cost more
-    in the second kernel that adds them than they gain), or failing that one tile a block."""
+    """(query tiles a block, runs of keys) for prompt portions of ``counts`` tokens.  Measured on 148 SMs: a grid of
+    about one block an SM (not more) is fastest; two neighbouring tiles of 128 rows a block, which share the key and
+    value tiles it fetches, win once a sequence has some 2,000 keys, one tile a block below that; where whole tiles
+    leave SMs without work, every tile's keys go in as many runs as fill them (at most 8, each of at least 4 key
+    tiles of 64), whose shares a second kernel adds."""
     tile = 128 // group
+    sms = _sm_count()
     pairs = sum(-(-c // (2 * tile)) for c in counts) * nkv
-    if pairs >= _sm_count():
+    singles = sum(-(-c // tile) for c in counts) * nkv
+    key_tiles = -(-max_seq_len // 64)
+    if 4 * pairs >= 3 * sms:
         return 2, 1
-    runs = min(_sm_count() // pairs, -(-max_seq_len // 64) // 12, 8)
-    if runs >= 2:
-        return 2, runs
-    return 1, 1
+    long_keys = max_seq_len >= 2048
+    if 4 * singles >= 3 * sms:   # one tile a block would fill the SMs
+        return (2, max(1, min(sms // pairs, 8, key_tiles // 4))) if long_keys else (1, 1)
+    if long_keys:
+        return 2, max(1, min(sms // pairs, 8, key_tiles // 4))
+    return 1, max(1, min(sms // singles, 8, key_tiles // 4))
 
 
 def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, per_block=None,

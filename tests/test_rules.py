@@ -75,3 +75,6 @@ def test_division_of_prompt_attention(ops):
     assert ops.tcgen05_attention_shape([512], 8, 4, 8192) == (2, 2)
     assert ops.tcgen05_attention_shape([64], 8, 4, 65536) == (2, 8)
     assert ops.tcgen05_attention_shape([40, 40, 40], 2, 16, 40) == (1, 1)
+    assert ops.tcgen05_attention_shape([1024], 8, 4, 5120) == (2, 1)       # 128 blocks of two tiles: about one an SM
+    assert ops.tcgen05_attention_shape([64], 8, 4, 1064) == (1, 4)         # few keys and few tiles: short runs, one tile a block
+    assert ops.tcgen05_attention_shape([128, 128, 128, 128], 8, 4, 1128) == (1, 1)
