@@ -50,7 +50,11 @@ constexpr int HD = 128, BM = 128, BN = 64;
 constexpr int K_PAIRS = 3, V_PAIRS = 2;     // rings of pairs of key tiles and of value tiles (the keys are asked for earlier: the scores run a pair ahead)
 constexpr int K_SLOTS = 2 * K_PAIRS, V_SLOTS = 2 * V_PAIRS;
 constexpr int THREADS = 384;   // a warpgroup of roles (producer, two MMA issuers, a spare warp) and one of softmax warps for each query tile
-constexpr int ROLE_REGS = 56, SOFTMAX_REGS = 224;   // registers a thread after the warpgroups have traded them (128 x 56 + 256 x 224 <= 65536)
+// Registers a thread: what the block is launched with (384 threads: 65536 / 384, rounded down to a multiple of 8), and
+// what the warpgroups have after trading.  A warpgroup that asks for more waits, without a limit, until others of its
+// own block have given that much back: the roles' warpgroup must free at least what the two softmax warpgroups take.
+constexpr int LAUNCH_REGS = 168, ROLE_REGS = 56, SOFTMAX_REGS = 224;
+static_assert((LAUNCH_REGS - ROLE_REGS) * 128 >= (SOFTMAX_REGS - LAUNCH_REGS) * (THREADS - 128), "the softmax warpgroups would wait for registers that nobody frees");
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int Q_BYTES = BM * HD * 2;        // 32 KB: two boxes of [128 rows][64 columns]
@@ -872,6 +876,10 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
     if (rmx_first_on_device(raised)) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RMX_FAIL("attention_tcgen05: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
+        cudaFuncAttributes fa;
+        e = cudaFuncGetAttributes(&fa, attention_tcgen05_kernel);
+        if (e != cudaSuccess || fa.numRegs != LAUNCH_REGS)   // the trade of registers between the warpgroups is worked out for this number
+            RMX_FAIL("attention_tcgen05: built with %d registers a thread, not %d", e == cudaSuccess ? fa.numRegs : -1, LAUNCH_REGS);
     }
     // blocks are handed to the SMs in the order x, then y: all kv heads of the tile that sees the most keys first
     attention_tcgen05_kernel<<<dim3(nkv, n_tiles, n_splits), THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
