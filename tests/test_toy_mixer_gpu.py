@@ -240,6 +240,107 @@ def test_toy_routed_feed_forward_and_unrotated_layers(tmp_path):
         unregister_architecture("ToyRoutedForCausalLM")
 
 
+@pytest.mark.parametrize("name, dtype", [("A", "float32"), ("D", "bfloat16")])
+def test_toy_position_encoding(tmp_path, name, dtype):
+    """Another position encoding, defined here and built by the engine without a change to its files: the angle of
+    pair j at position p is ln(1 + p) (j + 1) 0.37, which no table of inverse frequencies expresses (it is not a
+    multiple of the position), over the first three quarters of a head only, and with a factor of its own on the
+    scores.  The mixer asks its position encoding for the step's cosines and sines and hands them to the kernels
+    (in bfloat16 with heads of 128 a decoding step's attention kernel rotates with them itself).  Whole, in
+    portions, token by token at the end, and mixed; compared with the plain restatement below."""
+    import replay
+    from rust_mlx_b200.config import Qwen3Config
+    from rust_mlx_b200.engine import Engine
+    from rust_mlx_b200.models.qwen3 import build_qwen3
+    from rust_mlx_b200.parts import PositionEncoding
+    from rust_mlx_b200.parts.attention import AttentionMixer
+    from rust_mlx_b200.registry import register_architecture, unregister_architecture
+    from rust_mlx_b200.weights import write_random_model
+
+    def toy_angles(positions, rotary_dim):
+        j = torch.arange(rotary_dim // 2, device=positions.device, dtype=torch.float32)
+        return torch.log1p(positions.to(torch.float32))[:, None] * ((j + 1.0) * 0.37)
+
+    class LogPositions(PositionEncoding):
+        score_scale = 1.25
+
+        def __init__(self, rotary_dim):
+            self.rotary_dim, self.inv_freq = rotary_dim, None
+
+        def angles(self, batch):
+            key = ("log positions", self.rotary_dim)
+            if key not in batch.per_step:
+                a = toy_angles(batch.positions, self.rotary_dim)
+                batch.per_step[key] = torch.cat([a.cos(), a.sin()], 1).contiguous()
+            return batch.per_step[key]
+
+    raw, page = tiny.CONFIGS[name]
+    rotary = raw["head_dim"] if dtype == "bfloat16" else raw["head_dim"] * 3 // 4 // 2 * 2
+
+    def build(config):
+        spec = build_qwen3(config)
+        toy = LogPositions(rotary)
+        for block in spec.blocks:
+            old = block.mixer
+            block.mixer = AttentionMixer(old.prefix, old.width, old.heads, old.kv_heads, old.head_dim, toy,
+                                         qk_norm_eps=old.qk_norm_eps, window=old.window, bias=old.bias)
+        return spec
+
+    def rotate(x, positions):   # half-split pairs (j, j + rotary / 2) of the first `rotary` numbers of every head
+        a = toy_angles(positions, rotary).double()[:, None, :]
+        half = rotary // 2
+        x1, x2 = x[..., :half], x[..., half:rotary]
+        return torch.cat([x1 * a.cos() - x2 * a.sin(), x2 * a.cos() + x1 * a.sin(), x[..., rotary:]], -1)
+
+    def plain_logits(folder, ids, rounding=None):
+        """The plain implementation's forward pass (tests/plain_qwen3.py: ``forward``, ``attention``) with the toy
+        rotation and the factor on the scores in place of the model's own."""
+        config, tensors = plain.read_folder(folder)
+        w = plain.prepare_weights(config, tensors, rounding)
+        r = plain.make_round(rounding)
+        eps, T = config["rms_norm_eps"], len(ids)
+        nq, nkv, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+        pos = torch.arange(T)
+        windows = plain.layer_windows(config)
+        h = plain.embedding(w["model.embed_tokens.weight"], ids)
+        for i in range(config["num_hidden_layers"]):
+            p = f"model.layers.{i}"
+            a = p + ".self_attn"
+            x = r(plain.rms_norm(h, w[p + ".input_layernorm.weight"], eps))
+            q = plain.linear(x, w[a + ".q_proj.weight"], None, r).reshape(T, nq, hd)
+            k = plain.linear(x, w[a + ".k_proj.weight"], None, r).reshape(T, nkv, hd)
+            v = plain.linear(x, w[a + ".v_proj.weight"], None, r).reshape(T, nkv, hd)
+            q = r(rotate(plain.rms_norm(q, w[a + ".q_norm.weight"], eps), pos))
+            k = r(rotate(plain.rms_norm(k, w[a + ".k_norm.weight"], eps), pos))
+            o = r(plain.attention_scores(q, k, v, pos, windows[i], 1.25))
+            h = h + plain.linear(o.reshape(T, nq * hd), w[a + ".o_proj.weight"], None, r)
+            x = r(plain.rms_norm(h, w[p + ".post_attention_layernorm.weight"], eps))
+            h = h + plain.swiglu_mlp(x, w, p + ".mlp", r)
+        x = r(plain.rms_norm(h, w["model.norm.weight"], eps))
+        head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings") else w["lm_head.weight"]
+        return plain.linear(x, head)
+
+    register_architecture("ToyLogPositionsForCausalLM", Qwen3Config, build)
+    try:
+        config = dict(raw, architectures=["ToyLogPositionsForCausalLM"])
+        folder = str(tmp_path / "logpos")
+        write_random_model(Qwen3Config.from_dict(config), folder, seed=37, store_dtype="float32" if dtype == "float32" else "bfloat16")
+        reqs = {f"r{i}": p for i, p in enumerate(tiny.prompts(raw["vocab_size"], [70, 41, 9, 55], seed=6))}
+        exact = {rid: plain_logits(folder, ids).float() for rid, ids in reqs.items()}
+        bound = {rid: 5e-5 for rid in reqs}
+        if dtype == "bfloat16":   # as far from the exact logits as the same roundings put the plain restatement, at least 2e-2
+            bound = {rid: max(2e-2, tiny.max_abs(plain_logits(folder, ids, "bfloat16").float(), exact[rid])) for rid, ids in reqs.items()}
+        for way in ("whole", "portions", "tail_one_by_one", "mixed"):
+            steps = getattr(replay, way)(reqs, **({"live": 3} if way == "mixed" else {}))
+            eng = Engine(folder, dtype=dtype, max_tokens=replay.tokens_needed(steps, page), page_size=page, max_requests=4)
+            assert eng.graphs is None      # the toy part does not declare itself safe to capture
+            got = replay.run_engine(eng, steps)
+            for rid in reqs:
+                assert tiny.max_abs(got[rid], exact[rid]) < bound[rid], (way, rid, tiny.max_abs(got[rid], exact[rid]))
+    finally:
+        unregister_architecture("ToyLogPositionsForCausalLM")
+
+
 def test_toy_block_that_remembers_two_things(tmp_path):
     """A block defined here with two stateful sub-layers (attention over pages and a running average in a state
     slot, side by side): it says so in ``cache_specs()``, its schedule entry names one cache id for each, and its
