@@ -273,19 +273,32 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_smem)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
-    // which sequence and which pair of its tiles this block has: pairs are counted sequence by sequence, and handed
-    // out from the last to the first (tiles late in a sequence see the most keys)
+    // Which sequence and which pair of its tiles this block has: pairs are counted sequence by sequence, and handed
+    // out from the last to the first (tiles late in a sequence see the most keys).  A block's start is a chain of
+    // loads that wait for one another (the sequences' tokens, then the tile's position and its pages, then the
+    // copies), each most of a microsecond, so whatever needs nothing from them runs while they are under way: the
+    // first sequences' token counts are asked for before the stages are zeroed.
+    const int pair_tokens = p.per_block * p.tq;
+    int first_a = 0, first_n = 0;
+    if (tid < p.n_seqs) {
+        first_a = p.q_start[tid];
+        first_n = p.q_start[tid + 1] - first_a;
+    }
+    // the key and value stages start as zeros: a part of a tile that is never fetched (beyond the sequence's end, a
+    // page the request does not hold) must hold finite numbers, because a probability of zero still multiplies it
+    for (int idx = tid; idx < (K_SLOTS + V_SLOTS) * KV_BYTES / 16; idx += THREADS)
+        reinterpret_cast<uint4*>(kv_smem)[idx] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     {
-        const int pair_tokens = p.per_block * p.tq;
         int before_all = 0;
         for (int chunk = 0; chunk < p.n_seqs; chunk += THREADS) {
             const int sq = chunk + tid;
-            int a = 0, n = 0, pairs = 0;
-            if (sq < p.n_seqs) {
+            int a = first_a, n = first_n, pairs = 0;
+            if (chunk > 0 && sq < p.n_seqs) {
                 a = p.q_start[sq];
                 n = p.q_start[sq + 1] - a;
-                pairs = (n + pair_tokens - 1) / pair_tokens;
             }
+            if (sq < p.n_seqs) pairs = (n + pair_tokens - 1) / pair_tokens;
             int incl = pairs;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -310,21 +323,32 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             before_all += total;
         }
     }
-    // the key and value stages start as zeros: a part of a tile that is never fetched (beyond the sequence's end, a
-    // page the request does not hold) must hold finite numbers, because a probability of zero still multiplies it
-    for (int idx = tid; idx < (K_SLOTS + V_SLOTS) * KV_BYTES / 16; idx += THREADS)
-        reinterpret_cast<uint4*>(kv_smem)[idx] = make_uint4(0u, 0u, 0u, 0u);
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     fence_before();
     __syncthreads();
     fence_after();
     const uint32_t tmem = tmem_base_smem;
     const int seq = s_tile[0], tok0 = s_tile[1], n_tok = s_tile[2];
+    const bool two = n_tok > p.tq;   // the second tile has rows
+    const int* table = seq >= 0 ? p.block_table + (size_t)seq * p.table_stride : nullptr;
+    // The queries need the tile's first token only, and without a window the pages are read from the table's start:
+    // both are asked for before the tile's position is here.
+    int early[3] = {-1, -1, -1};   // the producer's first three runs of 32 table entries
+    if (warp == 0 && seq >= 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&q_full, two ? 2 * Q_BYTES : Q_BYTES);
+            for (int t = 0; t < (two ? 2 : 1); ++t) {
+                tma_3d(q_smem + t * Q_BYTES, &map_q, &q_full, 0, kvh * p.group, tok0 + t * p.tq);
+                tma_3d(q_smem + t * Q_BYTES + Q_BYTES / 2, &map_q, &q_full, 64, kvh * p.group, tok0 + t * p.tq);
+            }
+        }
+        if (p.window == 0 && p.n_splits == 1) {
+#pragma unroll
+            for (int i = 0; i < 3; ++i) early[i] = 32 * i + lane < p.table_stride ? table[32 * i + lane] : -1;
+        }
+    }
     int n_kt = 0, kt_lo = 0, pos0 = 0, pos_last = 0, lo_first = 0;
-    const int* table = nullptr;
     if (seq >= 0) {
         pos0 = p.positions[tok0];
-        table = p.block_table + (size_t)seq * p.table_stride;
         lo_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
         pos_last = pos0 + n_tok - 1;
         kt_lo = lo_first / BN;
@@ -336,7 +360,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             n_kt = last - first;
         }
     }
-    const bool two = n_tok > p.tq;   // the second tile has rows
     const int n_pairs = (n_kt + 1) / 2;
     // (the softmax warps hold a row's 128 scores in registers: the warpgroup of roles hands them most of its own,
     // every warp of a warpgroup as the first thing in its branch)
@@ -350,19 +373,13 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
         // runs of 32 entries, the last one still on its way), so that no copy waits for a load of its page's number
         // from global memory.
         constexpr uint32_t FULL = 0xffffffffu;
-        if (lane == 0) {
-            mbar_expect_tx(&q_full, two ? 2 * Q_BYTES : Q_BYTES);
-            for (int t = 0; t < (two ? 2 : 1); ++t) {
-                tma_3d(q_smem + t * Q_BYTES, &map_q, &q_full, 0, kvh * p.group, tok0 + t * p.tq);
-                tma_3d(q_smem + t * Q_BYTES + Q_BYTES / 2, &map_q, &q_full, 64, kvh * p.group, tok0 + t * p.tq);
-            }
-        }
         int win = ((kt_lo * BN) >> p.page_shift) & ~31;   // the table entry that lane 0 of `cur` holds
         auto entries = [&](int first) {
             const int e = first + lane;
             return e < p.table_stride ? table[e] : -1;
         };
-        int cur = entries(win), nxt = entries(win + 32), far = entries(win + 64);
+        const bool had = p.window == 0 && p.n_splits == 1;   // (then win is 0 and the entries were asked for above)
+        int cur = had ? early[0] : entries(win), nxt = had ? early[1] : entries(win + 32), far = had ? early[2] : entries(win + 64);
         auto wait = [&](uint64_t* bar, uint32_t parity) {
             int done = lane == 0 ? (int)mbar_wait(bar, parity) : 1;
             return __shfl_sync(FULL, done, 0) != 0;
