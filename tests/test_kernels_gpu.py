@@ -734,6 +734,47 @@ def test_attention_tcgen05_finds_a_far_key_and_respects_the_window_edge():
     assert status.item() == 0
 
 
+@pytest.mark.parametrize("shape", ["rising", "falling", "steps", "wide", "flat"])
+@pytest.mark.parametrize("per_block, runs", [(2, 1), (1, 1), (2, 3)])
+def test_attention_tcgen05_when_the_reference_has_to_move(shape, per_block, runs):
+    """The kernel takes exponentials against a reference that it moves only when a score exceeds it by 2^8: a pair of
+    key tiles is tried in one pass and done again where that pass meets a larger score.  Scores that rise with the
+    key's position make every pair move the reference (and rescale O); scores that fall never do after the first
+    keys; steps move it in the middle of a pair for some rows only; a wide spread mixes all of it; flat scores are
+    all equal.  Key j is a multiple of one direction, so the score of (query, key j) is known."""
+    nq, nkv, hd, page = 8, 2, 128, 64
+    lengths, new = [1500, 333], [330, 333]
+    k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, torch.bfloat16, seed=len(shape))
+    torch.manual_seed(7)
+    direction = torch.nn.functional.normalize(torch.randn(hd), dim=0)
+    for s, n in enumerate(lengths):
+        j = torch.arange(n, dtype=torch.float32)
+        amount = {"rising": j * 0.9, "falling": (n - j) * 0.9, "steps": torch.floor(j / 37.0) * 30.0,
+                  "wide": torch.randn(n) * 40.0, "flat": torch.full((n,), 3.0)}[shape]
+        keys = (amount[:, None] * direction[None, :] * (hd ** 0.5) / 8.0).to(torch.bfloat16)   # score = amount * |q . direction| / 8
+        ks[s] = keys[:, None, :].expand(n, nkv, hd).contiguous()
+        for i in range(-(-n // page)):
+            rows = keys[i * page:(i + 1) * page].to(DEV)
+            k_pool[table[s, i].item(), :, :rows.shape[0]] = rows[None].expand(nkv, rows.shape[0], hd)
+    qs = []
+    for c in new:
+        q = torch.randn(c, nq, hd) * 0.05 + direction * torch.linspace(2.0, 8.0, c)[:, None, None]   # rows of different steepness
+        qs.append(q.to(torch.bfloat16))
+    q = torch.cat(qs).to(DEV).reshape(-1, nq * hd)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full_like(q, float("nan"))
+    ops().attention_tcgen05(q, k_pool, v_pool, _Batch(lengths, new, status), table, page, out, nq, nkv, hd, 0, hd ** -0.5,
+                            per_block=per_block, n_splits=runs)
+    assert status.item() == 0
+    at = 0
+    for s, (n, c) in enumerate(zip(lengths, new)):
+        want = plain_attention(qs[s], ks[s], vs[s], torch.arange(n - c, n), 0, hd ** -0.5)
+        got = out[at:at + c].double().cpu().reshape(c, nq, hd)
+        assert not torch.isnan(got).any(), (s, n, c)
+        assert ((got - want).abs() <= 1e-2 * (1 + want.abs())).all(), (shape, s, (got - want).abs().max().item())
+        at += c
+
+
 @pytest.mark.parametrize("nq, nkv, page, norm, write_kv", [(32, 8, 64, True, True), (5, 3, 16, True, True), (4, 4, 8, False, True),
                                                            (6, 2, 32, True, False)])
 def test_qk_rope_cache_for_prompt_portions_agrees_with_the_general_kernel(nq, nkv, page, norm, write_kv):
