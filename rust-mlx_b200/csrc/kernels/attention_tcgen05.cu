@@ -1,4 +1,4 @@
-// Attention for prompt portions on the Blackwell tensor cores (tcgen05), head size 128, bfloat16.
+// Attention for prompt portions on the Blackwell tensor cores (tcgen05), head sizes 64 and 128, bfloat16.
 //
 // A block takes one kv head and one tile of 128 query rows of one sequence; a row is a (token, query
 // head of the group) pair, 128 / group tokens by `group` heads, so the heads that share a kv head share
@@ -46,7 +46,9 @@
 #include "common.cuh"
 
 namespace {
-constexpr int HD = 128, BM = 128, BN = 64;
+constexpr int BM = 128, BN = 64;
+constexpr int BOX_BYTES = 128;              // a row of a copied box: 64 numbers of d
+constexpr int Q_BOX = BM * BOX_BYTES, KV_BOX = BN * BOX_BYTES;   // 16 KB and 8 KB: a tile's rows by 64 numbers of d
 constexpr int K_PAIRS = 3, V_PAIRS = 2;     // rings of pairs of key tiles and of value tiles (the keys are asked for earlier: the scores run a pair ahead)
 constexpr int K_SLOTS = 2 * K_PAIRS, V_SLOTS = 2 * V_PAIRS;
 constexpr int THREADS = 384;   // a warpgroup of roles (producer, two MMA issuers, a spare warp) and one of softmax warps for each query tile
@@ -57,13 +59,11 @@ constexpr int LAUNCH_REGS = 168, ROLE_REGS = 56, SOFTMAX_REGS = 224;
 static_assert((LAUNCH_REGS - ROLE_REGS) * 128 >= (SOFTMAX_REGS - LAUNCH_REGS) * (THREADS - 128), "the softmax warpgroups would wait for registers that nobody frees");
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr int Q_BYTES = BM * HD * 2;        // 32 KB: two boxes of [128 rows][64 columns]
-constexpr int KV_BYTES = BN * HD * 2;       // 16 KB per key tile, the same per value tile
 // Tensor memory: the scores of a pair of key tiles in columns 0..127, one buffer that the two query tiles take in
-// turns (a tile's softmax warps read their scores into registers and hand it on); O of tile t in 128 (1 + t) ..;
-// P of tile t, bfloat16, 128 keys in 64 columns, from 384 + 64 t.
+// turns (a tile's softmax warps read their scores into registers and hand it on); O of tile t, HD columns, from
+// 128 + HD t; P of tile t, bfloat16, 128 keys in 64 columns, after them.
 constexpr int TMEM_COLS = 512;              // two query tiles: all of an SM's tensor memory
-constexpr int S_COL = 0, O_COL = 128, O_COLS = 128, P_COL = 384, P_COLS = 64;
+constexpr int S_COL = 0, O_COL = 128, P_COLS = 64;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -226,10 +226,14 @@ struct Params {
 // One block: two neighbouring query tiles (A and B, 128 rows each) of one sequence against one kv head.  Both use
 // every key and value tile the block fetches, and while the softmax warps of one tile work the tensor cores
 // serve the other.
+template <int HD>
 __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                    const __grid_constant__ CUtensorMap map_k,
                                                                    const __grid_constant__ CUtensorMap map_v,
                                                                    const Params p) {
+    constexpr int BOXES = HD / 64;                      // boxes of 64 numbers of d in a head
+    constexpr int Q_BYTES = BOXES * Q_BOX, KV_BYTES = BOXES * KV_BOX;   // a query tile; a key tile, and the same a value tile
+    constexpr int O_COLS = HD, P_COL = O_COL + 2 * O_COLS;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_smem = base;                               // [2 tiles][2 boxes][128 rows][128 B]
@@ -337,8 +341,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
         if (lane == 0) {
             mbar_expect_tx(&q_full, two ? 2 * Q_BYTES : Q_BYTES);
             for (int t = 0; t < (two ? 2 : 1); ++t) {
-                tma_3d(q_smem + t * Q_BYTES, &map_q, &q_full, 0, kvh * p.group, tok0 + t * p.tq);
-                tma_3d(q_smem + t * Q_BYTES + Q_BYTES / 2, &map_q, &q_full, 64, kvh * p.group, tok0 + t * p.tq);
+#pragma unroll
+                for (int x = 0; x < BOXES; ++x)
+                    tma_3d(q_smem + t * Q_BYTES + x * Q_BOX, &map_q, &q_full, 64 * x, kvh * p.group, tok0 + t * p.tq);
             }
         }
         if (p.window == 0 && p.n_splits == 1) {
@@ -385,8 +390,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             return __shfl_sync(FULL, done, 0) != 0;
         };
         // this lane's copy within a pair: which tile of the pair, which box of the tile, which half of d
-        const int boxes = BN / p.box_rows, per_tile = 2 * boxes;
-        const int my_tile = lane / per_tile, my_box = (lane % per_tile) >> 1, my_half = lane & 1;
+        const int boxes = BN / p.box_rows, per_tile = BOXES * boxes;
+        const int my_tile = lane / per_tile, my_box = (lane % per_tile) / BOXES, my_half = lane % BOXES;
         const uint32_t copy_bytes = p.box_rows * 64 * 2u;
         // the copies of tiles first .. first + n - 1 (keys when `keys`, else values) into their slots, counted by `bar`
         auto fetch = [&](int first, int n, bool keys, uint64_t* bar) {
@@ -413,8 +418,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             if (mine) {
                 const int st = i % (keys ? K_SLOTS : V_SLOTS);
                 const int row = (page * p.nkv + kvh) * p.page_size + (kp & (p.page_size - 1));
-                unsigned char* dst = keys ? k_smem + st * (KV_BYTES / 2) + my_half * (K_SLOTS * KV_BYTES / 2)
-                                          : v_smem + st * KV_BYTES + my_half * (KV_BYTES / 2);
+                unsigned char* dst = keys ? k_smem + st * KV_BOX + my_half * (K_SLOTS * KV_BOX)
+                                          : v_smem + st * KV_BYTES + my_half * KV_BOX;
                 tma_2d(dst + my_box * p.box_rows * 128, keys ? &map_k : &map_v, bar, my_half * 64, row);
             }
             __syncwarp();
@@ -471,13 +476,13 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
                 }
                 fence_after();
                 const uint64_t q_desc = q_desc0 + (uint64_t)((t * Q_BYTES) >> 4);
-                const uint64_t k_desc = k_desc0 + (uint64_t)(((j % K_PAIRS) * 2 * (KV_BYTES / 2)) >> 4);
+                const uint64_t k_desc = k_desc0 + (uint64_t)(((j % K_PAIRS) * 2 * KV_BOX) >> 4);
                 const uint32_t d_addr = tm + S_COL;
                 if (elect_one()) {
 #pragma unroll
                     for (int kk = 0; kk < HD / 16; ++kk)
-                        umma(d_addr, q_desc + (uint64_t)(((kk >> 2) * (Q_BYTES / 2) + (kk & 3) * 32) >> 4),
-                             k_desc + (uint64_t)(((kk >> 2) * (K_SLOTS * KV_BYTES / 2) + (kk & 3) * 32) >> 4), id_s, kk > 0);
+                        umma(d_addr, q_desc + (uint64_t)(((kk >> 2) * Q_BOX + (kk & 3) * 32) >> 4),
+                             k_desc + (uint64_t)(((kk >> 2) * (K_SLOTS * KV_BOX) + (kk & 3) * 32) >> 4), id_s, kk > 0);
                     umma_commit(&s_full[t]);
                     if (t == n_t - 1) umma_commit(&k_empty[j % K_PAIRS]);   // the pair's keys are free after the last tile's scores
                 }
@@ -489,7 +494,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             // reduction runs over a tile's 64 keys in 4 steps of 16; V is [key][d], MN-major: blocks of 64 d are 8 KB
             // apart, groups of 8 keys 1 KB
             const uint32_t id_o = idesc(HD, true);
-            const uint64_t v_desc0 = desc_mnmajor(q_addr + 2 * Q_BYTES + K_SLOTS * KV_BYTES, KV_BYTES / 2, 1024);
+            const uint64_t v_desc0 = desc_mnmajor(q_addr + 2 * Q_BYTES + K_SLOTS * KV_BYTES, KV_BOX, 1024);
             int t = 0, j = 0;
             for (int k = 0; k < jobs && ok; ++k) {
                 if (t == 0 && !wait(&v_full[j % V_PAIRS], (j / V_PAIRS) & 1)) { ok = false; break; }
@@ -676,9 +681,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
                 const int kt_end = pos_last / BN - kt_lo;   // the tile that holds the end, counted from this block's first
                 unsigned char* vd = v_smem + (kt_end % V_SLOTS) * KV_BYTES;
                 const int first_bad = pos_last + 1 - (kt_lo + kt_end) * BN;
-                for (int idx = quad * 32 + lane; idx < (BN - first_bad) * 16; idx += 128) {
-                    const int row = first_bad + idx / 16, c = idx % 16;   // 16 chunks of 16 bytes per row: two boxes of 8
-                    *reinterpret_cast<uint4*>(vd + (c >> 3) * (KV_BYTES / 2) + row * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                constexpr int CHUNKS = HD / 8;   // chunks of 16 bytes in a row: eight in every box
+                for (int idx = quad * 32 + lane; idx < (BN - first_bad) * CHUNKS; idx += 128) {
+                    const int row = first_bad + idx / CHUNKS, c = idx % CHUNKS;
+                    *reinterpret_cast<uint4*>(vd + (c >> 3) * KV_BOX + row * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             }
@@ -742,29 +748,38 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
 }
 
 // out[row] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the runs z of the row's keys, in run order.
+// A warp a row; a lane has HD / 32 neighbouring numbers of it.
+template <int HD>
 __global__ void __launch_bounds__(128) attention_tcgen05_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                       __nv_bfloat16* __restrict__ out, int n_rows, int n_splits,
                                                                       int first_row, int rows) {
+    constexpr int PER = HD / 32;
     const int lane = threadIdx.x & 31;
     if (blockIdx.x * 4 + (threadIdx.x >> 5) >= rows) return;
     const int row = first_row + blockIdx.x * 4 + (threadIdx.x >> 5);
     float M = -INFINITY;
     for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((size_t)z * n_rows + row) * 2]);
     float L = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
     for (int z = 0; z < n_splits; ++z) {
         const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((size_t)z * n_rows + row) * 2);
         if (ml.x == -INFINITY) continue;
         const float f = exp2f(ml.x - M);
-        const float4 v = *reinterpret_cast<const float4*>(part_o + ((size_t)z * n_rows + row) * HD + lane * 4);
+        const float* src = part_o + ((size_t)z * n_rows + row) * HD + lane * PER;
         L += f * ml.y;
-        acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+#pragma unroll
+        for (int i = 0; i < PER; i += 2) {
+            const float2 v = *reinterpret_cast<const float2*>(src + i);
+            acc[i] += f * v.x;
+            acc[i + 1] += f * v.y;
+        }
     }
     const float inv = L > 0.f ? 1.f / L : 0.f;
-    uint2 o;
-    o.x = pack_bf16(acc.x * inv, acc.y * inv);
-    o.y = pack_bf16(acc.z * inv, acc.w * inv);
-    *reinterpret_cast<uint2*>(out + (size_t)row * HD + lane * 4) = o;
+    __nv_bfloat16* dst = out + (size_t)row * HD + lane * PER;
+#pragma unroll
+    for (int i = 0; i < PER; i += 2) *reinterpret_cast<uint32_t*>(dst + i) = pack_bf16(acc[i] * inv, acc[i + 1] * inv);
 }
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -798,16 +813,16 @@ struct MapHash {
 std::mutex g_lock;
 std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;
 
-// A pool of one layer as [rows, 128] bfloat16; boxes of [box_rows, 64].
-int pool_map(CUtensorMap* map, const void* base, long long rows, int box_rows) {
+// A pool of one layer as [rows, hd] bfloat16; boxes of [box_rows, 64].
+int pool_map(CUtensorMap* map, const void* base, long long rows, int box_rows, int hd) {
     std::lock_guard<std::mutex> guard(g_lock);
-    const MapKey key{base, rows, 0, box_rows, 2};
+    const MapKey key{base, rows, hd, box_rows, 2};
     auto it = g_maps.find(key);
     if (it != g_maps.end()) { *map = it->second; return 0; }
     EncodeTiled fn = encoder();
     if (!fn) RMX_FAIL("attention_tcgen05: the driver has no cuTensorMapEncodeTiled");
-    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
     cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
@@ -819,17 +834,17 @@ int pool_map(CUtensorMap* map, const void* base, long long rows, int box_rows) {
     return 0;
 }
 
-// The queries [tokens, nq, 128]; boxes of [tq tokens, group heads, 64]: a tile's rows come out token by token, the
+// The queries [tokens, nq, hd]; boxes of [tq tokens, group heads, 64]: a tile's rows come out token by token, the
 // group's heads side by side.
-int q_map(CUtensorMap* map, const void* base, long long tokens, int nq, int group, int tq) {
+int q_map(CUtensorMap* map, const void* base, long long tokens, int nq, int group, int tq, int hd) {
     std::lock_guard<std::mutex> guard(g_lock);
-    const MapKey key{base, tokens, nq, group, 3};
+    const MapKey key{base, tokens, (long long)nq * 1024 + hd, group, 3};
     auto it = g_maps.find(key);
     if (it != g_maps.end()) { *map = it->second; return 0; }
     EncodeTiled fn = encoder();
     if (!fn) RMX_FAIL("attention_tcgen05: the driver has no cuTensorMapEncodeTiled");
-    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nq, (cuuint64_t)tokens};
-    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)nq * HD * 2};
+    cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)nq, (cuuint64_t)tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)nq * hd * 2};
     cuuint32_t box[3] = {64, (cuuint32_t)group, (cuuint32_t)tq};
     cuuint32_t elem[3] = {1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
@@ -840,11 +855,34 @@ int q_map(CUtensorMap* map, const void* base, long long tokens, int nq, int grou
     g_maps.emplace(key, *map);
     return 0;
 }
+template <int HD>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int n_tiles, int first_token,
+           int run_tokens, cudaStream_t stream) {
+    constexpr size_t smem = 1024 + (size_t)(HD / 64) * (2 * Q_BOX + (K_SLOTS + V_SLOTS) * KV_BOX);
+    static bool raised[64] = {};
+    if (rmx_first_on_device(raised)) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RMX_FAIL("attention_tcgen05: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
+        cudaFuncAttributes fa;
+        e = cudaFuncGetAttributes(&fa, attention_tcgen05_kernel<HD>);
+        if (e != cudaSuccess || fa.numRegs != LAUNCH_REGS)   // the trade of registers between the warpgroups is worked out for this number
+            RMX_FAIL("attention_tcgen05: built with %d registers a thread, not %d", e == cudaSuccess ? fa.numRegs : -1, LAUNCH_REGS);
+    }
+    // blocks are handed to the SMs in the order x, then y: all kv heads of the tile that sees the most keys first
+    attention_tcgen05_kernel<HD><<<dim3(p.nkv, n_tiles, p.n_splits), THREADS, smem, stream>>>(mq, mk, mv, p);
+    RMX_CHECK_LAUNCH("attention_tcgen05");
+    if (p.n_splits > 1) {
+        attention_tcgen05_merge_kernel<HD><<<(run_tokens * p.nq + 3) / 4, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, p.n_rows, p.n_splits,
+                                                                                          first_token * p.nq, run_tokens * p.nq);
+        RMX_CHECK_LAUNCH("attention_tcgen05_merge");
+    }
+    return 0;
+}
 }  // namespace
 
-// Head size 128, a group that divides 128, pages of at least 8 positions (a power of two).
+// Head size 64 or 128, a group that divides 128, pages of at least 8 positions (a power of two).
 RMX_API int rmx_attention_tcgen05_supports(int hd, int group, int page_size) {
-    return hd == 128 && group >= 1 && group <= 16 && (group & (group - 1)) == 0 && page_size >= 8 &&
+    return (hd == 64 || hd == 128) && group >= 1 && group <= 16 && (group & (group - 1)) == 0 && page_size >= 8 &&
            (page_size & (page_size - 1)) == 0;
 }
 
@@ -855,7 +893,7 @@ RMX_API int rmx_attention_tcgen05_tile_tokens(int group) { return BM / group; }
 // n_tiles: the number of blocks: sum over sequences of ceil(tokens / (tiles_per_block * 128 / group)).
 // pool_pages: pages in k_pool / v_pool.
 // n_splits > 1: every tile's keys in that many runs, one block each (blockIdx.z), added by a second kernel; part_o
-// [n_splits, n_tokens * nq, 128] and part_ml [n_splits, n_tokens * nq, 2] floats are their scratch; the sequences
+// [n_splits, n_tokens * nq, hd] and part_ml [n_splits, n_tokens * nq, 2] floats are their scratch; the sequences
 // given hold the step's tokens first_token .. first_token + run_tokens - 1 (only their rows of `out` are written).
 RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* q_start,
                                   const int* positions, const int* block_table, int table_stride, int page_size,
@@ -885,27 +923,11 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
     p.scale_log2 = scale * LOG2E;
     CUtensorMap mq, mk, mv;
     const long long pool_rows = (long long)pool_pages * nkv * page_size;
-    if (q_map(&mq, q, n_tokens, nq, group, p.tq) != 0) return -1;
-    if (pool_map(&mk, k_pool, pool_rows, p.box_rows) != 0) return -1;
-    if (pool_map(&mv, v_pool, pool_rows, p.box_rows) != 0) return -1;
-    constexpr size_t smem = 1024 + 2 * Q_BYTES + (size_t)(K_SLOTS + V_SLOTS) * KV_BYTES;
-    static bool raised[64] = {};
-    if (rmx_first_on_device(raised)) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) RMX_FAIL("attention_tcgen05: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
-        cudaFuncAttributes fa;
-        e = cudaFuncGetAttributes(&fa, attention_tcgen05_kernel);
-        if (e != cudaSuccess || fa.numRegs != LAUNCH_REGS)   // the trade of registers between the warpgroups is worked out for this number
-            RMX_FAIL("attention_tcgen05: built with %d registers a thread, not %d", e == cudaSuccess ? fa.numRegs : -1, LAUNCH_REGS);
-    }
-    // blocks are handed to the SMs in the order x, then y: all kv heads of the tile that sees the most keys first
-    attention_tcgen05_kernel<<<dim3(nkv, n_tiles, n_splits), THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
-    RMX_CHECK_LAUNCH("attention_tcgen05");
-    if (n_splits > 1) {
+    if (q_map(&mq, q, n_tokens, nq, group, p.tq, hd) != 0) return -1;
+    if (pool_map(&mk, k_pool, pool_rows, p.box_rows, hd) != 0) return -1;
+    if (pool_map(&mv, v_pool, pool_rows, p.box_rows, hd) != 0) return -1;
+    if (n_splits > 1)
         RMX_REQUIRE(first_token >= 0 && run_tokens > 0 && first_token + run_tokens <= n_tokens, "attention_tcgen05: the tokens of this launch are not among the step's");
-        attention_tcgen05_merge_kernel<<<(run_tokens * nq + 3) / 4, 128, 0, (cudaStream_t)stream>>>(part_o, part_ml, (__nv_bfloat16*)out, p.n_rows, n_splits,
-                                                                                                  first_token * nq, run_tokens * nq);
-        RMX_CHECK_LAUNCH("attention_tcgen05_merge");
-    }
-    return 0;
+    return hd == 64 ? launch<64>(mq, mk, mv, p, n_tiles, first_token, run_tokens, (cudaStream_t)stream)
+                    : launch<128>(mq, mk, mv, p, n_tiles, first_token, run_tokens, (cudaStream_t)stream);
 }

@@ -632,12 +632,12 @@ def test_gemm_tcgen05_refuses_what_it_cannot_do():
 @pytest.mark.parametrize("nq, nkv, page, window", [(32, 8, 64, 0), (8, 8, 16, 0), (16, 1, 8, 0), (4, 2, 32, 50), (8, 2, 128, 0),
                                                    (32, 8, 64, 300)])
 @pytest.mark.parametrize("per_block, runs", [(1, 1), (2, 1), (2, 3), (1, 2)])
-def test_attention_tcgen05_over_pages(nq, nkv, page, window, per_block, runs):
-    """Prompt portions on the tcgen05 tensor cores (head size 128): several sequences whose portions span
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attention_tcgen05_over_pages(nq, nkv, page, window, per_block, runs, hd):
+    """Prompt portions on the tcgen05 tensor cores (head sizes 128 and 64): several sequences whose portions span
     more than one tile of 128 rows and several key tiles, beside short ones; NaN in every slot of the pool
     that must not be read.  With two query tiles a block (they share the key tiles) and with one; with every
     tile's keys in one run and in several (some of which are empty for short sequences)."""
-    hd = 128
     torch.manual_seed(nq * 100 + page)
     lengths = [300, 40, 33, 130, 700, 64, 1]
     new = [170, 40, 5, 130, 260, 64, 1]
@@ -735,14 +735,14 @@ def test_attention_tcgen05_finds_a_far_key_and_respects_the_window_edge():
 
 
 @pytest.mark.parametrize("shape", ["rising", "falling", "steps", "wide", "flat"])
-@pytest.mark.parametrize("per_block, runs", [(2, 1), (1, 1), (2, 3)])
-def test_attention_tcgen05_when_the_reference_has_to_move(shape, per_block, runs):
+@pytest.mark.parametrize("per_block, runs, hd", [(2, 1, 128), (1, 1, 128), (2, 3, 128), (2, 1, 64), (2, 2, 64)])
+def test_attention_tcgen05_when_the_reference_has_to_move(shape, per_block, runs, hd):
     """The kernel takes exponentials against a reference that it moves only when a score exceeds it by 2^8: a pair of
     key tiles is tried in one pass and done again where that pass meets a larger score.  Scores that rise with the
     key's position make every pair move the reference (and rescale O); scores that fall never do after the first
     keys; steps move it in the middle of a pair for some rows only; a wide spread mixes all of it; flat scores are
     all equal.  Key j is a multiple of one direction, so the score of (query, key j) is known."""
-    nq, nkv, hd, page = 8, 2, 128, 64
+    nq, nkv, page = 8, 2, 64
     lengths, new = [1500, 333], [330, 333]
     k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, torch.bfloat16, seed=len(shape))
     torch.manual_seed(7)
